@@ -1,0 +1,357 @@
+"""Benchmark of the paged-KV attention hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Prints ONE JSON line.  Headline: paged bf16 GQA decode at serving scale (batch
+128, 64 query heads, 8 KV heads, head_dim 128, 64-token pages, cached lengths
+uniform in [1024, 32768], fused one-token append, causal), reported as KV bytes
+read per second (the reference benchmark's kv_bytes_read accounting).  A step
+is one decode call over the whole batch.
+
+* value: device-resident inputs, timed with CUDA events on the launch stream.
+* e2e: the same step through flywheel_tpu.flash_attn_with_kvcache with the
+  per-step inputs (q, new k/v, lengths, block table) in pinned host memory and
+  the output read back to the host inside the timed region; the KV cache stays
+  resident on the device, as it does in serving.
+* roofline: algorithmic KV bytes per launch / measured launch time, against
+  the measured HBM copy bandwidth in MEASURED_PEAKS.json.
+* cpu_baseline: the NumPy restatement of the reference's test oracle on a
+  bounded sample of the same workload, on the host cores.
+* --impl reference: that CPU restatement as its own arm (the reference itself
+  needs JAX, which this image lacks).
+
+With N > 1 (torchrun) every rank runs its own copy of the workload with its own
+seed (requests shard with no communication); value is the sum of bytes over
+ranks divided by the slowest rank's time.
+"""
+
+from __future__ import annotations
+
+import argparse
+import ctypes
+import json
+import os
+import pathlib
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = pathlib.Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT / "flywheel-tpu_b200"))
+sys.path.insert(0, str(ROOT))
+
+BATCH, HQ, HK, D, PAGE = 128, 64, 8, 128, 64
+LEN_LO, LEN_HI = 1024, 32768
+FALLBACK_HBM_GBS = 6650.0
+
+
+def measured_peaks():
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        data = json.loads(path.read_text())
+        return float(data["hbm_gbs"]), float(data.get("bf16_tflops", 0)), "measured"
+    return FALLBACK_HBM_GBS, 1590.0, "fallback"
+
+
+class ClockSampler(threading.Thread):
+    """Samples SM clock and throttle reasons through NVML (read-only) while the
+    timed region runs."""
+
+    def __init__(self, index):
+        super().__init__(daemon=True)
+        self.index, self.samples, self.reasons, self.max_mhz = index, [], set(), None
+        self.stop_flag = threading.Event()
+
+    def run(self):
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            handle = pynvml.nvmlDeviceGetHandleByIndex(self.index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(handle, pynvml.NVML_CLOCK_SM)
+            names = {
+                getattr(pynvml, "nvmlClocksThrottleReasonHwSlowdown", 0x8): "hw_slowdown",
+                getattr(pynvml, "nvmlClocksThrottleReasonHwThermalSlowdown", 0x40): "hw_thermal_slowdown",
+                getattr(pynvml, "nvmlClocksThrottleReasonSwThermalSlowdown", 0x20): "sw_thermal_slowdown",
+                getattr(pynvml, "nvmlClocksThrottleReasonSwPowerCap", 0x4): "sw_power_cap",
+            }
+            while not self.stop_flag.is_set():
+                self.samples.append(pynvml.nvmlDeviceGetClockInfo(handle, pynvml.NVML_CLOCK_SM))
+                mask = pynvml.nvmlDeviceGetCurrentClocksThrottleReasons(handle)
+                for bit, name in names.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+                time.sleep(0.05)
+        except Exception as exc:  # pylint: disable=broad-except
+            self.reasons.add(f"nvml_unavailable:{type(exc).__name__}")
+
+    def summary(self):
+        self.stop_flag.set()
+        self.join(timeout=2)
+        med = float(np.median(self.samples)) if self.samples else None
+        return {"sm_mhz": med, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
+                "samples": len(self.samples)}
+
+
+def physical_gpu_index(local_index):
+    visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+    if visible:
+        try:
+            return int(visible.split(",")[local_index])
+        except (ValueError, IndexError):
+            return local_index
+    return local_index
+
+
+def build_workload(seed, device):
+    """The serving-scale decode workload on `device`: returns a dict of device
+    tensors plus the host copies of the per-step inputs."""
+    import torch
+    from flywheel_tpu.testing import workloads
+    rng = np.random.default_rng(seed)
+    lens = rng.integers(LEN_LO, LEN_HI + 1, BATCH).astype(np.int32)
+    table, pool_pages = workloads.paged_table(rng, lens, 1, PAGE, slack=0.10)
+    gen = torch.Generator(device=device)
+    gen.manual_seed(seed)
+    pool = torch.empty((pool_pages, PAGE, 2 * HK, D), dtype=torch.bfloat16, device=device)
+    chunk = 4096
+    for lo in range(0, pool_pages, chunk):
+        hi = min(pool_pages, lo + chunk)
+        pool[lo:hi] = torch.randn((hi - lo, PAGE, 2 * HK, D), generator=gen, device=device,
+                                  dtype=torch.float32).to(torch.bfloat16)
+    host = {
+        "q": torch.randn((BATCH, 1, HQ, D), dtype=torch.float32).to(torch.bfloat16).pin_memory(),
+        "k": torch.randn((BATCH, 1, HK, D), dtype=torch.float32).to(torch.bfloat16).pin_memory(),
+        "v": torch.randn((BATCH, 1, HK, D), dtype=torch.float32).to(torch.bfloat16).pin_memory(),
+        "lens": torch.from_numpy(lens).pin_memory(),
+        "table": torch.from_numpy(table).pin_memory(),
+    }
+    dev = {name: t.to(device) for name, t in host.items()}
+    kv_bytes = workloads.decode_kv_bytes(lens, 1, HK, D, 2)
+    return {"pool": pool, "host": host, "dev": dev, "lens": lens, "table": table,
+            "kv_bytes": kv_bytes, "pool_pages": pool_pages}
+
+
+def make_decode_call(work, device):
+    """A closure that enqueues one decode step through the C ABI on device
+    buffers (no host traffic), and the output tensor it fills."""
+    import torch
+    from flywheel_tpu.softmax_attention import _native
+    dev = work["dev"]
+    out = torch.empty_like(dev["q"])
+    args = _native.FwDecodeArgs(
+        q=dev["q"].data_ptr(), out=out.data_ptr(), kv_cache=work["pool"].data_ptr(),
+        k_new=dev["k"].data_ptr(), v_new=dev["v"].data_ptr(),
+        cache_seqlens=dev["lens"].data_ptr(), block_table=dev["table"].data_ptr(),
+        num_pages=work["pool"].shape[0], page_size=PAGE, pages_per_seq=dev["table"].shape[1],
+        batch=BATCH, seqlen_q=1, nheads=HQ, nheads_k=HK, head_dim=D, kv_dtype=0, causal=1,
+        window_left=-1, softmax_scale=D ** -0.5, softcap=0.0, num_ctas=0)
+    lib = _native.library()
+    nbytes = lib.fw_decode_workspace_bytes(ctypes.byref(args))
+    if nbytes == 0:
+        raise RuntimeError(_native.last_error())
+    scratch = torch.zeros(nbytes, dtype=torch.uint8, device=device)
+    args.workspace, args.workspace_bytes = scratch.data_ptr(), nbytes
+    stream = torch.cuda.current_stream(device).cuda_stream
+
+    def call():
+        _native.check(lib.fw_decode_kvcache(ctypes.byref(args), stream))
+
+    return call, out, scratch
+
+
+def cpu_baseline(work, budget_bytes=1.0e9):
+    """Times the NumPy restatement of the reference's oracle on the first few
+    requests of the workload (about `budget_bytes` of KV) on the host cores."""
+    import torch
+    from flywheel_tpu.softmax_attention import _arrays
+    from oracle import paged_attention as oracle
+    lens, table = work["lens"], work["table"]
+    count, acc = 0, 0
+    while count < len(lens) and acc < budget_bytes:
+        acc += (int(lens[count]) + 1) * 2 * HK * D * 2
+        count += 1
+    used_pages = np.unique(np.concatenate(
+        [table[b, : -(-(int(lens[b]) + 1) // PAGE)] for b in range(count)]))
+    remap = np.zeros(work["pool_pages"], np.int32)
+    remap[used_pages] = np.arange(len(used_pages), dtype=np.int32)
+    pool = _arrays.to_host_numpy(work["pool"][torch.from_numpy(used_pages).to(work["pool"].device).long()])
+    host = work["host"]
+    q = _arrays.to_host_numpy(host["q"][:count])
+    k = _arrays.to_host_numpy(host["k"][:count])
+    v = _arrays.to_host_numpy(host["v"][:count])
+    sample_table = remap[table[:count]]
+    start = time.perf_counter()
+    out, _, _ = oracle.kvcache_paged(q, pool, k, v, lens[:count], sample_table, nheads_k=HK, causal=True)
+    seconds = time.perf_counter() - start
+    return {"value": acc / seconds / 1e9, "unit": "GB/s", "cores": os.cpu_count(), "kind": "port",
+            "sample": f"first {count} of {BATCH} requests ({acc / 1e9:.2f} GB of KV), "
+                      f"{seconds:.2f} s, NumPy (BLAS threads = host cores)"}, out, count
+
+
+def run_reference_arm(ns):
+    """The reference's CPU path stands in as the NumPy restatement of its own
+    test oracle (the reference needs JAX, absent from this image)."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from flywheel_tpu.testing import workloads
+    from oracle import paged_attention as oracle
+    rng = np.random.default_rng(0)
+    lens = rng.integers(LEN_LO, LEN_HI + 1, BATCH).astype(np.int32)
+    sample = 8
+    table, pool_pages = workloads.paged_table(rng, lens[:sample], 1, PAGE, slack=0.10)
+    draw = lambda shape: rng.standard_normal(shape, dtype=np.float32).astype(oracle.BF16)
+    pool = draw((pool_pages, PAGE, 2 * HK, D))
+    q, k, v = draw((sample, 1, HQ, D)), draw((sample, 1, HK, D)), draw((sample, 1, HK, D))
+    nbytes = workloads.decode_kv_bytes(lens[:sample], 1, HK, D, 2)
+    times = []
+    for step in range(ns.warmup + ns.steps):
+        start = time.perf_counter()
+        oracle.kvcache_paged(q, pool, k, v, lens[:sample], table, nheads_k=HK, causal=True)
+        if step >= ns.warmup:
+            times.append(time.perf_counter() - start)
+    ms = 1e3 * float(np.mean(times))
+    value = nbytes / (ms * 1e-3) / 1e9
+    sample_text = (f"first {sample} of {BATCH} requests per step ({nbytes / 1e9:.2f} GB of KV); "
+                   "NumPy restatement of the reference's test oracle")
+    print(json.dumps({
+        "impl": "reference", "metric": "paged_decode_kv_read_bandwidth", "value": value, "unit": "GB/s",
+        "n_gpus": ns.gpus, "steps": ns.steps, "warmup": ns.warmup, "ms_per_step": ms,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic", "config": workload_config(),
+        "cpu_baseline": {"value": value, "unit": "GB/s", "cores": os.cpu_count(), "kind": "port",
+                         "sample": sample_text},
+        "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+def workload_config():
+    return {"workload": "paged bf16 GQA decode, batch 128, 64 q heads, 8 kv heads, head_dim 128, "
+                        "page 64, cached lengths U[1024,32768], pool = pages in use + 10%, random block "
+                        "table, fused one-token append, causal",
+            "l2": "inputs (about 9 GB of KV per step) far exceed the 126 MB L2",
+            "sharding": "one independent copy of the workload per GPU (request sharding, no collective)"}
+
+
+def main():
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=20)
+    parser.add_argument("--warmup", type=int, default=3)
+    parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    parser.add_argument("--skip-cpu-baseline", action="store_true")
+    ns = parser.parse_args()
+    ns.warmup = max(ns.warmup, 3) if ns.impl == "ours" else ns.warmup
+    if ns.impl == "reference":
+        run_reference_arm(ns)
+        return
+
+    import torch
+    import torch.distributed as dist
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device; there is no CPU path.")
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    from flywheel_tpu import flash_attn_with_kvcache
+    work = build_workload(seed=rank, device=device)
+    call, out, scratch = make_decode_call(work, device)
+
+    # ---- device-resident arm
+    for _ in range(ns.warmup):
+        call()
+    barrier()
+    sampler = ClockSampler(physical_gpu_index(local_rank))
+    sampler.start()
+    starts = [torch.cuda.Event(enable_timing=True) for _ in range(ns.steps)]
+    ends = [torch.cuda.Event(enable_timing=True) for _ in range(ns.steps)]
+    whole_start, whole_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    whole_start.record()
+    for i in range(ns.steps):
+        starts[i].record()
+        call()
+        ends[i].record()
+    whole_end.record()
+    barrier()
+    clocks = sampler.summary()
+    total_ms = whole_start.elapsed_time(whole_end)
+    launch_ms = float(np.mean([s.elapsed_time(e) for s, e in zip(starts, ends)]))
+    from flywheel_tpu.softmax_attention import _native
+    status = _native.read_status(scratch, device)
+    if status != 0:
+        raise RuntimeError(f"decode kernel reported device status {status}")
+
+    # ---- end-to-end arm: host inputs in, host output back, every step
+    host = work["host"]
+    out_host = torch.empty_like(host["q"]).pin_memory()
+
+    def e2e_step():
+        result, _ = flash_attn_with_kvcache(
+            host["q"], work["pool"], None, host["k"], host["v"], cache_seqlens=host["lens"],
+            block_table=host["table"], causal=True)
+        out_host.copy_(result)      # device -> pinned host, synchronous
+
+    for _ in range(ns.warmup):
+        e2e_step()
+    barrier()
+    e2e_start, e2e_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e2e_start.record()
+    for _ in range(ns.steps):
+        e2e_step()
+    e2e_end.record()
+    barrier()
+    e2e_ms = e2e_start.elapsed_time(e2e_end)
+    h2d = sum(host[name].numel() * host[name].element_size() for name in ("q", "k", "v", "lens", "table"))
+    d2h = out_host.numel() * out_host.element_size()
+
+    times = torch.tensor([total_ms, e2e_ms, launch_ms], dtype=torch.float64, device=device)
+    nbytes = torch.tensor([float(work["kv_bytes"])], dtype=torch.float64, device=device)
+    if world > 1:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+        dist.all_reduce(nbytes, op=dist.ReduceOp.SUM)
+    total_ms, e2e_ms, launch_ms = (float(x) for x in times.tolist())
+    job_bytes = float(nbytes.item())
+
+    if rank == 0:
+        hbm_peak, _, peak_kind = measured_peaks()
+        value = job_bytes * ns.steps / (total_ms * 1e-3) / 1e9
+        achieved = work["kv_bytes"] / (launch_ms * 1e-3) / 1e9
+        line = {
+            "metric": "paged_decode_kv_read_bandwidth", "value": value, "unit": "GB/s", "n_gpus": world,
+            "steps": ns.steps, "warmup": ns.warmup, "ms_per_step": total_ms / ns.steps,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic", "config": workload_config(), "per_gpu": value / world,
+            "clocks": clocks, "gpu_launches": 2 * ns.steps,
+            "e2e": {"value": job_bytes * ns.steps / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s",
+                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "ms_per_step": e2e_ms / ns.steps},
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s",
+                         "frac": achieved / hbm_peak, "traffic": None, "peak_kind": f"of {peak_kind}",
+                         "kernel": "fw::decode_kernel<bf16> (+ combine_kernel, <1% of the launch pair)",
+                         "algorithmic_bytes_per_launch": work["kv_bytes"],
+                         "frac_of_nominal_8TBs": achieved / 8000.0},
+        }
+        if world == 1 and not ns.skip_cpu_baseline:
+            base, cpu_out, count = cpu_baseline(work)
+            line["cpu_baseline"] = base
+            got = out[:count].float().cpu().numpy()
+            line["sample_max_abs_err_vs_cpu"] = float(np.abs(got - cpu_out).max())
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

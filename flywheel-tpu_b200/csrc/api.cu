@@ -1,0 +1,103 @@
+// Host-side plumbing of the C ABI: thread-local error text, device queries,
+// tensor-map encoding through the driver entry point (no link-time dependency
+// on libcuda), status read-back.
+#include <cstdarg>
+#include <cstdio>
+#include <mutex>
+
+#include "common.cuh"
+
+namespace fw {
+
+static thread_local char g_error[512] = "";
+
+void set_error(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_error, sizeof(g_error), fmt, ap);
+  va_end(ap);
+}
+
+int sm_count() {
+  // Read once per device; the table is write-once data, so concurrent callers
+  // at worst repeat the query.
+  static int cached[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  if (cached[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    cached[dev] = n;
+  }
+  return cached[dev];
+}
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                   CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                   CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess) {
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+    }
+  });
+  return fn;
+}
+
+int encode_tensor_map_u8_4d(CUtensorMap* map, const void* base, const uint64_t dims[4],
+                            const uint64_t strides[3], const uint32_t box[4]) {
+  EncodeTiledFn fn = encode_fn();
+  if (fn == nullptr) {
+    set_error("cuTensorMapEncodeTiled is not available from this driver.");
+    return FW_ERR_LAUNCH;
+  }
+  cuuint64_t gdims[4] = {dims[0], dims[1], dims[2], dims[3]};
+  cuuint64_t gstrides[3] = {strides[0], strides[1], strides[2]};
+  cuuint32_t gbox[4] = {box[0], box[1], box[2], box[3]};
+  cuuint32_t estrides[4] = {1, 1, 1, 1};
+  CUresult res = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<void*>(base), gdims, gstrides, gbox,
+                    estrides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (res != CUDA_SUCCESS) {
+    set_error("cuTensorMapEncodeTiled failed with CUresult %d (dims %llu,%llu,%llu,%llu strides %llu,%llu,%llu "
+              "box %u,%u,%u,%u)",
+              static_cast<int>(res), (unsigned long long)dims[0], (unsigned long long)dims[1],
+              (unsigned long long)dims[2], (unsigned long long)dims[3], (unsigned long long)strides[0],
+              (unsigned long long)strides[1], (unsigned long long)strides[2], box[0], box[1], box[2], box[3]);
+    return FW_ERR_LAUNCH;
+  }
+  return FW_OK;
+}
+
+}  // namespace fw
+
+extern "C" const char* fw_last_error(void) { return fw::g_error; }
+
+extern "C" int fw_version(void) { return 1; }
+
+extern "C" int fw_read_status(const void* workspace, void* stream, int32_t* status) {
+  if (workspace == nullptr || status == nullptr) {
+    fw::set_error("workspace and status must not be NULL.");
+    return FW_ERR_WORKSPACE;
+  }
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  cudaError_t err = cudaMemcpyAsync(status, workspace, sizeof(int32_t), cudaMemcpyDeviceToHost, s);
+  if (err == cudaSuccess) err = cudaStreamSynchronize(s);
+  if (err != cudaSuccess) {
+    fw::set_error("reading the status word: %s", cudaGetErrorString(err));
+    return FW_ERR_LAUNCH;
+  }
+  if (*status != FW_STATUS_OK) {
+    // The word is sticky on the device; clear it once it has been reported.
+    cudaMemsetAsync(const_cast<void*>(workspace), 0, sizeof(int32_t), s);
+    cudaStreamSynchronize(s);
+  }
+  return FW_OK;
+}

@@ -1,0 +1,910 @@
+// Split-KV decode over a paged (merged [k0,v0,k1,v1,...]) or contiguous KV
+// cache with the new tokens' K/V append fused into the same launch, plus the
+// log-sum-exp combine of the per-CTA partial states.
+//
+// Behaviour follows flash_attn_with_kvcache of the reference project
+// (flywheel_tpu/softmax_attention/decode.py:189-625 and the kernel it calls,
+// kernels/decode.py:463-1914): append at cache_seqlens[b] + t, bottom-right
+// aligned causal / left-window mask, softcap before masking, sinks in the
+// denominator only, out 0 / lse -inf (or the sink) for rows that see no key.
+//
+// Design (B200): the flattened list of 16-token KV tiles of all requests is cut
+// into equal contiguous ranges, one per persistent CTA (one CTA per SM), so
+// every SM streams the same number of bytes whatever the length distribution.
+// A CTA owns up to 8 KV heads of its token rows: one producer warp walks the
+// block table and issues one tiled TMA copy per 16-token stage (128-byte
+// swizzle, token-major inside each 128-byte head segment, so ldmatrix is
+// bank-conflict free), guarded by full/empty mbarriers with bounded waits.
+// Consumer warp w owns one KV head (and one 16-row slice of its GQA query
+// rows): QK^T and PV run on mma.sync m16n8k16 with the softmax state in
+// registers (quad shuffles for row max / row sum), so each KV byte is read
+// from HBM once and from shared memory once per 16 query rows.  fp8 pages are
+// widened to f16 in registers straight out of ldmatrix.  Each (CTA, request)
+// segment leaves an un-normalised (o, m, l) partial; the combine kernel merges
+// the segments of a request, folds the sink and v_descale and writes bf16.
+#include "common.cuh"
+
+namespace fw {
+
+constexpr int kTile = 16;          // tokens per pipeline stage
+constexpr int kMaxStages = 8;
+constexpr int kMaxConsumerWarps = 8;
+constexpr int kHeadDim = 128;
+constexpr int kMaxInlineBatch = 2048;  // requests whose tile counts fit the CTA-local scan
+
+struct DecodeParams {
+  const __nv_bfloat16* q;
+  const uint8_t* k_new;
+  const uint8_t* v_new;
+  uint8_t* k_base;
+  uint8_t* v_base;
+  const int* cache_seqlens;
+  const int* block_table;
+  const int* cache_batch_idx;
+  const int* num_active;
+  const float* k_descale;
+  float* part_o;
+  float* part_ml;
+  int* status;
+  long long num_pages;
+  int page_size, pages_per_seq, batch, seqlen_q, nheads, nheads_k, group;
+  int hpc, mt, nhg, ncta;
+  int merged;
+  int row_bytes;    // bytes of one token row of the tensor k_base points at
+  int plane_bytes;  // head_dim * itemsize
+  int spp;          // 128-byte segments per head plane
+  int stages, stage_bytes;
+  int has_new, causal, window_left;
+  int zero_pad_head;  // fp8 merged pool with an odd nheads_k: append zeroes the pad head
+  float scale, softcap;
+};
+
+struct Span {
+  int total, cache_len, first_tile, n_tiles;
+};
+
+__device__ __forceinline__ Span request_span(const DecodeParams& p, int b, int n_active) {
+  Span s{0, 0, 0, 0};
+  if (b >= n_active) return s;
+  int len = max(p.cache_seqlens[b], 0);
+  s.cache_len = len;
+  s.total = len + (p.has_new ? p.seqlen_q : 0);
+  if (s.total <= 0) return s;
+  int first_key = (p.window_left >= 0) ? max(0, s.total - p.seqlen_q - p.window_left) : 0;
+  s.first_tile = first_key / kTile;
+  s.n_tiles = (s.total + kTile - 1) / kTile - s.first_tile;
+  return s;
+}
+
+__device__ __forceinline__ int load_num_active(const DecodeParams& p) {
+  return p.num_active ? min(p.batch, max(0, *p.num_active)) : p.batch;
+}
+
+// Exclusive prefix of per-request tile counts into pre[0..batch]; every thread
+// of the block must call it.  pre lives in shared memory.
+__device__ __forceinline__ void scan_tiles(const DecodeParams& p, int n_active, int* pre) {
+  const int tid = threadIdx.x, nthreads = blockDim.x;
+  for (int b = tid; b < p.batch; b += nthreads) pre[b + 1] = request_span(p, b, n_active).n_tiles;
+  if (tid == 0) pre[0] = 0;
+  __syncthreads();
+  if (tid < 32) {
+    int carry = 0;
+    for (int base = 0; base < p.batch; base += 32) {
+      int idx = base + tid;
+      int v = idx < p.batch ? pre[idx + 1] : 0;
+#pragma unroll
+      for (int off = 1; off < 32; off <<= 1) {
+        int n = __shfl_up_sync(0xffffffffu, v, off);
+        if (tid >= off) v += n;
+      }
+      if (idx < p.batch) pre[idx + 1] = v + carry;
+      carry += __shfl_sync(0xffffffffu, v, 31);
+    }
+  }
+  __syncthreads();
+}
+
+// Largest b with pre[b] <= f (f < pre[batch]).
+__device__ __forceinline__ int find_request(const int* pre, int batch, int f) {
+  int lo = 0, hi = batch;
+  while (hi - lo > 1) {
+    int mid = (lo + hi) >> 1;
+    if (pre[mid] <= f) lo = mid; else hi = mid;
+  }
+  return lo;
+}
+
+__device__ __forceinline__ void cta_range(long long nt, int ncta, int cta, int& f0, int& f1) {
+  f0 = static_cast<int>(nt * cta / ncta);
+  f1 = static_cast<int>(nt * (cta + 1) / ncta);
+}
+
+// Segment index of head hl's K / V plane inside a stage, in units of
+// (kTile * 128) bytes.
+__device__ __forceinline__ int k_seg(const DecodeParams& p, int hl) {
+  return p.merged ? 2 * hl * p.spp : hl * p.spp;
+}
+__device__ __forceinline__ int v_seg(const DecodeParams& p, int hl) {
+  return p.merged ? (2 * hl + 1) * p.spp : (p.hpc + hl) * p.spp;
+}
+
+template <int KVT>
+__global__ void __launch_bounds__((kMaxConsumerWarps + 1) * 32, 1)
+decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+              const DecodeParams p) {
+  constexpr bool kFp8 = KVT != FW_DTYPE_BF16;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint8_t* stage_base = smem;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + p.stages * p.stage_bytes);
+  uint64_t* empty_bar = full_bar + kMaxStages;
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(empty_bar + kMaxStages);
+  int* pre = const_cast<int*>(abort_flag) + 4;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int cta = blockIdx.x, hg = blockIdx.y;
+  const int n_active = load_num_active(p);
+  const int heads_here = min(p.hpc, p.nheads_k - hg * p.hpc);
+  const int consumer_warps = heads_here * p.mt;
+  const int producer_warp = p.hpc * p.mt;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < p.stages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], consumer_warps);
+    }
+    *abort_flag = 0;
+    fence_barrier_init();
+  }
+  scan_tiles(p, n_active, pre);  // contains __syncthreads
+
+  const long long nt = pre[p.batch];
+  int f0, f1;
+  cta_range(nt, p.ncta, cta, f0, f1);
+  if (f0 >= f1) return;
+
+  // ------------------------------------------------------------ producer
+  if (warp == producer_warp) {
+    if (lane != 0) return;
+    tma_prefetch_desc(&map_k);
+    if (!p.merged) tma_prefetch_desc(&map_v);
+    int stage = 0;
+    uint32_t phase = 0;
+    int issued = 0;
+    bool ok = true;
+    int b = find_request(pre, p.batch, f0);
+    for (int f = f0; f < f1 && ok;) {
+      while (pre[b + 1] <= f) ++b;
+      const Span sp = request_span(p, b, n_active);
+      const int seg_end = min(f1, pre[b + 1]);
+      int cur_page_idx = -1, cur_page = 0;
+      for (; f < seg_end; ++f) {
+        const int pos0 = (f - pre[b] + sp.first_tile) * kTile;
+        const int page_idx = pos0 / p.page_size;
+        if (page_idx != cur_page_idx) {
+          cur_page_idx = page_idx;
+          int page = p.merged ? p.block_table[static_cast<long long>(b) * p.pages_per_seq + page_idx]
+                              : (p.cache_batch_idx ? p.cache_batch_idx[b] : b);
+          if (page < 0 || page >= p.num_pages) {
+            report_status(p.status, FW_STATUS_BAD_PAGE);
+            page = 0;
+          }
+          cur_page = page;
+        }
+        if (!mbar_wait_bounded(&empty_bar[stage], phase ^ 1, abort_flag)) {
+          ok = false;
+          break;
+        }
+        uint8_t* dst = stage_base + stage * p.stage_bytes;
+        mbar_arrive_expect_tx(&full_bar[stage], p.stage_bytes);
+        const int tok = pos0 - page_idx * p.page_size;
+        if (p.merged) {
+          tma_load_4d(dst, &map_k, &full_bar[stage], 0, tok, hg * p.hpc * 2 * p.spp, cur_page);
+        } else {
+          tma_load_4d(dst, &map_k, &full_bar[stage], 0, tok, hg * p.hpc * p.spp, cur_page);
+          tma_load_4d(dst + p.stage_bytes / 2, &map_v, &full_bar[stage], 0, tok,
+                      hg * p.hpc * p.spp, cur_page);
+        }
+        ++issued;
+        if (++stage == p.stages) {
+          stage = 0;
+          phase ^= 1;
+        }
+      }
+    }
+    if (!ok) {
+      // A wait gave up: record it, tell the consumers, and let the copies that
+      // are still in flight land before this CTA's shared memory goes away.
+      *abort_flag = 1;
+      report_status(p.status, FW_STATUS_WAIT_TIMEOUT);
+      const int pending = min(issued, p.stages);
+      for (int i = 0; i < pending; ++i) {
+        if (stage == 0) {
+          stage = p.stages;
+          phase ^= 1;
+        }
+        --stage;
+        for (uint32_t spin = 0; spin < (1u << 16) && !mbar_try_wait(&full_bar[stage], phase); ++spin) {
+          __nanosleep(64);
+        }
+      }
+    }
+    return;
+  }
+
+  // ------------------------------------------------------------ consumers
+  if (warp >= consumer_warps) return;
+  const int hl = warp / p.mt, mti = warp - hl * p.mt;
+  const int h = hg * p.hpc + hl;             // KV head
+  const int rows_per_head = p.seqlen_q * p.group;
+  const int quad = lane >> 2, tq = lane & 3;
+  const int row0 = mti * 16 + quad, row1 = row0 + 8;
+  const bool row0_ok = row0 < rows_per_head, row1_ok = row1 < rows_per_head;
+  const int t0 = row0 / p.group, g0 = row0 - t0 * p.group;
+  const int t1 = row1 / p.group, g1 = row1 - t1 * p.group;
+  const int rq = p.seqlen_q * p.nheads;      // partial rows per slot
+  const int seg_bytes = kTile * 128;
+  const uint32_t stage_u32 = smem_u32(stage_base);
+  const int kseg = k_seg(p, hl), vseg = v_seg(p, hl);
+
+  const float kd = p.k_descale ? *p.k_descale : 1.0f;
+  const float c1 = p.softcap > 0.f ? p.scale * kd / p.softcap : p.scale * kd * kLog2e;
+  const float c2 = p.softcap * kLog2e;
+
+  int stage = 0;
+  uint32_t phase = 0;
+  bool ok = true;
+
+  int b = find_request(pre, p.batch, f0);
+  for (int f = f0; f < f1 && ok;) {
+    while (pre[b + 1] <= f) ++b;
+    const Span sp = request_span(p, b, n_active);
+    const int seg_end = min(f1, pre[b + 1]);
+
+    // ---- Q fragments of this warp's 16 rows (zero for rows past the window)
+    uint32_t qa[8][4];
+    {
+      const __nv_bfloat16* q0 =
+          p.q + ((static_cast<long long>(b) * p.seqlen_q + t0) * p.nheads + h * p.group + g0) * kHeadDim;
+      const __nv_bfloat16* q1 =
+          p.q + ((static_cast<long long>(b) * p.seqlen_q + t1) * p.nheads + h * p.group + g1) * kHeadDim;
+#pragma unroll
+      for (int ks = 0; ks < 8; ++ks) {
+        if constexpr (!kFp8) {
+          const int d = ks * 16 + 2 * tq;
+          qa[ks][0] = row0_ok ? *reinterpret_cast<const uint32_t*>(q0 + d) : 0u;
+          qa[ks][1] = row1_ok ? *reinterpret_cast<const uint32_t*>(q1 + d) : 0u;
+          qa[ks][2] = row0_ok ? *reinterpret_cast<const uint32_t*>(q0 + d + 8) : 0u;
+          qa[ks][3] = row1_ok ? *reinterpret_cast<const uint32_t*>(q1 + d + 8) : 0u;
+        } else {
+          // fp8 K comes out of ldmatrix four consecutive head_dim elements per
+          // thread, so the contraction index is permuted the same way here.
+          const int d = ks * 16 + 4 * tq;
+          uint2 v0 = row0_ok ? *reinterpret_cast<const uint2*>(q0 + d) : make_uint2(0u, 0u);
+          uint2 v1 = row1_ok ? *reinterpret_cast<const uint2*>(q1 + d) : make_uint2(0u, 0u);
+          auto to_f16 = [](uint32_t two_bf16) {
+            float lo = __uint_as_float(two_bf16 << 16), hi = __uint_as_float(two_bf16 & 0xffff0000u);
+            return pack_f16(lo, hi);
+          };
+          qa[ks][0] = to_f16(v0.x);
+          qa[ks][1] = to_f16(v1.x);
+          qa[ks][2] = to_f16(v0.y);
+          qa[ks][3] = to_f16(v1.y);
+        }
+      }
+    }
+    float o[16][4];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+    // Bottom-right diagonals of the two rows this thread owns.
+    const int diag0 = sp.total - p.seqlen_q + t0, diag1 = sp.total - p.seqlen_q + t1;
+
+    for (; f < seg_end; ++f) {
+      const int pos0 = (f - pre[b] + sp.first_tile) * kTile;
+      if (!mbar_wait_bounded(&full_bar[stage], phase, abort_flag)) {
+        ok = false;
+        break;
+      }
+      const uint32_t st = stage_u32 + stage * p.stage_bytes;
+      uint8_t* st_ptr = stage_base + stage * p.stage_bytes;
+
+      // ---- boundary tile: patch in the new tokens (and write them to their
+      // page), and zero V rows past the valid length so 0 * NaN never forms.
+      if (pos0 + kTile > sp.cache_len) {
+        const int chunks = p.plane_bytes >> 4;  // 16-byte chunks per head plane
+        for (int tk = 0; tk < kTile; ++tk) {
+          const int pos = pos0 + tk;
+          if (pos < sp.cache_len) continue;
+          const bool is_new = p.has_new && pos < sp.total;
+          const int tnew = pos - sp.cache_len;
+          uint8_t* gk = nullptr;
+          uint8_t* gv = nullptr;
+          if (is_new && mti == 0) {
+            const int page_idx = pos / p.page_size;
+            int page = p.merged ? p.block_table[static_cast<long long>(b) * p.pages_per_seq + page_idx]
+                                : (p.cache_batch_idx ? p.cache_batch_idx[b] : b);
+            if (page < 0 || page >= p.num_pages) page = 0;
+            const long long row = (static_cast<long long>(page) * p.page_size + (pos - page_idx * p.page_size)) *
+                                  p.row_bytes;
+            if (p.merged) {
+              gk = p.k_base + row + static_cast<long long>(2 * h) * p.plane_bytes;
+              gv = gk + p.plane_bytes;
+            } else {
+              gk = p.k_base + row + static_cast<long long>(h) * p.plane_bytes;
+              gv = p.v_base + row + static_cast<long long>(h) * p.plane_bytes;
+            }
+          }
+          for (int i = lane; i < 2 * chunks; i += 32) {
+            const int is_v = i >= chunks;
+            const int c = is_v ? i - chunks : i;
+            const int seg = (is_v ? vseg : kseg) + (c >> 3);
+            uint4* dst = reinterpret_cast<uint4*>(st_ptr + seg * seg_bytes + tk * 128 +
+                                                  (((c & 7) ^ (tk & 7)) << 4));
+            if (is_new) {
+              const uint8_t* src = (is_v ? p.v_new : p.k_new) +
+                                   ((static_cast<long long>(b) * p.seqlen_q + tnew) * p.nheads_k + h) *
+                                       p.plane_bytes + (c << 4);
+              const uint4 val = *reinterpret_cast<const uint4*>(src);
+              *dst = val;
+              if (gk != nullptr) *reinterpret_cast<uint4*>((is_v ? gv : gk) + (c << 4)) = val;
+              if (gk != nullptr && p.zero_pad_head && h == p.nheads_k - 1) {
+                // the fp8 pad head sits right after the last real head's V plane
+                *reinterpret_cast<uint4*>((is_v ? gv : gk) + 2 * p.plane_bytes + (c << 4)) =
+                    make_uint4(0u, 0u, 0u, 0u);
+              }
+            } else if (is_v) {
+              *dst = make_uint4(0u, 0u, 0u, 0u);
+            }
+          }
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+      }
+
+      // ---- S = Q K^T for 16 keys (two 8-key n-tiles)
+      float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+      if constexpr (!kFp8) {
+        const int mi = lane >> 3;
+        const int key = ((mi >> 1) << 3) + (lane & 7);
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+          const int chunk = ks * 2 + (mi & 1);
+          const uint32_t addr = st + (kseg + (chunk >> 3)) * seg_bytes + key * 128 +
+                                (((chunk & 7) ^ (key & 7)) << 4);
+          uint32_t r0, r1, r2, r3;
+          ldmatrix_x4(addr, r0, r1, r2, r3);
+          mma_bf16(s[0], qa[ks], r0, r1);
+          mma_bf16(s[1], qa[ks], r2, r3);
+        }
+      } else {
+        const int mi = lane >> 3;
+        const int key = ((mi & 1) << 3) + (lane & 7);
+#pragma unroll
+        for (int kp = 0; kp < 4; ++kp) {
+          const int chunk = kp * 2 + (mi >> 1);
+          const uint32_t addr = st + kseg * seg_bytes + key * 128 + (((chunk & 7) ^ (key & 7)) << 4);
+          uint32_t r0, r1, r2, r3;  // (keys 0-7, c), (keys 8-15, c), (keys 0-7, c+1), (keys 8-15, c+1)
+          ldmatrix_x4(addr, r0, r1, r2, r3);
+          mma_f16(s[0], qa[2 * kp], fp8x2_to_f16x2<KVT>(r0 & 0xffff), fp8x2_to_f16x2<KVT>(r0 >> 16));
+          mma_f16(s[1], qa[2 * kp], fp8x2_to_f16x2<KVT>(r1 & 0xffff), fp8x2_to_f16x2<KVT>(r1 >> 16));
+          mma_f16(s[0], qa[2 * kp + 1], fp8x2_to_f16x2<KVT>(r2 & 0xffff), fp8x2_to_f16x2<KVT>(r2 >> 16));
+          mma_f16(s[1], qa[2 * kp + 1], fp8x2_to_f16x2<KVT>(r3 & 0xffff), fp8x2_to_f16x2<KVT>(r3 >> 16));
+        }
+      }
+
+      // ---- scale (+ softcap), mask
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          float x = s[nt][i] * c1;
+          if (p.softcap > 0.f) x = accurate_tanh(x) * c2;
+          s[nt][i] = x;
+        }
+      const bool mask_right = pos0 + kTile > sp.total - p.seqlen_q;
+      const bool mask_left = p.window_left >= 0 && pos0 < sp.total - 1 - p.window_left;
+      if (mask_right || mask_left) {
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const int j = pos0 + nt * 8 + 2 * tq + (i & 1);
+            const int diag = (i < 2) ? diag0 : diag1;
+            bool vis = j < sp.total && (!p.causal || j <= diag);
+            if (p.window_left >= 0) vis = vis && (j >= diag - p.window_left);
+            if (!vis) s[nt][i] = -INFINITY;
+          }
+      }
+
+      // ---- online softmax (rows quad and quad + 8)
+      float alpha[2];
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        float mx = fmaxf(fmaxf(s[0][2 * r], s[0][2 * r + 1]), fmaxf(s[1][2 * r], s[1][2 * r + 1]));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+        const float m_new = fmaxf(m_run[r], mx);
+        const float base = m_new == -INFINITY ? 0.f : m_new;
+        alpha[r] = fast_exp2(m_run[r] - base);
+        m_run[r] = m_new;
+        float sum = 0.f;
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt) {
+          s[nt][2 * r] = fast_exp2(s[nt][2 * r] - base);
+          s[nt][2 * r + 1] = fast_exp2(s[nt][2 * r + 1] - base);
+          sum += s[nt][2 * r] + s[nt][2 * r + 1];
+        }
+        l_run[r] = l_run[r] * alpha[r] + sum;
+      }
+      if (__any_sync(0xffffffffu, alpha[0] != 1.f || alpha[1] != 1.f)) {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          o[i][0] *= alpha[0];
+          o[i][1] *= alpha[0];
+          o[i][2] *= alpha[1];
+          o[i][3] *= alpha[1];
+        }
+      }
+
+      // ---- O += P V
+      uint32_t pa[4];
+      if constexpr (!kFp8) {
+        pa[0] = pack_bf16(s[0][0], s[0][1]);
+        pa[1] = pack_bf16(s[0][2], s[0][3]);
+        pa[2] = pack_bf16(s[1][0], s[1][1]);
+        pa[3] = pack_bf16(s[1][2], s[1][3]);
+        const int mi = lane >> 3;
+        const int key = ((mi & 1) << 3) + (lane & 7);
+#pragma unroll
+        for (int cp = 0; cp < 8; ++cp) {
+          const int chunk = cp * 2 + (mi >> 1);
+          const uint32_t addr = st + (vseg + (chunk >> 3)) * seg_bytes + key * 128 +
+                                (((chunk & 7) ^ (key & 7)) << 4);
+          uint32_t r0, r1, r2, r3;
+          ldmatrix_x4_trans(addr, r0, r1, r2, r3);
+          mma_bf16(o[2 * cp], pa, r0, r1);
+          mma_bf16(o[2 * cp + 1], pa, r2, r3);
+        }
+      } else {
+        pa[0] = pack_f16(s[0][0], s[0][1]);
+        pa[1] = pack_f16(s[0][2], s[0][3]);
+        pa[2] = pack_f16(s[1][0], s[1][1]);
+        pa[3] = pack_f16(s[1][2], s[1][3]);
+        const int mi = lane >> 3;
+        const int key = ((mi & 1) << 3) + (lane & 7);
+#pragma unroll
+        for (int cp = 0; cp < 4; ++cp) {
+          const int chunk = cp * 2 + (mi >> 1);
+          const uint32_t addr = st + vseg * seg_bytes + key * 128 + (((chunk & 7) ^ (key & 7)) << 4);
+          uint32_t r0, r1, r2, r3;  // (keys 0-7, c), (keys 8-15, c), (keys 0-7, c+1), (keys 8-15, c+1)
+          ldmatrix_x4_trans(addr, r0, r1, r2, r3);
+          // Each register holds keys (2tq, 2tq+1) x head_dim (2u, 2u+1); regroup
+          // to [even d: k0 k1 | odd d: k0 k1].
+          r0 = __byte_perm(r0, 0, 0x3120);
+          r1 = __byte_perm(r1, 0, 0x3120);
+          r2 = __byte_perm(r2, 0, 0x3120);
+          r3 = __byte_perm(r3, 0, 0x3120);
+          mma_f16(o[4 * cp + 0], pa, fp8x2_to_f16x2<KVT>(r0 & 0xffff), fp8x2_to_f16x2<KVT>(r1 & 0xffff));
+          mma_f16(o[4 * cp + 1], pa, fp8x2_to_f16x2<KVT>(r0 >> 16), fp8x2_to_f16x2<KVT>(r1 >> 16));
+          mma_f16(o[4 * cp + 2], pa, fp8x2_to_f16x2<KVT>(r2 & 0xffff), fp8x2_to_f16x2<KVT>(r3 & 0xffff));
+          mma_f16(o[4 * cp + 3], pa, fp8x2_to_f16x2<KVT>(r2 >> 16), fp8x2_to_f16x2<KVT>(r3 >> 16));
+        }
+      }
+
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&empty_bar[stage]);
+      if (++stage == p.stages) {
+        stage = 0;
+        phase ^= 1;
+      }
+    }
+    if (!ok) break;
+
+    // ---- partial state of this (CTA, request) segment
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
+      l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
+    }
+    const long long slot = static_cast<long long>(b) + cta;
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      if (!(r ? row1_ok : row0_ok)) continue;
+      const int t = r ? t1 : t0, g = r ? g1 : g0;
+      const long long prow = slot * rq + t * p.nheads + h * p.group + g;
+      if (tq == 0) {
+        p.part_ml[prow * 2] = m_run[r];
+        p.part_ml[prow * 2 + 1] = l_run[r];
+      }
+      float* po = p.part_o + prow * kHeadDim;
+      if constexpr (!kFp8) {
+#pragma unroll
+        for (int nd = 0; nd < 16; ++nd)
+          *reinterpret_cast<float2*>(po + nd * 8 + 2 * tq) = make_float2(o[nd][2 * r], o[nd][2 * r + 1]);
+      } else {
+#pragma unroll
+        for (int c = 0; c < 8; ++c)
+          *reinterpret_cast<float4*>(po + c * 16 + 4 * tq) =
+              make_float4(o[2 * c][2 * r], o[2 * c + 1][2 * r], o[2 * c][2 * r + 1], o[2 * c + 1][2 * r + 1]);
+      }
+    }
+  }
+  if (!ok && lane == 0) {
+    *abort_flag = 1;
+    report_status(p.status, FW_STATUS_WAIT_TIMEOUT);
+  }
+}
+
+// ---------------------------------------------------------------- combine
+struct CombineParams {
+  DecodeParams d;
+  __nv_bfloat16* out;
+  float* lse;
+  float* partial_out;
+  float* partial_lse;
+  const float* v_descale;
+  const float* sinks;
+};
+
+constexpr int kCombineWarps = 4;
+
+// One block per (request, group of kCombineWarps rows); a warp merges the
+// segments of one (token, head) row.  Recomputes the tile prefix the decode
+// kernel used, so the two agree on which CTAs touched the request.
+__global__ void __launch_bounds__(kCombineWarps * 32) combine_kernel(const CombineParams cp) {
+  const DecodeParams& p = cp.d;
+  __shared__ int red[kCombineWarps * 2];
+  const int b = blockIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n_active = load_num_active(p);
+  // tiles before request b and tiles in total
+  int before = 0, total_tiles = 0;
+  for (int i = threadIdx.x; i < p.batch; i += blockDim.x) {
+    const int n = request_span(p, i, n_active).n_tiles;
+    total_tiles += n;
+    if (i < b) before += n;
+  }
+#pragma unroll
+  for (int off = 16; off; off >>= 1) {
+    before += __shfl_xor_sync(0xffffffffu, before, off);
+    total_tiles += __shfl_xor_sync(0xffffffffu, total_tiles, off);
+  }
+  if (lane == 0) {
+    red[warp * 2] = before;
+    red[warp * 2 + 1] = total_tiles;
+  }
+  __syncthreads();
+  before = total_tiles = 0;
+  for (int w = 0; w < kCombineWarps; ++w) {
+    before += red[w * 2];
+    total_tiles += red[w * 2 + 1];
+  }
+  const Span sp = request_span(p, b, n_active);
+  const int rq = p.seqlen_q * p.nheads;
+  const int row = blockIdx.y * kCombineWarps + warp;
+  if (row >= rq) return;
+  const int t = row / p.nheads, hq = row - t * p.nheads;
+
+  int c_lo = 0, c_hi = -1;
+  if (sp.n_tiles > 0) {
+    const long long nt = total_tiles;
+    const long long end = static_cast<long long>(before) + sp.n_tiles;
+    c_lo = static_cast<int>(((before + 1LL) * p.ncta + nt - 1) / nt) - 1;
+    c_hi = static_cast<int>((end * p.ncta + nt - 1) / nt) - 1;
+    c_lo = max(c_lo, 0);
+    c_hi = min(c_hi, p.ncta - 1);
+    // The closed forms above are exact; the loops keep the two kernels in
+    // agreement even if that ever changes.
+    int f0, f1;
+    for (cta_range(nt, p.ncta, c_lo, f0, f1); f1 <= before && c_lo < p.ncta - 1;) cta_range(nt, p.ncta, ++c_lo, f0, f1);
+    for (cta_range(nt, p.ncta, c_hi, f0, f1); f0 >= end && c_hi > 0;) cta_range(nt, p.ncta, --c_hi, f0, f1);
+  }
+
+  const float sink2 = cp.sinks ? cp.sinks[hq] * kLog2e : -INFINITY;
+  float m_max = -INFINITY;
+  for (int c = c_lo + lane; c <= c_hi; c += 32) {
+    int f0, f1;
+    cta_range(total_tiles, p.ncta, c, f0, f1);
+    if (f1 <= f0) continue;
+    const long long prow = (static_cast<long long>(b) + c) * rq + row;
+    m_max = fmaxf(m_max, p.part_ml[prow * 2]);
+  }
+#pragma unroll
+  for (int off = 16; off; off >>= 1) m_max = fmaxf(m_max, __shfl_xor_sync(0xffffffffu, m_max, off));
+
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  float den = 0.f;
+  if (m_max != -INFINITY) {
+    for (int c = c_lo; c <= c_hi; ++c) {
+      int f0, f1;
+      cta_range(total_tiles, p.ncta, c, f0, f1);
+      if (f1 <= f0) continue;
+      const long long prow = (static_cast<long long>(b) + c) * rq + row;
+      const float m = p.part_ml[prow * 2];
+      if (m == -INFINITY) continue;
+      const float w = fast_exp2(m - m_max);
+      den += p.part_ml[prow * 2 + 1] * w;
+      const float4 o = *reinterpret_cast<const float4*>(p.part_o + prow * kHeadDim + lane * 4);
+      acc.x += o.x * w;
+      acc.y += o.y * w;
+      acc.z += o.z * w;
+      acc.w += o.w * w;
+    }
+  }
+
+  if (cp.partial_out != nullptr) {
+    // Sink-free normalised state for a cross-GPU merge.
+    const long long orow = static_cast<long long>(b) * rq + row;
+    const float inv = den > 0.f ? 1.f / den : 0.f;
+    const float vd = cp.v_descale ? *cp.v_descale : 1.0f;
+    *reinterpret_cast<float4*>(cp.partial_out + orow * kHeadDim + lane * 4) =
+        make_float4(acc.x * inv * vd, acc.y * inv * vd, acc.z * inv * vd, acc.w * inv * vd);
+    if (lane == 0) cp.partial_lse[orow] = den > 0.f ? (m_max + log2f(den)) * kLn2 : -INFINITY;
+    return;
+  }
+
+  // Fold the sink: it joins the denominator only.
+  float m_all = fmaxf(m_max, sink2);
+  float out_scale = 0.f, lse = -INFINITY;
+  if (m_all != -INFINITY) {
+    const float w_keys = m_max == -INFINITY ? 0.f : fast_exp2(m_max - m_all);
+    const float den_all = den * w_keys + (sink2 == -INFINITY ? 0.f : fast_exp2(sink2 - m_all));
+    if (den_all > 0.f) {
+      const float vd = cp.v_descale ? *cp.v_descale : 1.0f;
+      out_scale = w_keys * vd / den_all;
+      lse = (m_all + log2f(den_all)) * kLn2;
+    }
+  }
+  const long long orow = (static_cast<long long>(b) * p.seqlen_q + t) * p.nheads + hq;
+  uint2 packed;
+  packed.x = pack_bf16(acc.x * out_scale, acc.y * out_scale);
+  packed.y = pack_bf16(acc.z * out_scale, acc.w * out_scale);
+  *reinterpret_cast<uint2*>(cp.out + orow * kHeadDim + lane * 4) = packed;
+  if (cp.lse != nullptr && lane == 0)
+    cp.lse[(static_cast<long long>(b) * p.nheads + hq) * p.seqlen_q + t] = lse;
+}
+
+// ---------------------------------------------------------------- host
+struct DecodePlan {
+  DecodeParams p;
+  int itemsize;
+  int rows_q;
+  long long slots;
+  uint64_t off_ml, off_o, bytes;
+  size_t smem;
+};
+
+static int plan_decode(const FwDecodeArgs* a, DecodePlan* plan) {
+  if (a == nullptr) {
+    set_error("args is NULL");
+    return FW_ERR_BAD_SHAPE;
+  }
+  if (a->kv_dtype != FW_DTYPE_BF16 && a->kv_dtype != FW_DTYPE_E4M3 && a->kv_dtype != FW_DTYPE_E5M2) {
+    set_error("kv_dtype must be bf16, e4m3 or e5m2; got %d", a->kv_dtype);
+    return FW_ERR_BAD_DTYPE;
+  }
+  const bool paged = a->block_table != nullptr;
+  if (a->batch <= 0 || a->seqlen_q <= 0) {
+    set_error("batch and seqlen_q must be positive.");
+    return FW_ERR_BAD_SHAPE;
+  }
+  if (a->nheads_k <= 0 || a->nheads <= 0 || a->nheads % a->nheads_k) {
+    set_error("nheads=%d must be a multiple of nheads_k=%d.", a->nheads, a->nheads_k);
+    return FW_ERR_BAD_SHAPE;
+  }
+  if (a->head_dim != kHeadDim) {
+    set_error("head_dim %d is not built; this library serves head_dim 128.", a->head_dim);
+    return FW_ERR_UNSUPPORTED;
+  }
+  if (paged) {
+    if (a->v_cache != nullptr) {
+      set_error("With block_table, pass one merged cache as kv_cache and v_cache=NULL.");
+      return FW_ERR_BAD_SHAPE;
+    }
+    if (a->cache_batch_idx != nullptr) {
+      set_error("block_table and cache_batch_idx are mutually exclusive.");
+      return FW_ERR_BAD_SHAPE;
+    }
+    if (a->page_size <= 0 || a->page_size % kTile) {
+      set_error("page_size must be a positive multiple of %d; got %d.", kTile, a->page_size);
+      return FW_ERR_BAD_SHAPE;
+    }
+    if (a->pages_per_seq <= 0 || a->num_pages <= 0) {
+      set_error("block_table must be (batch, max_pages_per_seq) over a non-empty pool.");
+      return FW_ERR_BAD_SHAPE;
+    }
+  } else {
+    if (a->v_cache == nullptr) {
+      set_error("Without block_table, kv_cache and v_cache must be separate caches.");
+      return FW_ERR_BAD_SHAPE;
+    }
+    if (a->kv_dtype != FW_DTYPE_BF16) {
+      set_error("the contiguous K/V pair is bfloat16 only; fp8 needs the paged pool.");
+      return FW_ERR_BAD_DTYPE;
+    }
+    if (a->seqlen_q != 1) {
+      set_error("the contiguous K/V pair serves single-token decode only.");
+      return FW_ERR_UNSUPPORTED;
+    }
+    if (a->page_size <= 0 || a->page_size % kTile || a->num_pages <= 0) {
+      set_error("capacity must be a positive multiple of %d; got %d.", kTile, a->page_size);
+      return FW_ERR_BAD_SHAPE;
+    }
+  }
+  if ((a->k_new == nullptr) != (a->v_new == nullptr)) {
+    set_error("k and v must be passed together, or both left out.");
+    return FW_ERR_BAD_SHAPE;
+  }
+  if (a->softcap < 0.f) {
+    set_error("softcap must be non-negative; got %f.", a->softcap);
+    return FW_ERR_BAD_SHAPE;
+  }
+  if (a->window_left < -1) {
+    set_error("window_left must be -1 (unbounded) or non-negative; got %d.", a->window_left);
+    return FW_ERR_BAD_SHAPE;
+  }
+  if (a->batch > kMaxInlineBatch) {
+    set_error("batch %d exceeds %d per call; split the batch.", a->batch, kMaxInlineBatch);
+    return FW_ERR_UNSUPPORTED;
+  }
+  if ((a->partial_out == nullptr) != (a->partial_lse == nullptr)) {
+    set_error("partial_out and partial_lse must be passed together.");
+    return FW_ERR_BAD_SHAPE;
+  }
+  const int group = a->nheads / a->nheads_k;
+  const int rows_per_head = a->seqlen_q * group;
+  const int mt = (rows_per_head + 15) / 16;
+  if (mt > kMaxConsumerWarps) {
+    set_error("seqlen_q * (nheads / nheads_k) = %d exceeds %d query rows per KV head.", rows_per_head,
+              16 * kMaxConsumerWarps);
+    return FW_ERR_UNSUPPORTED;
+  }
+  const int itemsize = a->kv_dtype == FW_DTYPE_BF16 ? 2 : 1;
+  DecodeParams& p = plan->p;
+  p = DecodeParams{};
+  p.plane_bytes = a->head_dim * itemsize;
+  p.spp = p.plane_bytes / 128;
+  p.merged = paged ? 1 : 0;
+  p.mt = mt;
+  p.hpc = max(1, min(a->nheads_k, kMaxConsumerWarps / mt));
+  p.nhg = (a->nheads_k + p.hpc - 1) / p.hpc;
+  const int heads_per_word = itemsize == 1 ? 2 : 1;
+  const int cache_heads = paged ? 2 * ((a->nheads_k + heads_per_word - 1) / heads_per_word * heads_per_word)
+                                : a->nheads_k;
+  p.zero_pad_head = paged && cache_heads != 2 * a->nheads_k;
+  p.row_bytes = cache_heads * p.plane_bytes;
+  const int segs_per_stage = p.hpc * 2 * p.spp;
+  p.stage_bytes = segs_per_stage * kTile * 128;
+  const int smem_budget = 200 * 1024;
+  p.stages = min(kMaxStages, smem_budget / p.stage_bytes);
+  if (p.stages < 2) {
+    set_error("stage of %d bytes leaves fewer than two pipeline stages.", p.stage_bytes);
+    return FW_ERR_UNSUPPORTED;
+  }
+  plan->smem = static_cast<size_t>(p.stages) * p.stage_bytes + 1024 /*alignment*/ +
+               2 * kMaxStages * sizeof(uint64_t) + 16 + (a->batch + 1) * sizeof(int) + 64;
+  // Small CTAs share an SM; size the grid so every SM is covered.
+  const int threads = (p.hpc * p.mt + 1) * 32;
+  int per_sm = min(static_cast<int>(220 * 1024 / plan->smem), 2048 / threads);
+  per_sm = max(1, min(per_sm, 8));
+  p.ncta = a->num_ctas > 0 ? a->num_ctas : max(1, sm_count() * per_sm / p.nhg);
+  p.q = static_cast<const __nv_bfloat16*>(a->q);
+  p.k_new = static_cast<const uint8_t*>(a->k_new);
+  p.v_new = static_cast<const uint8_t*>(a->v_new);
+  p.k_base = static_cast<uint8_t*>(a->kv_cache);
+  p.v_base = static_cast<uint8_t*>(paged ? a->kv_cache : a->v_cache);
+  p.cache_seqlens = a->cache_seqlens;
+  p.block_table = a->block_table;
+  p.cache_batch_idx = a->cache_batch_idx;
+  p.num_active = a->num_active;
+  p.k_descale = a->k_descale;
+  p.num_pages = a->num_pages;
+  p.page_size = a->page_size;
+  p.pages_per_seq = paged ? a->pages_per_seq : 1;
+  p.batch = a->batch;
+  p.seqlen_q = a->seqlen_q;
+  p.nheads = a->nheads;
+  p.nheads_k = a->nheads_k;
+  p.group = group;
+  p.has_new = a->k_new != nullptr;
+  p.causal = a->causal != 0;
+  p.window_left = a->window_left;
+  p.scale = a->softmax_scale;
+  p.softcap = a->softcap;
+  plan->itemsize = itemsize;
+  plan->rows_q = a->seqlen_q * a->nheads;
+  plan->slots = static_cast<long long>(a->batch) + p.ncta;
+  plan->off_ml = 256;
+  const uint64_t ml_bytes = static_cast<uint64_t>(plan->slots) * plan->rows_q * 2 * sizeof(float);
+  plan->off_o = (plan->off_ml + ml_bytes + 255) & ~255ull;
+  plan->bytes = plan->off_o + static_cast<uint64_t>(plan->slots) * plan->rows_q * kHeadDim * sizeof(float);
+  return FW_OK;
+}
+
+}  // namespace fw
+
+using namespace fw;
+
+extern "C" uint64_t fw_decode_workspace_bytes(const FwDecodeArgs* args) {
+  DecodePlan plan;
+  if (plan_decode(args, &plan) != FW_OK) return 0;
+  return plan.bytes;
+}
+
+extern "C" int fw_decode_kvcache(const FwDecodeArgs* a, void* stream_ptr) {
+  DecodePlan plan;
+  int rc = plan_decode(a, &plan);
+  if (rc != FW_OK) return rc;
+  if (a->q == nullptr || a->kv_cache == nullptr || a->cache_seqlens == nullptr ||
+      (a->out == nullptr && a->partial_out == nullptr)) {
+    set_error("q, kv_cache, cache_seqlens and out must be device pointers, not NULL.");
+    return FW_ERR_BAD_SHAPE;
+  }
+  if (a->workspace == nullptr || a->workspace_bytes < plan.bytes ||
+      (reinterpret_cast<uintptr_t>(a->workspace) & 255)) {
+    set_error("workspace must be 256-byte aligned and hold %llu bytes; got %llu.",
+              static_cast<unsigned long long>(plan.bytes), static_cast<unsigned long long>(a->workspace_bytes));
+    return FW_ERR_WORKSPACE;
+  }
+  if ((reinterpret_cast<uintptr_t>(a->kv_cache) & 15) || (reinterpret_cast<uintptr_t>(a->v_cache) & 15) ||
+      (reinterpret_cast<uintptr_t>(a->q) & 15) || (reinterpret_cast<uintptr_t>(a->k_new) & 15) ||
+      (reinterpret_cast<uintptr_t>(a->v_new) & 15) || (reinterpret_cast<uintptr_t>(a->out) & 15)) {
+    set_error("q, out, caches and new k/v must be 16-byte aligned.");
+    return FW_ERR_BAD_SHAPE;
+  }
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
+  DecodeParams& p = plan.p;
+  uint8_t* ws = static_cast<uint8_t*>(a->workspace);
+  p.status = reinterpret_cast<int*>(ws);
+  p.part_ml = reinterpret_cast<float*>(ws + plan.off_ml);
+  p.part_o = reinterpret_cast<float*>(ws + plan.off_o);
+
+  // Tensor maps: bytes (128) x tokens-in-page x 128-byte segments x pages, so a
+  // stage lands token-major inside each head segment.
+  CUtensorMap map_k, map_v;
+  const uint64_t segs = static_cast<uint64_t>(p.row_bytes) / 128;
+  const uint64_t dims[4] = {128, static_cast<uint64_t>(p.page_size), segs, static_cast<uint64_t>(p.num_pages)};
+  const uint64_t strides[3] = {static_cast<uint64_t>(p.row_bytes), 128,
+                               static_cast<uint64_t>(p.page_size) * p.row_bytes};
+  const uint32_t box[4] = {128, kTile, static_cast<uint32_t>(p.merged ? p.hpc * 2 * p.spp : p.hpc * p.spp), 1};
+  rc = encode_tensor_map_u8_4d(&map_k, p.k_base, dims, strides, box);
+  if (rc != FW_OK) return rc;
+  rc = encode_tensor_map_u8_4d(&map_v, p.v_base, dims, strides, box);
+  if (rc != FW_OK) return rc;
+
+  auto kernel = a->kv_dtype == FW_DTYPE_BF16   ? decode_kernel<FW_DTYPE_BF16>
+                : a->kv_dtype == FW_DTYPE_E4M3 ? decode_kernel<FW_DTYPE_E4M3>
+                                               : decode_kernel<FW_DTYPE_E5M2>;
+  cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         static_cast<int>(plan.smem));
+  if (err != cudaSuccess) {
+    set_error("cudaFuncSetAttribute(%zu bytes): %s", plan.smem, cudaGetErrorString(err));
+    return FW_ERR_LAUNCH;
+  }
+  dim3 grid(p.ncta, p.nhg);
+  dim3 block((p.hpc * p.mt + 1) * 32);
+  kernel<<<grid, block, plan.smem, stream>>>(map_k, map_v, p);
+  err = cudaGetLastError();
+  if (err != cudaSuccess) {
+    set_error("decode kernel launch: %s", cudaGetErrorString(err));
+    return FW_ERR_LAUNCH;
+  }
+  CombineParams cp;
+  cp.d = p;
+  cp.out = static_cast<__nv_bfloat16*>(a->out);
+  cp.lse = a->lse;
+  cp.partial_out = a->partial_out;
+  cp.partial_lse = a->partial_lse;
+  cp.v_descale = a->v_descale;
+  cp.sinks = a->sinks;
+  dim3 cgrid(p.batch, (plan.rows_q + kCombineWarps - 1) / kCombineWarps);
+  combine_kernel<<<cgrid, kCombineWarps * 32, 0, stream>>>(cp);
+  err = cudaGetLastError();
+  if (err != cudaSuccess) {
+    set_error("combine kernel launch: %s", cudaGetErrorString(err));
+    return FW_ERR_LAUNCH;
+  }
+  return FW_OK;
+}

@@ -1,0 +1,147 @@
+"""ctypes binding of the C ABI in include/flywheel_b200.h.
+
+The shared library is built in-tree (build.py) and must be present: importing
+the entry points without it raises, there is no fallback.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import os
+import pathlib
+
+import torch
+
+PACKAGE_ROOT = pathlib.Path(__file__).resolve().parents[2]
+LIBRARY_PATH = PACKAGE_ROOT / "lib" / "libflywheel_b200.so"
+
+FW_OK = 0
+ERRORS = {
+    -1: ValueError,            # FW_ERR_BAD_SHAPE
+    -2: NotImplementedError,   # FW_ERR_BAD_DTYPE
+    -3: NotImplementedError,   # FW_ERR_UNSUPPORTED
+    -4: RuntimeError,          # FW_ERR_LAUNCH
+    -5: TimeoutError,          # FW_ERR_TIMEOUT
+    -6: ValueError,            # FW_ERR_WORKSPACE
+}
+DTYPE_CODE = {"bfloat16": 0, "float8_e4m3fn": 1, "float8_e5m2": 2}
+
+c_ptr = ctypes.c_void_p
+i32, i64, u64, f32 = ctypes.c_int32, ctypes.c_int64, ctypes.c_uint64, ctypes.c_float
+
+
+class FwDecodeArgs(ctypes.Structure):
+    _fields_ = [
+        ("q", c_ptr), ("out", c_ptr), ("lse", c_ptr), ("kv_cache", c_ptr),
+        ("v_cache", c_ptr), ("k_new", c_ptr), ("v_new", c_ptr),
+        ("cache_seqlens", c_ptr), ("block_table", c_ptr),
+        ("cache_batch_idx", c_ptr), ("num_active", c_ptr),
+        ("k_descale", c_ptr), ("v_descale", c_ptr), ("sinks", c_ptr),
+        ("partial_out", c_ptr), ("partial_lse", c_ptr), ("workspace", c_ptr),
+        ("workspace_bytes", u64), ("num_pages", i64), ("page_size", i32),
+        ("pages_per_seq", i32), ("batch", i32), ("seqlen_q", i32),
+        ("nheads", i32), ("nheads_k", i32), ("head_dim", i32),
+        ("kv_dtype", i32), ("causal", i32), ("window_left", i32),
+        ("softmax_scale", f32), ("softcap", f32), ("num_ctas", i32),
+    ]
+
+
+class FwAppendArgs(ctypes.Structure):
+    _fields_ = [
+        ("kv_cache", c_ptr), ("k_new", c_ptr), ("v_new", c_ptr),
+        ("cu_seqlens_q", c_ptr), ("cache_seqlens", c_ptr),
+        ("block_table", c_ptr), ("num_active", c_ptr), ("num_pages", i64),
+        ("page_size", i32), ("pages_per_seq", i32), ("batch", i32),
+        ("total_tokens", i32), ("nheads_k", i32), ("head_dim", i32),
+        ("kv_dtype", i32),
+    ]
+
+
+class FwPrefillArgs(ctypes.Structure):
+    _fields_ = [
+        ("q", c_ptr), ("out", c_ptr), ("lse", c_ptr), ("kv_cache", c_ptr),
+        ("cu_seqlens_q", c_ptr), ("seqused_k", c_ptr), ("block_table", c_ptr),
+        ("num_active", c_ptr), ("k_descale", c_ptr), ("v_descale", c_ptr),
+        ("sinks", c_ptr), ("workspace", c_ptr), ("workspace_bytes", u64),
+        ("num_pages", i64), ("page_size", i32), ("pages_per_seq", i32),
+        ("batch", i32), ("total_q", i32), ("max_seqlen_q", i32),
+        ("nheads", i32), ("nheads_k", i32), ("head_dim", i32),
+        ("kv_dtype", i32), ("causal", i32), ("window_left", i32),
+        ("softmax_scale", f32), ("softcap", f32), ("token_major", i32),
+    ]
+
+
+class FwCombineArgs(ctypes.Structure):
+    _fields_ = [
+        ("partial_out", c_ptr), ("partial_lse", c_ptr), ("sinks", c_ptr),
+        ("out", c_ptr), ("lse", c_ptr), ("parts", i32), ("rows", i32),
+        ("nheads", i32), ("head_dim", i32), ("lse_head_stride", i32),
+        ("lse_token_stride", i32),
+    ]
+
+
+EXPORTS = {
+    "fw_decode_workspace_bytes": (u64, [ctypes.POINTER(FwDecodeArgs)]),
+    "fw_decode_kvcache": (ctypes.c_int, [ctypes.POINTER(FwDecodeArgs), c_ptr]),
+    "fw_append_ragged": (ctypes.c_int, [ctypes.POINTER(FwAppendArgs), c_ptr]),
+    "fw_prefill_workspace_bytes": (u64, [ctypes.POINTER(FwPrefillArgs)]),
+    "fw_prefill_paged": (ctypes.c_int, [ctypes.POINTER(FwPrefillArgs), c_ptr]),
+    "fw_lse_combine": (ctypes.c_int, [ctypes.POINTER(FwCombineArgs), c_ptr]),
+    "fw_read_status": (ctypes.c_int, [c_ptr, c_ptr, ctypes.POINTER(i32)]),
+    "fw_last_error": (ctypes.c_char_p, []),
+    "fw_version": (ctypes.c_int, []),
+}
+
+_LIB = None
+
+
+def library() -> ctypes.CDLL:
+    """The loaded shared library; raises if it has not been built."""
+    global _LIB
+    if _LIB is None:
+        path = pathlib.Path(os.environ.get("FLYWHEEL_B200_LIBRARY", LIBRARY_PATH))
+        if not path.exists():
+            raise ImportError(
+                f"{path} is missing: build the CUDA library first"
+                " (python flywheel-tpu_b200/build.py). There is no fallback"
+                " path.")
+        lib = ctypes.CDLL(str(path))
+        for name, (restype, argtypes) in EXPORTS.items():
+            fn = getattr(lib, name)
+            fn.restype, fn.argtypes = restype, argtypes
+        _LIB = lib
+    return _LIB
+
+
+def last_error() -> str:
+    return library().fw_last_error().decode("utf-8", "replace")
+
+
+def check(code: int) -> None:
+    if code != FW_OK:
+        raise ERRORS.get(code, RuntimeError)(last_error())
+
+
+def current_stream(device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+_WORKSPACES: dict = {}
+
+
+def workspace(device, nbytes: int) -> torch.Tensor:
+    """A zero-initialised, 256-byte aligned scratch buffer on `device`, grown
+    on demand and reused by later calls on the same device and stream."""
+    key = (device.index, torch.cuda.current_stream(device).cuda_stream)
+    buf = _WORKSPACES.get(key)
+    if buf is None or buf.numel() < nbytes:
+        buf = torch.zeros(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        _WORKSPACES[key] = buf
+    return buf
+
+
+def read_status(buf: torch.Tensor, device) -> int:
+    status = i32(0)
+    check(library().fw_read_status(buf.data_ptr(), current_stream(device),
+                                   ctypes.byref(status)))
+    return status.value

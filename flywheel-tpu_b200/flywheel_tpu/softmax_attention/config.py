@@ -1,0 +1,13 @@
+"""Static limits of the B200 kernels."""
+
+from flywheel_tpu.core.tiling import DECODE_TILE_TOKENS
+
+# The reference needs page_size % 128 == 0
+# (flywheel_tpu/softmax_attention/config.py:40); these kernels stage 16-token
+# tiles, so any multiple of 16 works (64-token pages included).
+PAGE_SIZE_MULTIPLE = DECODE_TILE_TOKENS
+# Query rows per KV head (seqlen_q * nheads / nheads_k) the decode kernel takes
+# in one launch; the reference folds a verify window up to the same bound
+# (decode.py:49-53).
+MAX_FOLDED_QUERY_ROWS = 128
+SUPPORTED_HEAD_DIMS = (128,)

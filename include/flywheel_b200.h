@@ -1,0 +1,229 @@
+/*
+ * flywheel_b200.h -- C ABI of the B200 (sm_100a) paged-KV softmax attention path.
+ *
+ * This is the boundary a host binding (XLA FFI handler, ctypes, cgo ...) calls.
+ * Every pointer below is a DEVICE pointer unless a comment says "host".  No
+ * entry point allocates, frees or synchronises: work is enqueued on the CUDA
+ * stream the caller passes (a cudaStream_t cast to void*), scratch memory is a
+ * caller-owned workspace sized by the matching *_workspace_bytes call, and
+ * values the reference allows to be traced (lengths, tables, descales, sinks,
+ * num_active) are read on the device, never on the host.
+ *
+ * Reference interfaces these entry points stand behind (paths relative to the
+ * heavyball-research/flywheel-tpu project):
+ *   fw_decode_kvcache   <- flywheel_tpu/softmax_attention/decode.py:189-625
+ *                          (flash_attn_with_kvcache) and the custom call it
+ *                          lowers to, kernels/decode.py:2046-2475
+ *   fw_append_ragged    <- kernels/kv_append.py:116-184 (append_ragged)
+ *   fw_prefill_paged    <- flywheel_tpu/softmax_attention/prefill.py:437-661
+ *                          (flash_attn_varlen_func with block_table) and
+ *                          kernels/fwd_paged.py:1351-1491
+ *   fw_lse_combine      <- patches/tpu-inference.patch:7174-7186 (_merge_states;
+ *                          the library itself has no split-KV merge)
+ *
+ * Return value: FW_OK or a negative FW_ERR_* code; fw_last_error() returns a
+ * thread-local message for the last failing call on the calling thread.
+ */
+#ifndef FLYWHEEL_B200_H_
+#define FLYWHEEL_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define FW_OK 0
+#define FW_ERR_BAD_SHAPE (-1)   /* reference raises ValueError               */
+#define FW_ERR_BAD_DTYPE (-2)   /* reference raises NotImplementedError      */
+#define FW_ERR_UNSUPPORTED (-3) /* valid in the reference, not built here    */
+#define FW_ERR_LAUNCH (-4)      /* CUDA refused the launch / descriptor      */
+#define FW_ERR_TIMEOUT (-5)     /* a bounded device-side wait gave up        */
+#define FW_ERR_WORKSPACE (-6)   /* workspace missing, small or misaligned    */
+
+/* KV cache element types (flywheel_tpu/softmax_attention/kv_layout.py:30-34). */
+#define FW_DTYPE_BF16 0
+#define FW_DTYPE_E4M3 1
+#define FW_DTYPE_E5M2 2
+
+/* Device status word written at workspace offset 0 by kernels whose bounded
+ * waits gave up; 0 = clean.  Read it with fw_read_status after a sync. */
+#define FW_STATUS_OK 0
+#define FW_STATUS_WAIT_TIMEOUT 1
+#define FW_STATUS_BAD_PAGE 2
+
+/*
+ * Attention of q against a KV cache with the new tokens' K/V appended in the
+ * same launch (flash_attn_with_kvcache, decode.py:189-625).
+ *
+ * Layouts
+ *   paged merged (block_table != NULL): kv_cache is one pool
+ *     (num_pages, page_size, cache_heads, head_dim) whose token rows hold
+ *     [k0, v0, k1, v1, ...] (kv_layout.py:39-46); v_cache must be NULL.
+ *     cache_heads = 2*nheads_k, an odd fp8 nheads_k padded by one zero head.
+ *     page_size must be a multiple of 16 (the reference asks for 128).
+ *   contiguous pair (block_table == NULL): kv_cache and v_cache are
+ *     (batch_cache, capacity, nheads_k, head_dim) bf16; cache_batch_idx (or
+ *     NULL = identity) picks the cache row of each query row; seqlen_q == 1.
+ * q / out: (batch, seqlen_q, nheads, head_dim) bf16.  k_new / v_new: NULL, or
+ * (batch, seqlen_q, nheads_k, head_dim) in the cache dtype; token t of row b
+ * is written at position cache_seqlens[b] + t and then attended.
+ * lse: NULL or (batch, nheads, seqlen_q) f32, natural log.
+ * Mask: bottom-right aligned; causal != 0 forces the right bound to 0;
+ * window_left < 0 is unbounded.  softcap > 0 maps a scaled score s to
+ * softcap * tanh(s / softcap).  sinks: NULL or (nheads,) f32.
+ * Rows b >= *num_active (NULL = batch) append nothing and return out 0,
+ * lse -inf.
+ *
+ * partial_out != NULL switches to "partial state" mode for a cache whose
+ * pages are split over several GPUs: instead of out/lse the call writes the
+ * sink-free normalised f32 state partial_out (batch, seqlen_q, nheads,
+ * head_dim) and partial_lse (batch, seqlen_q, nheads); merge the gathered
+ * states with fw_lse_combine.
+ */
+typedef struct FwDecodeArgs {
+  const void* q;
+  void* out;
+  float* lse;
+  void* kv_cache;
+  void* v_cache;
+  const void* k_new;
+  const void* v_new;
+  const int32_t* cache_seqlens;
+  const int32_t* block_table;
+  const int32_t* cache_batch_idx;
+  const int32_t* num_active;
+  const float* k_descale;
+  const float* v_descale;
+  const float* sinks;
+  float* partial_out;
+  float* partial_lse;
+  void* workspace;
+  uint64_t workspace_bytes;
+  int64_t num_pages;        /* paged: pool pages; contiguous: batch_cache */
+  int32_t page_size;        /* paged: tokens per page; contiguous: capacity */
+  int32_t pages_per_seq;    /* block_table row length */
+  int32_t batch;
+  int32_t seqlen_q;
+  int32_t nheads;
+  int32_t nheads_k;
+  int32_t head_dim;
+  int32_t kv_dtype;         /* FW_DTYPE_* */
+  int32_t causal;
+  int32_t window_left;      /* -1 = unbounded */
+  float softmax_scale;
+  float softcap;
+  int32_t num_ctas;         /* 0 = pick from the device; tests may pin it */
+} FwDecodeArgs;
+
+uint64_t fw_decode_workspace_bytes(const FwDecodeArgs* args);
+int fw_decode_kvcache(const FwDecodeArgs* args, void* stream);
+
+/*
+ * Packed new K/V rows -> merged pages (append_ragged, kv_append.py:116-184).
+ * k_new / v_new: (total_tokens, nheads_k, head_dim) in the pool dtype;
+ * request r < *num_active owns rows [cu_seqlens_q[r], cu_seqlens_q[r+1]) and
+ * writes them at cache_seqlens[r] + t.  Whole merged rows are written.
+ */
+typedef struct FwAppendArgs {
+  void* kv_cache;
+  const void* k_new;
+  const void* v_new;
+  const int32_t* cu_seqlens_q;   /* (batch + 1,) */
+  const int32_t* cache_seqlens;  /* (batch,) lengths before the append */
+  const int32_t* block_table;
+  const int32_t* num_active;
+  int64_t num_pages;
+  int32_t page_size;
+  int32_t pages_per_seq;
+  int32_t batch;
+  int32_t total_tokens;
+  int32_t nheads_k;
+  int32_t head_dim;
+  int32_t kv_dtype;
+} FwAppendArgs;
+
+int fw_append_ragged(const FwAppendArgs* args, void* stream);
+
+/*
+ * Read-only chunked prefill over the merged pool (flash_attn_varlen_func with
+ * block_table, prefill.py:437-661).  q / out: head-major (nheads, total_q,
+ * head_dim) bf16; lse: NULL or (nheads, total_q) f32.  seqused_k[r] is request
+ * r's KV length, its new tokens included, already in the pool.  Rows past
+ * cu_seqlens_q[*num_active] return out 0, lse -inf.
+ */
+typedef struct FwPrefillArgs {
+  const void* q;
+  void* out;
+  float* lse;
+  const void* kv_cache;
+  const int32_t* cu_seqlens_q;   /* (batch + 1,), cu_seqlens_q[0] == 0 */
+  const int32_t* seqused_k;      /* (batch,) */
+  const int32_t* block_table;
+  const int32_t* num_active;
+  const float* k_descale;
+  const float* v_descale;
+  const float* sinks;
+  void* workspace;
+  uint64_t workspace_bytes;
+  int64_t num_pages;
+  int32_t page_size;
+  int32_t pages_per_seq;
+  int32_t batch;
+  int32_t total_q;
+  int32_t max_seqlen_q;
+  int32_t nheads;
+  int32_t nheads_k;
+  int32_t head_dim;
+  int32_t kv_dtype;
+  int32_t causal;
+  int32_t window_left;
+  float softmax_scale;
+  float softcap;
+  int32_t token_major;  /* 1: q/out are (total_q, nheads, head_dim) */
+} FwPrefillArgs;
+
+uint64_t fw_prefill_workspace_bytes(const FwPrefillArgs* args);
+int fw_prefill_paged(const FwPrefillArgs* args, void* stream);
+
+/*
+ * Merge `parts` sink-free partial states over disjoint key sets
+ * (_merge_states, patches/tpu-inference.patch:7174-7186).
+ * partial_out: (parts, rows, head_dim) f32 normalised; partial_lse:
+ * (parts, rows) f32 natural log, -inf for an empty part; row = token * nheads
+ * + head.  sinks: NULL or (nheads,) f32, joins the denominator once.
+ * out: (rows, head_dim) bf16; lse: NULL or (rows,) f32 with stride given by
+ * lse_head_stride / lse_token_stride (elements) so it can land in the
+ * (batch, nheads, seqlen_q) layout.
+ */
+typedef struct FwCombineArgs {
+  const float* partial_out;
+  const float* partial_lse;
+  const float* sinks;
+  void* out;
+  float* lse;
+  int32_t parts;
+  int32_t rows;
+  int32_t nheads;
+  int32_t head_dim;
+  int32_t lse_head_stride;
+  int32_t lse_token_stride;
+} FwCombineArgs;
+
+int fw_lse_combine(const FwCombineArgs* args, void* stream);
+
+/* Copies the device status word at the head of `workspace` to *status (host).
+ * Synchronises `stream`; meant for tests and debugging, not the hot path. */
+int fw_read_status(const void* workspace, void* stream, int32_t* status);
+
+/* Thread-local text of the last error on this thread ("" if none). */
+const char* fw_last_error(void);
+
+/* ABI version: bumped when a struct above changes. */
+int fw_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FLYWHEEL_B200_H_ */

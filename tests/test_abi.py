@@ -1,0 +1,92 @@
+"""The C-ABI library loads and exports every symbol include/flywheel_b200.h
+declares; argument validation answers without touching a GPU."""
+
+import ctypes
+import pathlib
+import re
+
+import pytest
+
+ROOT = pathlib.Path(__file__).resolve().parent.parent
+
+
+def declared_symbols():
+    header = (ROOT / "include" / "flywheel_b200.h").read_text()
+    return sorted(set(re.findall(r"\b(fw_[a-z_0-9]+)\s*\(", header)))
+
+
+def test_library_exports_every_declared_symbol():
+    from flywheel_tpu.softmax_attention import _native
+    lib = _native.library()
+    names = declared_symbols()
+    assert {"fw_decode_kvcache", "fw_append_ragged", "fw_prefill_paged",
+            "fw_lse_combine", "fw_last_error", "fw_version"} <= set(names)
+    for name in names:
+        assert getattr(lib, name) is not None, name
+    assert set(names) == set(_native.EXPORTS), set(names) ^ set(_native.EXPORTS)
+
+
+def test_struct_sizes_match_header_layout():
+    from flywheel_tpu.softmax_attention import _native
+    # 17 pointers + u64 + i64 + 11 i32/f32 fields + 1 i32 (padded to 8)
+    assert ctypes.sizeof(_native.FwDecodeArgs) == 17 * 8 + 8 + 8 + 14 * 4
+    assert ctypes.sizeof(_native.FwAppendArgs) == 7 * 8 + 8 + 7 * 4 + 4
+    assert ctypes.sizeof(_native.FwCombineArgs) == 5 * 8 + 6 * 4
+
+
+def test_argument_errors_mirror_reference_exception_types():
+    from flywheel_tpu.softmax_attention import _native
+    lib = _native.library()
+    args = _native.FwDecodeArgs(batch=2, seqlen_q=1, nheads=6, nheads_k=4, head_dim=128,
+                                block_table=1, page_size=64, pages_per_seq=2, num_pages=4)
+    assert lib.fw_decode_workspace_bytes(ctypes.byref(args)) == 0
+    assert "multiple of nheads_k" in _native.last_error()
+    with pytest.raises(ValueError):
+        _native.check(lib.fw_decode_kvcache(ctypes.byref(args), None))
+    args.nheads_k, args.kv_dtype = 2, 7
+    with pytest.raises(NotImplementedError):
+        _native.check(lib.fw_decode_kvcache(ctypes.byref(args), None))
+    args.kv_dtype, args.page_size = 0, 40
+    with pytest.raises(ValueError, match="page_size"):
+        _native.check(lib.fw_decode_kvcache(ctypes.byref(args), None))
+    args.page_size, args.head_dim = 64, 96
+    with pytest.raises(NotImplementedError, match="head_dim"):
+        _native.check(lib.fw_decode_kvcache(ctypes.byref(args), None))
+
+
+def test_host_api_rejections_follow_the_reference():
+    import numpy as np
+    import ml_dtypes
+    from flywheel_tpu import flash_attn_with_kvcache, flash_attn_varlen_func
+    bf16 = np.dtype(ml_dtypes.bfloat16)
+    q = np.zeros((2, 1, 4, 128), bf16)
+    pool = np.zeros((4, 64, 4, 128), bf16)
+    table = np.zeros((2, 2), np.int32)
+    with pytest.raises(ValueError, match="v_cache=None"):
+        flash_attn_with_kvcache(q, pool, pool, cache_seqlens=1, block_table=table)
+    with pytest.raises(ValueError, match="mutually exclusive"):
+        flash_attn_with_kvcache(q, pool, None, cache_seqlens=1, block_table=table,
+                                cache_batch_idx=np.zeros(2, np.int32))
+    with pytest.raises(NotImplementedError, match="paged merged"):
+        flash_attn_with_kvcache(np.zeros((2, 3, 4, 128), bf16), pool, pool, cache_seqlens=1)
+    with pytest.raises(ValueError, match="window_size"):
+        flash_attn_with_kvcache(q, pool, None, cache_seqlens=1, block_table=table,
+                                window_size=(-2, 0))
+    with pytest.raises(NotImplementedError, match="bfloat16"):
+        flash_attn_with_kvcache(q.astype(np.float32), pool, None, cache_seqlens=1,
+                                block_table=table)
+    with pytest.raises(ValueError, match="passed together"):
+        flash_attn_with_kvcache(q, pool, None, np.zeros((2, 1, 2, 128), bf16), None,
+                                cache_seqlens=1, block_table=table)
+    with pytest.raises(ValueError, match="head rows per"):
+        flash_attn_with_kvcache(q, pool, None, cache_seqlens=1, block_table=table, nheads_k=3)
+    with pytest.raises(ValueError, match="max_seqlen_q"):
+        flash_attn_with_kvcache(np.zeros((5, 4, 128), bf16), pool, None, cache_seqlens=1,
+                                block_table=table, cu_seqlens_q=np.array([0, 2, 5], np.int32))
+    with pytest.raises(ValueError, match="seqused_k"):
+        flash_attn_varlen_func(np.zeros((4, 5, 128), bf16), pool, None,
+                               np.array([0, 2, 5], np.int32), None, 3, 64, block_table=table)
+    with pytest.raises(NotImplementedError, match="right bound"):
+        flash_attn_varlen_func(np.zeros((4, 5, 128), bf16), pool, None,
+                               np.array([0, 2, 5], np.int32), None, 3, 64, block_table=table,
+                               seqused_k=np.array([3, 4], np.int32), window_size=(-1, 5))
