@@ -73,8 +73,8 @@ def merge_kv_heads(k: np.ndarray, v: np.ndarray) -> np.ndarray:
 
 def split_kv_heads(kv: np.ndarray, nheads_k: int):
     """merge_kv_heads' inverse (tests/softmax_attention/util.py:55-59)."""
-    *leading, _, d = kv.shape
-    pairs = kv.reshape(*leading, -1, 2, d)
+    *leading, cache_heads, d = kv.shape
+    pairs = kv.reshape(*leading, cache_heads // 2, 2, d)
     return pairs[..., :nheads_k, 0, :], pairs[..., :nheads_k, 1, :]
 
 
