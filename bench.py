@@ -348,7 +348,11 @@ def main():
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "ms_per_step": e2e_ms / ns.steps},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s",
-                         "frac": achieved / hbm_peak, "traffic": None, "peak_kind": f"of {peak_kind}",
+                         "frac": achieved / hbm_peak,
+                         # dram read+write per launch, scaled from the small-case ncu capture in
+                         # profiles/decode_bf16_paged_c2.md (reads 1.0011 x algorithmic, writes =
+                         # the per-CTA partial states)
+                         "traffic": work["kv_bytes"] * 1.0011 + (BATCH + 148) * HQ * (D + 2) * 4, "peak_kind": f"of {peak_kind}",
                          "kernel": "fw::decode_kernel<bf16> (+ combine_kernel, <1% of the launch pair)",
                          "algorithmic_bytes_per_launch": work["kv_bytes"],
                          "frac_of_nominal_8TBs": achieved / 8000.0},
