@@ -22,6 +22,8 @@
 // widened to f16 in registers straight out of ldmatrix.  Each (CTA, request)
 // segment leaves an un-normalised (o, m, l) partial; the combine kernel merges
 // the segments of a request, folds the sink and v_descale and writes bf16.
+#include <mutex>
+
 #include "common.cuh"
 
 namespace fw {
@@ -907,4 +909,67 @@ extern "C" int fw_decode_kvcache(const FwDecodeArgs* a, void* stream_ptr) {
     return FW_ERR_LAUNCH;
   }
   return FW_OK;
+}
+
+// ---------------------------------------------------------------- static scratch
+// Decode for callers that cannot allocate device memory.  The split-KV partial
+// states live in a fixed array inside this library's device image instead of a
+// caller-provided workspace.
+namespace fw {
+
+static __device__ __align__(256) unsigned char g_decode_static_scratch[FW_STATIC_SCRATCH_BYTES];
+
+// The array's name is only a host-side handle; kernels need the device address,
+// which differs per GPU.  Looked up once per device, with that device current.
+static int static_scratch_address(void** address) {
+  static std::mutex guard;
+  static void* per_device[64] = {nullptr};
+  int dev = -1;
+  cudaError_t err = cudaGetDevice(&dev);
+  if (err != cudaSuccess || dev < 0 || dev >= 64) {
+    set_error("cudaGetDevice: %s (device %d)", cudaGetErrorString(err), dev);
+    return FW_ERR_LAUNCH;
+  }
+  std::lock_guard<std::mutex> lock(guard);
+  if (per_device[dev] == nullptr) {
+    void* ptr = nullptr;
+    err = cudaGetSymbolAddress(&ptr, g_decode_static_scratch);
+    if (err != cudaSuccess || ptr == nullptr) {
+      set_error("cudaGetSymbolAddress(static scratch) on device %d: %s", dev, cudaGetErrorString(err));
+      return FW_ERR_LAUNCH;
+    }
+    per_device[dev] = ptr;
+  }
+  *address = per_device[dev];
+  return FW_OK;
+}
+
+}  // namespace fw
+
+extern "C" int fw_decode_kvcache_static(const FwDecodeArgs* a, void* stream_ptr) {
+  DecodePlan plan;
+  int rc = plan_decode(a, &plan);
+  if (rc != FW_OK) return rc;
+  if (plan.bytes > FW_STATIC_SCRATCH_BYTES) {
+    set_error("this call needs %llu bytes of scratch; the built-in scratch holds %llu. Use fw_decode_kvcache "
+              "with a caller workspace, or a smaller batch.",
+              static_cast<unsigned long long>(plan.bytes),
+              static_cast<unsigned long long>(FW_STATIC_SCRATCH_BYTES));
+    return FW_ERR_WORKSPACE;
+  }
+  void* scratch = nullptr;
+  rc = static_scratch_address(&scratch);
+  if (rc != FW_OK) return rc;
+  // The array keeps whatever the previous call left.  Only the status word has
+  // to start at zero; every partial state the combine reads is rewritten by
+  // this call's decode kernel first.
+  cudaError_t err = cudaMemsetAsync(scratch, 0, 256, static_cast<cudaStream_t>(stream_ptr));
+  if (err != cudaSuccess) {
+    set_error("clearing the status word: %s", cudaGetErrorString(err));
+    return FW_ERR_LAUNCH;
+  }
+  FwDecodeArgs with_scratch = *a;
+  with_scratch.workspace = scratch;
+  with_scratch.workspace_bytes = FW_STATIC_SCRATCH_BYTES;
+  return fw_decode_kvcache(&with_scratch, stream_ptr);
 }

@@ -83,6 +83,7 @@ class FwCombineArgs(ctypes.Structure):
 EXPORTS = {
     "fw_decode_workspace_bytes": (u64, [ctypes.POINTER(FwDecodeArgs)]),
     "fw_decode_kvcache": (ctypes.c_int, [ctypes.POINTER(FwDecodeArgs), c_ptr]),
+    "fw_decode_kvcache_static": (ctypes.c_int, [ctypes.POINTER(FwDecodeArgs), c_ptr]),
     "fw_append_ragged": (ctypes.c_int, [ctypes.POINTER(FwAppendArgs), c_ptr]),
     "fw_prefill_workspace_bytes": (u64, [ctypes.POINTER(FwPrefillArgs)]),
     "fw_prefill_paged": (ctypes.c_int, [ctypes.POINTER(FwPrefillArgs), c_ptr]),

@@ -121,6 +121,33 @@ uint64_t fw_decode_workspace_bytes(const FwDecodeArgs* args);
 int fw_decode_kvcache(const FwDecodeArgs* args, void* stream);
 
 /*
+ * fw_decode_kvcache for hosts that must not allocate device memory.
+ * (No counterpart in the reference: its kernels get their scratch from XLA.)
+ *
+ * Some callers cannot hand this library a workspace: a serving engine that
+ * has already given every free byte of HBM to its KV-cache pool, a runtime
+ * whose allocator must not be re-entered from inside a custom-call handler,
+ * or latency-critical code that cannot afford the device-wide synchronisation
+ * a cudaMalloc may imply.  For them this entry point keeps the split-KV
+ * partial states in a fixed array of FW_STATIC_SCRATCH_BYTES that is part of
+ * the library's device image: every GPU that loads the library holds that
+ * much memory until the process exits, and nothing is allocated or freed
+ * here.  args->workspace and args->workspace_bytes are ignored; inputs and
+ * outputs are still the caller's.  A call whose fw_decode_workspace_bytes
+ * exceeds FW_STATIC_SCRATCH_BYTES (very large batch x heads) is refused with
+ * FW_ERR_WORKSPACE.
+ *
+ * The first call on each device looks up the array's address on that device
+ * (the device must be current, as for every call); make that first call before
+ * starting any stream capture.  All calls on one device share the one array:
+ * two calls that overlap on the GPU (different streams, no dependency) race on
+ * it, so keep them ordered.  The array keeps the previous call's contents;
+ * the entry point clears the status word itself, nothing else needs zeroing.
+ */
+#define FW_STATIC_SCRATCH_BYTES (32ull << 20)
+int fw_decode_kvcache_static(const FwDecodeArgs* args, void* stream);
+
+/*
  * Packed new K/V rows -> merged pages (append_ragged, kv_append.py:116-184).
  * k_new / v_new: (total_tokens, nheads_k, head_dim) in the pool dtype;
  * request r < *num_active owns rows [cu_seqlens_q[r], cu_seqlens_q[r+1]) and
