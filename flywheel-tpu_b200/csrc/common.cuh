@@ -178,4 +178,8 @@ int sm_count();
 int encode_tensor_map_u8_4d(CUtensorMap* map, const void* base, const uint64_t dims[4],
                             const uint64_t strides[3], const uint32_t box[4]);
 
+// Chunked prefill through the split-KV decode kernel (decode.cu).
+uint64_t splitkv_prefill_workspace_bytes(const FwPrefillArgs* args);
+int splitkv_prefill(const FwPrefillArgs* args, cudaStream_t stream);
+
 }  // namespace fw

@@ -47,6 +47,7 @@ struct DecodeParams {
   const float* k_descale;
   float* part_o;
   float* part_ml;
+  int* tile_prefix;  // (batch + 1) exclusive tile prefix, written by CTA (0, 0) for the combine
   int* status;
   long long num_pages;
   int page_size, pages_per_seq, batch, seqlen_q, nheads, nheads_k, group;
@@ -59,18 +60,47 @@ struct DecodeParams {
   int has_new, causal, window_left;
   int zero_pad_head;  // fp8 merged pool with an odd nheads_k: append zeroes the pad head
   float scale, softcap;
+  // Item mode (chunked prefill through the split-KV kernel): "request" b is a
+  // block of up to seqlen_q query tokens of packed request items[8b]; see
+  // prefill_plan_kernel for the table.  NULL = plain decode.
+  const int* items;
+  long long q_tok_stride, q_head_stride;  // elements; q and out share them
+  int total_q;
 };
 
 struct Span {
   int total, cache_len, first_tile, n_tiles;
+  int kv_end;     // keys [0, kv_end) exist for this request / item
+  int diag_base;  // query token t sits on diagonal diag_base + t
+  int req;        // block-table row
+  int q_row0;     // first packed q row
+  int q_valid;    // query tokens that are real rows
 };
 
 __device__ __forceinline__ Span request_span(const DecodeParams& p, int b, int n_active) {
-  Span s{0, 0, 0, 0};
+  Span s{0, 0, 0, 0, 0, 0, b, b * p.seqlen_q, p.seqlen_q};
+  if (p.items != nullptr) {
+    const int4 it = *reinterpret_cast<const int4*>(p.items + 8 * b);  // req, q_row0, q_valid, total
+    const int kv_limit = p.items[8 * b + 4];
+    s.req = it.x;
+    s.q_row0 = it.y;
+    s.q_valid = it.z;
+    s.total = it.w;
+    s.kv_end = p.causal ? min(it.w, kv_limit) : kv_limit;
+    s.cache_len = s.kv_end;
+    s.diag_base = s.total - p.seqlen_q;
+    if (s.q_valid <= 0 || s.kv_end <= 0) return s;
+    const int first_key = (p.window_left >= 0) ? max(0, s.diag_base - p.window_left) : 0;
+    s.first_tile = first_key / kTile;
+    s.n_tiles = max(0, (s.kv_end + kTile - 1) / kTile - s.first_tile);
+    return s;
+  }
   if (b >= n_active) return s;
   int len = max(p.cache_seqlens[b], 0);
   s.cache_len = len;
   s.total = len + (p.has_new ? p.seqlen_q : 0);
+  s.kv_end = s.total;
+  s.diag_base = s.total - p.seqlen_q;
   if (s.total <= 0) return s;
   int first_key = (p.window_left >= 0) ? max(0, s.total - p.seqlen_q - p.window_left) : 0;
   s.first_tile = first_key / kTile;
@@ -162,6 +192,8 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
   scan_tiles(p, n_active, pre);  // contains __syncthreads
 
   const long long nt = pre[p.batch];
+  if (cta == 0 && hg == 0)
+    for (int i = threadIdx.x; i <= p.batch; i += blockDim.x) p.tile_prefix[i] = pre[i];
   int f0, f1;
   cta_range(nt, p.ncta, cta, f0, f1);
   if (f0 >= f1) return;
@@ -186,7 +218,7 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
         const int page_idx = pos0 / p.page_size;
         if (page_idx != cur_page_idx) {
           cur_page_idx = page_idx;
-          int page = p.merged ? p.block_table[static_cast<long long>(b) * p.pages_per_seq + page_idx]
+          int page = p.merged ? p.block_table[static_cast<long long>(sp.req) * p.pages_per_seq + page_idx]
                               : (p.cache_batch_idx ? p.cache_batch_idx[b] : b);
           if (page < 0 || page >= p.num_pages) {
             report_status(p.status, FW_STATUS_BAD_PAGE);
@@ -242,7 +274,7 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
   const int rows_per_head = p.seqlen_q * p.group;
   const int quad = lane >> 2, tq = lane & 3;
   const int row0 = mti * 16 + quad, row1 = row0 + 8;
-  const bool row0_ok = row0 < rows_per_head, row1_ok = row1 < rows_per_head;
+  const bool row0_in = row0 < rows_per_head, row1_in = row1 < rows_per_head;
   const int t0 = row0 / p.group, g0 = row0 - t0 * p.group;
   const int t1 = row1 / p.group, g1 = row1 - t1 * p.group;
   const int rq = p.seqlen_q * p.nheads;      // partial rows per slot
@@ -263,14 +295,15 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
     while (pre[b + 1] <= f) ++b;
     const Span sp = request_span(p, b, n_active);
     const int seg_end = min(f1, pre[b + 1]);
+    const bool row0_ok = row0_in && t0 < sp.q_valid, row1_ok = row1_in && t1 < sp.q_valid;
 
     // ---- Q fragments of this warp's 16 rows (zero for rows past the window)
     uint32_t qa[8][4];
     {
-      const __nv_bfloat16* q0 =
-          p.q + ((static_cast<long long>(b) * p.seqlen_q + t0) * p.nheads + h * p.group + g0) * kHeadDim;
-      const __nv_bfloat16* q1 =
-          p.q + ((static_cast<long long>(b) * p.seqlen_q + t1) * p.nheads + h * p.group + g1) * kHeadDim;
+      const __nv_bfloat16* q0 = p.q + (static_cast<long long>(sp.q_row0) + t0) * p.q_tok_stride +
+                                static_cast<long long>(h * p.group + g0) * p.q_head_stride;
+      const __nv_bfloat16* q1 = p.q + (static_cast<long long>(sp.q_row0) + t1) * p.q_tok_stride +
+                                static_cast<long long>(h * p.group + g1) * p.q_head_stride;
 #pragma unroll
       for (int ks = 0; ks < 8; ++ks) {
         if constexpr (!kFp8) {
@@ -301,7 +334,7 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
     for (int i = 0; i < 16; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
     float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
     // Bottom-right diagonals of the two rows this thread owns.
-    const int diag0 = sp.total - p.seqlen_q + t0, diag1 = sp.total - p.seqlen_q + t1;
+    const int diag0 = sp.diag_base + t0, diag1 = sp.diag_base + t1;
 
     for (; f < seg_end; ++f) {
       const int pos0 = (f - pre[b] + sp.first_tile) * kTile;
@@ -325,7 +358,7 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
           uint8_t* gv = nullptr;
           if (is_new && mti == 0) {
             const int page_idx = pos / p.page_size;
-            int page = p.merged ? p.block_table[static_cast<long long>(b) * p.pages_per_seq + page_idx]
+            int page = p.merged ? p.block_table[static_cast<long long>(sp.req) * p.pages_per_seq + page_idx]
                                 : (p.cache_batch_idx ? p.cache_batch_idx[b] : b);
             if (page < 0 || page >= p.num_pages) page = 0;
             const long long row = (static_cast<long long>(page) * p.page_size + (pos - page_idx * p.page_size)) *
@@ -405,7 +438,7 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
           if (p.softcap > 0.f) x = accurate_tanh(x) * c2;
           s[nt][i] = x;
         }
-      const bool mask_right = pos0 + kTile > sp.total - p.seqlen_q;
+      const bool mask_right = pos0 + kTile > min(sp.diag_base, sp.kv_end);
       const bool mask_left = p.window_left >= 0 && pos0 < sp.total - 1 - p.window_left;
       if (mask_right || mask_left) {
 #pragma unroll
@@ -414,7 +447,7 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
           for (int i = 0; i < 4; ++i) {
             const int j = pos0 + nt * 8 + 2 * tq + (i & 1);
             const int diag = (i < 2) ? diag0 : diag1;
-            bool vis = j < sp.total && (!p.causal || j <= diag);
+            bool vis = j < sp.kv_end && (!p.causal || j <= diag);
             if (p.window_left >= 0) vis = vis && (j >= diag - p.window_left);
             if (!vis) s[nt][i] = -INFINITY;
           }
@@ -553,41 +586,21 @@ struct CombineParams {
 constexpr int kCombineWarps = 4;
 
 // One block per (request, group of kCombineWarps rows); a warp merges the
-// segments of one (token, head) row.  Recomputes the tile prefix the decode
-// kernel used, so the two agree on which CTAs touched the request.
+// segments of one (token, head) row.  Reads the tile prefix the decode kernel
+// left in the workspace, so the two agree on which CTAs touched the request.
 __global__ void __launch_bounds__(kCombineWarps * 32) combine_kernel(const CombineParams cp) {
   const DecodeParams& p = cp.d;
-  __shared__ int red[kCombineWarps * 2];
   const int b = blockIdx.x;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n_active = load_num_active(p);
-  // tiles before request b and tiles in total
-  int before = 0, total_tiles = 0;
-  for (int i = threadIdx.x; i < p.batch; i += blockDim.x) {
-    const int n = request_span(p, i, n_active).n_tiles;
-    total_tiles += n;
-    if (i < b) before += n;
-  }
-#pragma unroll
-  for (int off = 16; off; off >>= 1) {
-    before += __shfl_xor_sync(0xffffffffu, before, off);
-    total_tiles += __shfl_xor_sync(0xffffffffu, total_tiles, off);
-  }
-  if (lane == 0) {
-    red[warp * 2] = before;
-    red[warp * 2 + 1] = total_tiles;
-  }
-  __syncthreads();
-  before = total_tiles = 0;
-  for (int w = 0; w < kCombineWarps; ++w) {
-    before += red[w * 2];
-    total_tiles += red[w * 2 + 1];
-  }
+  const int before = p.tile_prefix[b];
+  const int total_tiles = p.tile_prefix[p.batch];
   const Span sp = request_span(p, b, n_active);
   const int rq = p.seqlen_q * p.nheads;
   const int row = blockIdx.y * kCombineWarps + warp;
   if (row >= rq) return;
   const int t = row / p.nheads, hq = row - t * p.nheads;
+  if (t >= sp.q_valid) return;  // not a real query row of this item
 
   int c_lo = 0, c_hi = -1;
   if (sp.n_tiles > 0) {
@@ -659,13 +672,18 @@ __global__ void __launch_bounds__(kCombineWarps * 32) combine_kernel(const Combi
       lse = (m_all + log2f(den_all)) * kLn2;
     }
   }
-  const long long orow = (static_cast<long long>(b) * p.seqlen_q + t) * p.nheads + hq;
+  const long long ooff = (static_cast<long long>(sp.q_row0) + t) * p.q_tok_stride +
+                         static_cast<long long>(hq) * p.q_head_stride;
   uint2 packed;
   packed.x = pack_bf16(acc.x * out_scale, acc.y * out_scale);
   packed.y = pack_bf16(acc.z * out_scale, acc.w * out_scale);
-  *reinterpret_cast<uint2*>(cp.out + orow * kHeadDim + lane * 4) = packed;
-  if (cp.lse != nullptr && lane == 0)
-    cp.lse[(static_cast<long long>(b) * p.nheads + hq) * p.seqlen_q + t] = lse;
+  *reinterpret_cast<uint2*>(cp.out + ooff + lane * 4) = packed;
+  if (cp.lse != nullptr && lane == 0) {
+    if (p.items != nullptr)
+      cp.lse[static_cast<long long>(hq) * p.total_q + sp.q_row0 + t] = lse;
+    else
+      cp.lse[(static_cast<long long>(b) * p.nheads + hq) * p.seqlen_q + t] = lse;
+  }
 }
 
 // ---------------------------------------------------------------- host
@@ -674,11 +692,11 @@ struct DecodePlan {
   int itemsize;
   int rows_q;
   long long slots;
-  uint64_t off_ml, off_o, bytes;
+  uint64_t off_prefix, off_ml, off_o, bytes;
   size_t smem;
 };
 
-static int plan_decode(const FwDecodeArgs* a, DecodePlan* plan) {
+static int plan_decode(const FwDecodeArgs* a, DecodePlan* plan, int max_batch = kMaxInlineBatch) {
   if (a == nullptr) {
     set_error("args is NULL");
     return FW_ERR_BAD_SHAPE;
@@ -747,8 +765,8 @@ static int plan_decode(const FwDecodeArgs* a, DecodePlan* plan) {
     set_error("window_left must be -1 (unbounded) or non-negative; got %d.", a->window_left);
     return FW_ERR_BAD_SHAPE;
   }
-  if (a->batch > kMaxInlineBatch) {
-    set_error("batch %d exceeds %d per call; split the batch.", a->batch, kMaxInlineBatch);
+  if (a->batch > max_batch) {
+    set_error("batch %d exceeds %d per call; split the batch.", a->batch, max_batch);
     return FW_ERR_UNSUPPORTED;
   }
   if ((a->partial_out == nullptr) != (a->partial_lse == nullptr)) {
@@ -815,13 +833,82 @@ static int plan_decode(const FwDecodeArgs* a, DecodePlan* plan) {
   p.window_left = a->window_left;
   p.scale = a->softmax_scale;
   p.softcap = a->softcap;
+  p.items = nullptr;
+  p.q_tok_stride = static_cast<long long>(a->nheads) * kHeadDim;
+  p.q_head_stride = kHeadDim;
+  p.total_q = a->batch * a->seqlen_q;
   plan->itemsize = itemsize;
   plan->rows_q = a->seqlen_q * a->nheads;
   plan->slots = static_cast<long long>(a->batch) + p.ncta;
-  plan->off_ml = 256;
+  plan->off_prefix = 256;
+  plan->off_ml = (plan->off_prefix + (static_cast<uint64_t>(a->batch) + 1) * sizeof(int) + 255) & ~255ull;
   const uint64_t ml_bytes = static_cast<uint64_t>(plan->slots) * plan->rows_q * 2 * sizeof(float);
   plan->off_o = (plan->off_ml + ml_bytes + 255) & ~255ull;
   plan->bytes = plan->off_o + static_cast<uint64_t>(plan->slots) * plan->rows_q * kHeadDim * sizeof(float);
+  return FW_OK;
+}
+
+}  // namespace fw
+
+namespace fw {
+
+// Enqueues decode_kernel + combine_kernel for a finished plan.
+static int launch_decode(DecodePlan& plan, void* workspace, cudaStream_t stream, int kv_dtype, void* out,
+                         float* lse, float* partial_out, float* partial_lse, const float* v_descale,
+                         const float* sinks) {
+  int rc;
+  DecodeParams& p = plan.p;
+  uint8_t* ws = static_cast<uint8_t*>(workspace);
+  p.status = reinterpret_cast<int*>(ws);
+  p.tile_prefix = reinterpret_cast<int*>(ws + plan.off_prefix);
+  p.part_ml = reinterpret_cast<float*>(ws + plan.off_ml);
+  p.part_o = reinterpret_cast<float*>(ws + plan.off_o);
+
+  // Tensor maps: bytes (128) x tokens-in-page x 128-byte segments x pages, so a
+  // stage lands token-major inside each head segment.
+  CUtensorMap map_k, map_v;
+  const uint64_t segs = static_cast<uint64_t>(p.row_bytes) / 128;
+  const uint64_t dims[4] = {128, static_cast<uint64_t>(p.page_size), segs, static_cast<uint64_t>(p.num_pages)};
+  const uint64_t strides[3] = {static_cast<uint64_t>(p.row_bytes), 128,
+                               static_cast<uint64_t>(p.page_size) * p.row_bytes};
+  const uint32_t box[4] = {128, kTile, static_cast<uint32_t>(p.merged ? p.hpc * 2 * p.spp : p.hpc * p.spp), 1};
+  rc = encode_tensor_map_u8_4d(&map_k, p.k_base, dims, strides, box);
+  if (rc != FW_OK) return rc;
+  rc = encode_tensor_map_u8_4d(&map_v, p.v_base, dims, strides, box);
+  if (rc != FW_OK) return rc;
+
+  auto kernel = kv_dtype == FW_DTYPE_BF16   ? decode_kernel<FW_DTYPE_BF16>
+                : kv_dtype == FW_DTYPE_E4M3 ? decode_kernel<FW_DTYPE_E4M3>
+                                               : decode_kernel<FW_DTYPE_E5M2>;
+  cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         static_cast<int>(plan.smem));
+  if (err != cudaSuccess) {
+    set_error("cudaFuncSetAttribute(%zu bytes): %s", plan.smem, cudaGetErrorString(err));
+    return FW_ERR_LAUNCH;
+  }
+  dim3 grid(p.ncta, p.nhg);
+  dim3 block((p.hpc * p.mt + 1) * 32);
+  kernel<<<grid, block, plan.smem, stream>>>(map_k, map_v, p);
+  err = cudaGetLastError();
+  if (err != cudaSuccess) {
+    set_error("decode kernel launch: %s", cudaGetErrorString(err));
+    return FW_ERR_LAUNCH;
+  }
+  CombineParams cp;
+  cp.d = p;
+  cp.out = static_cast<__nv_bfloat16*>(out);
+  cp.lse = lse;
+  cp.partial_out = partial_out;
+  cp.partial_lse = partial_lse;
+  cp.v_descale = v_descale;
+  cp.sinks = sinks;
+  dim3 cgrid(p.batch, (plan.rows_q + kCombineWarps - 1) / kCombineWarps);
+  combine_kernel<<<cgrid, kCombineWarps * 32, 0, stream>>>(cp);
+  err = cudaGetLastError();
+  if (err != cudaSuccess) {
+    set_error("combine kernel launch: %s", cudaGetErrorString(err));
+    return FW_ERR_LAUNCH;
+  }
   return FW_OK;
 }
 
@@ -856,60 +943,206 @@ extern "C" int fw_decode_kvcache(const FwDecodeArgs* a, void* stream_ptr) {
     set_error("q, out, caches and new k/v must be 16-byte aligned.");
     return FW_ERR_BAD_SHAPE;
   }
-  cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
-  DecodeParams& p = plan.p;
-  uint8_t* ws = static_cast<uint8_t*>(a->workspace);
-  p.status = reinterpret_cast<int*>(ws);
-  p.part_ml = reinterpret_cast<float*>(ws + plan.off_ml);
-  p.part_o = reinterpret_cast<float*>(ws + plan.off_o);
+  return launch_decode(plan, a->workspace, static_cast<cudaStream_t>(stream_ptr), a->kv_dtype, a->out, a->lse,
+                       a->partial_out, a->partial_lse, a->v_descale, a->sinks);
+}
 
-  // Tensor maps: bytes (128) x tokens-in-page x 128-byte segments x pages, so a
-  // stage lands token-major inside each head segment.
-  CUtensorMap map_k, map_v;
-  const uint64_t segs = static_cast<uint64_t>(p.row_bytes) / 128;
-  const uint64_t dims[4] = {128, static_cast<uint64_t>(p.page_size), segs, static_cast<uint64_t>(p.num_pages)};
-  const uint64_t strides[3] = {static_cast<uint64_t>(p.row_bytes), 128,
-                               static_cast<uint64_t>(p.page_size) * p.row_bytes};
-  const uint32_t box[4] = {128, kTile, static_cast<uint32_t>(p.merged ? p.hpc * 2 * p.spp : p.hpc * p.spp), 1};
-  rc = encode_tensor_map_u8_4d(&map_k, p.k_base, dims, strides, box);
-  if (rc != FW_OK) return rc;
-  rc = encode_tensor_map_u8_4d(&map_v, p.v_base, dims, strides, box);
-  if (rc != FW_OK) return rc;
+// ---------------------------------------------------------------- split-KV prefill
+// Chunked prefill through the split-KV kernel: each packed request is cut into
+// blocks of qb = 128 / group query tokens ("items"); an item is to the decode
+// kernel what a request with a qb-token verify window is, with its own causal
+// diagonal.  Right for short chunks over long prefixes (the work is KV
+// streaming); long chunks go to the tensor-core prefill kernel.
+namespace fw {
 
-  auto kernel = a->kv_dtype == FW_DTYPE_BF16   ? decode_kernel<FW_DTYPE_BF16>
-                : a->kv_dtype == FW_DTYPE_E4M3 ? decode_kernel<FW_DTYPE_E4M3>
-                                               : decode_kernel<FW_DTYPE_E5M2>;
-  cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         static_cast<int>(plan.smem));
-  if (err != cudaSuccess) {
-    set_error("cudaFuncSetAttribute(%zu bytes): %s", plan.smem, cudaGetErrorString(err));
-    return FW_ERR_LAUNCH;
+constexpr int kMaxItems = 8192;
+
+struct PrefillPlanParams {
+  const int* cu;
+  const int* seqused;
+  const int* num_active;
+  int* items;
+  __nv_bfloat16* out;
+  float* lse;
+  long long tok_stride, head_stride;
+  int batch, qb, max_items, total_q, nheads;
+};
+
+// Block 0 writes the item table {request, first q row, valid tokens, diagonal
+// anchor, kv length} (8 ints per item, zero past the last item); all blocks
+// clear the packed rows that belong to no active request (out 0, lse -inf).
+__global__ void __launch_bounds__(256) prefill_plan_kernel(const PrefillPlanParams pp) {
+  __shared__ int off[kMaxInlineBatch + 1];
+  const int n_active = pp.num_active ? min(pp.batch, max(0, *pp.num_active)) : pp.batch;
+  if (blockIdx.x == 0) {
+    for (int r = threadIdx.x; r < pp.batch; r += blockDim.x) {
+      const int c = r < n_active ? max(0, pp.cu[r + 1] - pp.cu[r]) : 0;
+      off[r + 1] = (c + pp.qb - 1) / pp.qb;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      off[0] = 0;
+      for (int r = 0; r < pp.batch; ++r) off[r + 1] += off[r];
+    }
+    __syncthreads();
+    const int n_items = min(off[pp.batch], pp.max_items);
+    for (int r = threadIdx.x; r < pp.batch; r += blockDim.x) {
+      const int blocks = off[r + 1] - off[r];
+      if (blocks == 0) continue;
+      const int c = pp.cu[r + 1] - pp.cu[r];
+      const int used = pp.seqused[r];
+      for (int j = 0; j < blocks; ++j) {
+        const int idx = off[r] + j;
+        if (idx >= pp.max_items) break;
+        int* it = pp.items + 8 * idx;
+        it[0] = r;
+        it[1] = pp.cu[r] + j * pp.qb;
+        it[2] = min(pp.qb, c - j * pp.qb);
+        it[3] = used - c + (j + 1) * pp.qb;  // token t of the block sits on diagonal it[3] - qb + t
+        it[4] = used;
+        it[5] = it[6] = it[7] = 0;
+      }
+    }
+    for (int idx = n_items + threadIdx.x; idx < pp.max_items; idx += blockDim.x) {
+      int* it = pp.items + 8 * idx;
+#pragma unroll
+      for (int k = 0; k < 8; ++k) it[k] = 0;
+    }
   }
-  dim3 grid(p.ncta, p.nhg);
-  dim3 block((p.hpc * p.mt + 1) * 32);
-  kernel<<<grid, block, plan.smem, stream>>>(map_k, map_v, p);
-  err = cudaGetLastError();
-  if (err != cudaSuccess) {
-    set_error("decode kernel launch: %s", cudaGetErrorString(err));
-    return FW_ERR_LAUNCH;
+  const int pad_start = min(max(pp.cu[n_active], 0), pp.total_q);
+  const long long pad_rows = pp.total_q - pad_start;
+  const long long chunks = pad_rows * pp.nheads * (kHeadDim / 8);
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < chunks;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int c = static_cast<int>(i % (kHeadDim / 8));
+    const long long rh = i / (kHeadDim / 8);
+    const int hq = static_cast<int>(rh % pp.nheads);
+    const long long row = pad_start + rh / pp.nheads;
+    *reinterpret_cast<uint4*>(pp.out + row * pp.tok_stride + hq * pp.head_stride + c * 8) =
+        make_uint4(0u, 0u, 0u, 0u);
+    if (c == 0 && pp.lse != nullptr) pp.lse[static_cast<long long>(hq) * pp.total_q + row] = -INFINITY;
   }
-  CombineParams cp;
-  cp.d = p;
-  cp.out = static_cast<__nv_bfloat16*>(a->out);
-  cp.lse = a->lse;
-  cp.partial_out = a->partial_out;
-  cp.partial_lse = a->partial_lse;
-  cp.v_descale = a->v_descale;
-  cp.sinks = a->sinks;
-  dim3 cgrid(p.batch, (plan.rows_q + kCombineWarps - 1) / kCombineWarps);
-  combine_kernel<<<cgrid, kCombineWarps * 32, 0, stream>>>(cp);
-  err = cudaGetLastError();
-  if (err != cudaSuccess) {
-    set_error("combine kernel launch: %s", cudaGetErrorString(err));
-    return FW_ERR_LAUNCH;
+}
+
+struct SplitKvPrefillPlan {
+  DecodePlan decode;
+  int qb, max_items;
+  uint64_t off_items, bytes;
+};
+
+static int plan_splitkv_prefill(const FwPrefillArgs* a, SplitKvPrefillPlan* sp) {
+  if (a == nullptr) {
+    set_error("args is NULL");
+    return FW_ERR_BAD_SHAPE;
   }
+  if (a->batch <= 0 || a->total_q <= 0 || a->nheads <= 0 || a->nheads_k <= 0 || a->nheads % a->nheads_k) {
+    set_error("batch, total_q must be positive and nheads=%d a multiple of nheads_k=%d.", a->nheads,
+              a->nheads_k);
+    return FW_ERR_BAD_SHAPE;
+  }
+  if (a->batch > kMaxInlineBatch) {
+    set_error("batch %d exceeds %d per call; split the batch.", a->batch, kMaxInlineBatch);
+    return FW_ERR_UNSUPPORTED;
+  }
+  const int group = a->nheads / a->nheads_k;
+  if (group > 128) {
+    set_error("nheads / nheads_k = %d exceeds 128 query heads per KV head.", group);
+    return FW_ERR_UNSUPPORTED;
+  }
+  sp->qb = 128 / group;
+  sp->max_items = (a->total_q + sp->qb - 1) / sp->qb + a->batch;
+  if (sp->max_items > kMaxItems) {
+    set_error("total_q %d makes %d query blocks; the split-KV prefill takes at most %d per call.", a->total_q,
+              sp->max_items, kMaxItems);
+    return FW_ERR_UNSUPPORTED;
+  }
+  FwDecodeArgs fa = {};
+  fa.block_table = a->block_table != nullptr ? a->block_table : reinterpret_cast<const int32_t*>(16);
+  fa.num_pages = a->num_pages;
+  fa.page_size = a->page_size;
+  fa.pages_per_seq = a->pages_per_seq;
+  fa.batch = sp->max_items;
+  fa.seqlen_q = sp->qb;
+  fa.nheads = a->nheads;
+  fa.nheads_k = a->nheads_k;
+  fa.head_dim = a->head_dim;
+  fa.kv_dtype = a->kv_dtype;
+  fa.causal = a->causal;
+  fa.window_left = a->window_left;
+  fa.softmax_scale = a->softmax_scale;
+  fa.softcap = a->softcap;
+  int rc = plan_decode(&fa, &sp->decode, kMaxItems);
+  if (rc != FW_OK) return rc;
+  DecodeParams& p = sp->decode.p;
+  p.k_base = p.v_base = static_cast<uint8_t*>(const_cast<void*>(a->kv_cache));
+  p.block_table = a->block_table;
+  p.k_descale = a->k_descale;
+  p.total_q = a->total_q;
+  if (a->token_major) {
+    p.q_tok_stride = static_cast<long long>(a->nheads) * kHeadDim;
+    p.q_head_stride = kHeadDim;
+  } else {
+    p.q_tok_stride = kHeadDim;
+    p.q_head_stride = static_cast<long long>(a->total_q) * kHeadDim;
+  }
+  sp->off_items = (sp->decode.bytes + 255) & ~255ull;
+  sp->bytes = sp->off_items + static_cast<uint64_t>(sp->max_items) * 8 * sizeof(int);
   return FW_OK;
 }
+
+uint64_t splitkv_prefill_workspace_bytes(const FwPrefillArgs* a) {
+  SplitKvPrefillPlan sp;
+  return plan_splitkv_prefill(a, &sp) == FW_OK ? sp.bytes : 0;
+}
+
+int splitkv_prefill(const FwPrefillArgs* a, cudaStream_t stream) {
+  SplitKvPrefillPlan sp;
+  int rc = plan_splitkv_prefill(a, &sp);
+  if (rc != FW_OK) return rc;
+  if (a->q == nullptr || a->out == nullptr || a->kv_cache == nullptr || a->cu_seqlens_q == nullptr ||
+      a->seqused_k == nullptr || a->block_table == nullptr) {
+    set_error("q, out, kv_cache, cu_seqlens_q, seqused_k and block_table must not be NULL.");
+    return FW_ERR_BAD_SHAPE;
+  }
+  if (a->workspace == nullptr || a->workspace_bytes < sp.bytes || (reinterpret_cast<uintptr_t>(a->workspace) & 255)) {
+    set_error("workspace must be 256-byte aligned and hold %llu bytes; got %llu.",
+              static_cast<unsigned long long>(sp.bytes), static_cast<unsigned long long>(a->workspace_bytes));
+    return FW_ERR_WORKSPACE;
+  }
+  if ((reinterpret_cast<uintptr_t>(a->kv_cache) & 15) || (reinterpret_cast<uintptr_t>(a->q) & 15) ||
+      (reinterpret_cast<uintptr_t>(a->out) & 15)) {
+    set_error("q, out and the cache must be 16-byte aligned.");
+    return FW_ERR_BAD_SHAPE;
+  }
+  DecodeParams& p = sp.decode.p;
+  int* items = reinterpret_cast<int*>(static_cast<uint8_t*>(a->workspace) + sp.off_items);
+  p.q = static_cast<const __nv_bfloat16*>(a->q);
+  p.items = items;
+  PrefillPlanParams pp;
+  pp.cu = a->cu_seqlens_q;
+  pp.seqused = a->seqused_k;
+  pp.num_active = a->num_active;
+  pp.items = items;
+  pp.out = static_cast<__nv_bfloat16*>(a->out);
+  pp.lse = a->lse;
+  pp.tok_stride = p.q_tok_stride;
+  pp.head_stride = p.q_head_stride;
+  pp.batch = a->batch;
+  pp.qb = sp.qb;
+  pp.max_items = sp.max_items;
+  pp.total_q = a->total_q;
+  pp.nheads = a->nheads;
+  prefill_plan_kernel<<<min(sm_count(), 64), 256, 0, stream>>>(pp);
+  cudaError_t err = cudaGetLastError();
+  if (err != cudaSuccess) {
+    set_error("prefill plan kernel launch: %s", cudaGetErrorString(err));
+    return FW_ERR_LAUNCH;
+  }
+  return launch_decode(sp.decode, a->workspace, stream, a->kv_dtype, a->out, a->lse, nullptr, nullptr,
+                       a->v_descale, a->sinks);
+}
+
+}  // namespace fw
 
 // ---------------------------------------------------------------- static scratch
 // Decode for callers that cannot allocate device memory.  The split-KV partial
