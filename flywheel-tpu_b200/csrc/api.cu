@@ -76,6 +76,31 @@ int encode_tensor_map_u8_4d(CUtensorMap* map, const void* base, const uint64_t d
   return FW_OK;
 }
 
+int encode_tensor_map_bf16(CUtensorMap* map, int rank, const void* base, const uint64_t* dims,
+                           const uint64_t* strides, const uint32_t* box) {
+  EncodeTiledFn fn = encode_fn();
+  if (fn == nullptr) {
+    set_error("cuTensorMapEncodeTiled is not available from this driver.");
+    return FW_ERR_LAUNCH;
+  }
+  cuuint64_t gdims[5], gstrides[4];
+  cuuint32_t gbox[5], estrides[5];
+  for (int i = 0; i < rank; ++i) {
+    gdims[i] = dims[i];
+    gbox[i] = box[i];
+    estrides[i] = 1;
+    if (i + 1 < rank) gstrides[i] = strides[i];
+  }
+  CUresult res = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, rank, const_cast<void*>(base), gdims, gstrides, gbox,
+                    estrides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (res != CUDA_SUCCESS) {
+    set_error("cuTensorMapEncodeTiled (bf16, rank %d) failed with CUresult %d", rank, static_cast<int>(res));
+    return FW_ERR_LAUNCH;
+  }
+  return FW_OK;
+}
+
 }  // namespace fw
 
 extern "C" const char* fw_last_error(void) { return fw::g_error; }

@@ -178,6 +178,22 @@ int sm_count();
 int encode_tensor_map_u8_4d(CUtensorMap* map, const void* base, const uint64_t dims[4],
                             const uint64_t strides[3], const uint32_t box[4]);
 
+// bf16-typed tiled tensor map of rank 3 or 4 with 128-byte swizzle; strides are
+// for dims 1..rank-1 in bytes.
+int encode_tensor_map_bf16(CUtensorMap* map, int rank, const void* base, const uint64_t* dims,
+                           const uint64_t* strides, const uint32_t* box);
+
+// Query-block table for chunked prefill (decode.cu): cuts every active request
+// into blocks of qb tokens, writes 8 ints per block into items[0..max_items)
+// and clears the packed rows no active request owns.
+int launch_prefill_plan(const FwPrefillArgs* args, int qb, int max_items, int* items, long long tok_stride,
+                        long long head_stride, cudaStream_t stream);
+
+// Chunked prefill on tcgen05 tensor cores (prefill_tcgen05.cu).
+bool tcgen05_prefill_supported(const FwPrefillArgs* args);
+uint64_t tcgen05_prefill_workspace_bytes(const FwPrefillArgs* args);
+int tcgen05_prefill(const FwPrefillArgs* args, cudaStream_t stream);
+
 // Chunked prefill through the split-KV decode kernel (decode.cu).
 uint64_t splitkv_prefill_workspace_bytes(const FwPrefillArgs* args);
 int splitkv_prefill(const FwPrefillArgs* args, cudaStream_t stream);

@@ -1024,6 +1024,35 @@ __global__ void __launch_bounds__(256) prefill_plan_kernel(const PrefillPlanPara
   }
 }
 
+int launch_prefill_plan(const FwPrefillArgs* a, int qb, int max_items, int* items, long long tok_stride,
+                        long long head_stride, cudaStream_t stream) {
+  if (a->batch > kMaxInlineBatch) {
+    set_error("batch %d exceeds %d per call; split the batch.", a->batch, kMaxInlineBatch);
+    return FW_ERR_UNSUPPORTED;
+  }
+  PrefillPlanParams pp;
+  pp.cu = a->cu_seqlens_q;
+  pp.seqused = a->seqused_k;
+  pp.num_active = a->num_active;
+  pp.items = items;
+  pp.out = static_cast<__nv_bfloat16*>(a->out);
+  pp.lse = a->lse;
+  pp.tok_stride = tok_stride;
+  pp.head_stride = head_stride;
+  pp.batch = a->batch;
+  pp.qb = qb;
+  pp.max_items = max_items;
+  pp.total_q = a->total_q;
+  pp.nheads = a->nheads;
+  prefill_plan_kernel<<<min(sm_count(), 64), 256, 0, stream>>>(pp);
+  cudaError_t err = cudaGetLastError();
+  if (err != cudaSuccess) {
+    set_error("prefill plan kernel launch: %s", cudaGetErrorString(err));
+    return FW_ERR_LAUNCH;
+  }
+  return FW_OK;
+}
+
 struct SplitKvPrefillPlan {
   DecodePlan decode;
   int qb, max_items;
@@ -1118,26 +1147,8 @@ int splitkv_prefill(const FwPrefillArgs* a, cudaStream_t stream) {
   int* items = reinterpret_cast<int*>(static_cast<uint8_t*>(a->workspace) + sp.off_items);
   p.q = static_cast<const __nv_bfloat16*>(a->q);
   p.items = items;
-  PrefillPlanParams pp;
-  pp.cu = a->cu_seqlens_q;
-  pp.seqused = a->seqused_k;
-  pp.num_active = a->num_active;
-  pp.items = items;
-  pp.out = static_cast<__nv_bfloat16*>(a->out);
-  pp.lse = a->lse;
-  pp.tok_stride = p.q_tok_stride;
-  pp.head_stride = p.q_head_stride;
-  pp.batch = a->batch;
-  pp.qb = sp.qb;
-  pp.max_items = sp.max_items;
-  pp.total_q = a->total_q;
-  pp.nheads = a->nheads;
-  prefill_plan_kernel<<<min(sm_count(), 64), 256, 0, stream>>>(pp);
-  cudaError_t err = cudaGetLastError();
-  if (err != cudaSuccess) {
-    set_error("prefill plan kernel launch: %s", cudaGetErrorString(err));
-    return FW_ERR_LAUNCH;
-  }
+  rc = launch_prefill_plan(a, sp.qb, sp.max_items, items, p.q_tok_stride, p.q_head_stride, stream);
+  if (rc != FW_OK) return rc;
   return launch_decode(sp.decode, a->workspace, stream, a->kv_dtype, a->out, a->lse, nullptr, nullptr,
                        a->v_descale, a->sinks);
 }

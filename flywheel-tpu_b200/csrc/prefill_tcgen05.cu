@@ -1,0 +1,558 @@
+// Chunked prefill over the paged merged bf16 cache on the 5th-generation tensor
+// cores: QK^T and PV are tcgen05.mma with f32 accumulators in tensor memory,
+// Q and the paged K/V tiles are staged by tiled (non-multicast) TMA copies.
+//
+// Follows the block_table branch of flash_attn_varlen_func in the reference
+// project (flywheel_tpu/softmax_attention/prefill.py:437-661 and
+// kernels/fwd_paged.py:331-1019): bottom-right aligned causal / left-window
+// mask per packed request, softcap before masking, sinks in the denominator,
+// out 0 / lse -inf for padding rows.  Fully masked KV tiles are never loaded.
+//
+// One CTA = one query block of one KV head: 128 rows = (128 / group) tokens x
+// the `group` query heads that share the KV head (rows ordered head-major), so
+// every K/V tile is fetched once for the whole GQA group.  KV advances in
+// 64-key tiles (one 64-token page, or a 64-token slice of a larger page).
+// Warp roles: warp 0 issues TMA, warp 1 owns tensor memory and issues the MMAs,
+// warps 2-5 are the softmax group (one thread per row: tcgen05.ld of S, online
+// softmax with lazy rescale, P written to shared memory as the A operand of
+// the PV MMA).  Two CTAs share an SM (~112 KiB shared memory, 256 TMEM columns
+// each), so one CTA's softmax overlaps the other's MMAs.
+#include "common.cuh"
+
+namespace fw {
+
+constexpr int kBM = 128;       // query rows per CTA
+constexpr int kBN = 64;        // keys per KV tile
+constexpr int kKvStages = 2;
+constexpr int kTmemCols = 256; // O: [0,128), S double buffer: [128,192), [192,256)
+constexpr float kRescaleThreshold = 8.0f;  // log2 units a row max may drift before O is rescaled
+
+constexpr int kSmemQ = 0;                      // 2 halves x [128 rows][128 B]
+constexpr int kSmemK = 32768;                  // stages x 2 halves x [64 keys][128 B]
+constexpr int kSmemV = kSmemK + kKvStages * 16384;
+constexpr int kSmemP = kSmemV + kKvStages * 16384;  // [128 rows][128 B]
+constexpr int kSmemBar = kSmemP + 16384;
+constexpr int kSmemBytes = kSmemBar + 256;
+
+struct Tc05Params {
+  const int* items;  // 8 ints per query block: request, first q row, valid tokens, diagonal anchor, kv length
+  const int* block_table;
+  const float* k_descale;
+  const float* v_descale;
+  const float* sinks;
+  __nv_bfloat16* out;
+  float* lse;
+  int* status;
+  long long tok_stride, head_stride;  // elements, shared by q and out
+  long long num_pages;
+  int total_q, nheads, group, tpb, page_size, pages_per_seq;
+  int causal, window_left;
+  float scale, softcap;
+};
+
+// ---------------------------------------------------------------- tcgen05 wrappers
+__device__ __forceinline__ void tmem_alloc(uint32_t* smem_slot, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_slot)),
+               "r"(cols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() {
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after() {
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+               : "memory");
+}
+// D(tmem) (+)= A(smem) * B(smem), bf16 operands, f32 accumulate.
+__device__ __forceinline__ void tc_mma(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                       uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t"
+      "}\n" ::"r"(tmem_d),
+      "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,"
+      "%28,%29,%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]),
+        "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]),
+        "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,"
+      "%29,%30,%31,%32};" ::"r"(taddr),
+      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+      "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]),
+      "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]),
+      "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor, 128-byte swizzle, sm_100 version bits.
+// K-major operand: rows of 128 B, 8-row groups 1024 B apart (SBO); LBO unused.
+// MN-major operand: 64-element (128 B) runs along MN, next run LBO bytes away,
+// next group of 8 K-rows SBO bytes away.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((addr >> 4) & 0x3fff);
+  d |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3fff) << 16;
+  d |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3fff) << 32;
+  d |= 1ull << 46;  // descriptor version for sm_100
+  d |= 2ull << 61;  // SWIZZLE_128B
+  return d;
+}
+
+// kind::f16 instruction descriptor: f32 accumulate, bf16 A and B, M = 128.
+__host__ __device__ constexpr uint32_t instr_desc(int n, bool b_mn_major) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | (b_mn_major ? (1u << 16) : 0u) |
+         (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(kBM >> 4) << 24);
+}
+
+struct Bars {
+  uint64_t q_full;
+  uint64_t k_full[kKvStages], v_full[kKvStages], kv_empty[kKvStages];
+  uint64_t s_full[2], s_empty[2];
+  uint64_t p_full, pv_done;
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+__global__ void __launch_bounds__(192, 2)
+prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv,
+                       const Tc05Params p) {
+  extern __shared__ __align__(1024) uint8_t smem[];
+  Bars* bars = reinterpret_cast<Bars*>(smem + kSmemBar);
+  volatile int* abort_flag = &bars->abort_flag;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int item = blockIdx.x, h = blockIdx.y;
+
+  const int4 it = *reinterpret_cast<const int4*>(p.items + 8 * item);
+  const int req = it.x, q_row0 = it.y, q_valid = it.z, anchor = it.w;
+  const int kv_limit = p.items[8 * item + 4];
+  const int kv_end = p.causal ? min(anchor, kv_limit) : kv_limit;
+  if (q_valid <= 0) return;  // uniform across the CTA: nothing allocated yet
+  const int diag_base = anchor - p.tpb;  // token t of the block sits on diagonal diag_base + t
+  const int first_key = p.window_left >= 0 ? max(0, diag_base - p.window_left) : 0;
+  const int tile_lo = first_key / kBN;
+  const int tile_hi = kv_end > 0 ? (kv_end + kBN - 1) / kBN : 0;  // exclusive
+  const int n_tiles = max(0, tile_hi - tile_lo);
+
+  if (threadIdx.x == 0) {
+    mbar_init(&bars->q_full, 1);
+    for (int s = 0; s < kKvStages; ++s) {
+      mbar_init(&bars->k_full[s], 1);
+      mbar_init(&bars->v_full[s], 1);
+      mbar_init(&bars->kv_empty[s], 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&bars->s_full[s], 1);
+      mbar_init(&bars->s_empty[s], 4);
+    }
+    mbar_init(&bars->p_full, 4);
+    mbar_init(&bars->pv_done, 1);
+    bars->abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 1 && n_tiles > 0) {
+    tmem_alloc(&bars->tmem_base, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = bars->tmem_base;
+
+  if (n_tiles > 0 && warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      tma_prefetch_desc(&map_q);
+      tma_prefetch_desc(&map_kv);
+      mbar_arrive_expect_tx(&bars->q_full, kBM * 256);
+      for (int g = 0; g < p.group; ++g)
+        for (int half = 0; half < 2; ++half)
+          tma_load_3d(smem + kSmemQ + half * 16384 + g * p.tpb * 128, &map_q, &bars->q_full, half * 64, q_row0,
+                      h * p.group + g);
+      bool ok = true;
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        const int s = j % kKvStages;
+        const uint32_t round = j / kKvStages;
+        if (!mbar_wait_bounded(&bars->kv_empty[s], (round & 1) ^ 1, abort_flag)) {
+          ok = false;
+          break;
+        }
+        const int pos0 = (tile_lo + j) * kBN;
+        const int page_idx = pos0 / p.page_size;
+        int page = p.block_table[static_cast<long long>(req) * p.pages_per_seq + page_idx];
+        if (page < 0 || page >= p.num_pages) {
+          report_status(p.status, FW_STATUS_BAD_PAGE);
+          page = 0;
+        }
+        const int tok = pos0 - page_idx * p.page_size;
+        mbar_arrive_expect_tx(&bars->k_full[s], kBN * 256);
+        mbar_arrive_expect_tx(&bars->v_full[s], kBN * 256);
+        for (int half = 0; half < 2; ++half) {
+          tma_load_4d(smem + kSmemK + s * 16384 + half * 8192, &map_kv, &bars->k_full[s], half * 64, 2 * h, tok,
+                      page);
+          tma_load_4d(smem + kSmemV + s * 16384 + half * 8192, &map_kv, &bars->v_full[s], half * 64, 2 * h + 1,
+                      tok, page);
+        }
+      }
+      if (!ok) {
+        *abort_flag = 1;
+        report_status(p.status, FW_STATUS_WAIT_TIMEOUT);
+      }
+    }
+  } else if (n_tiles > 0 && warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc_qk = instr_desc(kBN, false);
+      constexpr uint32_t idesc_pv = instr_desc(128, true);
+      const uint32_t q_addr = smem_u32(smem + kSmemQ), p_addr = smem_u32(smem + kSmemP);
+      bool ok = mbar_wait_bounded(&bars->q_full, 0, abort_flag);
+      auto issue_qk = [&](int j) {
+        const int s = j % kKvStages, sb = j & 1;
+        const uint32_t k_addr = smem_u32(smem + kSmemK + s * 16384);
+        tc_fence_after();
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const uint32_t off = (k >> 2) * 16384 + (k & 3) * 32;
+          const uint32_t koff = (k >> 2) * 8192 + (k & 3) * 32;
+          tc_mma(tmem + 128 + sb * 64, smem_desc(q_addr + off, 16, 1024), smem_desc(k_addr + koff, 16, 1024),
+                 idesc_qk, k > 0);
+        }
+        tc_commit(&bars->s_full[sb]);
+      };
+      if (ok) ok = mbar_wait_bounded(&bars->k_full[0], 0, abort_flag);
+      if (ok) issue_qk(0);
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        const int s = j % kKvStages;
+        const uint32_t round = j / kKvStages;
+        if (j + 1 < n_tiles) {
+          const int s1 = (j + 1) % kKvStages, sb1 = (j + 1) & 1;
+          ok = mbar_wait_bounded(&bars->k_full[s1], ((j + 1) / kKvStages) & 1, abort_flag);
+          // S buffer sb1 was last read by the softmax of tile j - 1.
+          if (ok && j >= 1) ok = mbar_wait_bounded(&bars->s_empty[sb1], ((j - 1) >> 1) & 1, abort_flag);
+          if (!ok) break;
+          issue_qk(j + 1);
+        }
+        ok = mbar_wait_bounded(&bars->p_full, j & 1, abort_flag);
+        if (ok) ok = mbar_wait_bounded(&bars->v_full[s], round & 1, abort_flag);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t v_addr = smem_u32(smem + kSmemV + s * 16384);
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          tc_mma(tmem, smem_desc(p_addr + k * 32, 16, 1024), smem_desc(v_addr + k * 2048, 8192, 1024), idesc_pv,
+                 (j > 0 || k > 0) ? 1u : 0u);
+        tc_commit(&bars->kv_empty[s]);
+        tc_commit(&bars->pv_done);
+      }
+      if (!ok) {
+        *abort_flag = 1;
+        report_status(p.status, FW_STATUS_WAIT_TIMEOUT);
+      }
+    }
+  } else if (warp >= 2) {
+    // ------------------------------------------------------------ softmax group
+    const int quarter = warp & 3;            // TMEM lane quarter this warp may touch
+    const int row = quarter * 32 + lane;     // row of the 128-row tile
+    const int g = row / p.tpb, tl = row - g * p.tpb;
+    const bool row_ok = g < p.group && tl < q_valid;
+    const int diag = diag_base + tl;
+    const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
+    const float kd = p.k_descale ? *p.k_descale : 1.0f;
+    const float c1 = p.softcap > 0.f ? p.scale * kd / p.softcap : p.scale * kd * kLog2e;
+    const float c2 = p.softcap * kLog2e;
+    float m_used = -INFINITY, l_run = 0.f;
+    bool ok = true;
+
+    for (int j = 0; j < n_tiles && ok; ++j) {
+      const int sb = j & 1, s = j % kKvStages;
+      const int pos0 = (tile_lo + j) * kBN;
+      if (!mbar_wait_bounded(&bars->s_full[sb], (j >> 1) & 1, abort_flag)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      uint32_t sr[2][32];
+      tmem_ld32(tmem + lane_addr + 128 + sb * 64, sr[0]);
+      tmem_ld32(tmem + lane_addr + 128 + sb * 64 + 32, sr[1]);
+      tmem_wait_ld();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars->s_empty[sb]);
+
+      const bool need_mask = pos0 + kBN > min(diag_base, kv_end) ||
+                             (p.window_left >= 0 && pos0 < diag_base + p.tpb - 1 - p.window_left);
+      float mx = -INFINITY;
+#pragma unroll
+      for (int c = 0; c < 2; ++c)
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          float x = __uint_as_float(sr[c][i]) * c1;
+          if (p.softcap > 0.f) x = accurate_tanh(x) * c2;
+          if (need_mask) {
+            const int key = pos0 + c * 32 + i;
+            bool vis = key < kv_end && (!p.causal || key <= diag);
+            if (p.window_left >= 0) vis = vis && key >= diag - p.window_left;
+            if (!vis) x = -INFINITY;
+          }
+          sr[c][i] = __float_as_uint(x);
+          mx = fmaxf(mx, x);
+        }
+      // Lazy rescale: the exponent base only moves when the row max outruns it
+      // by more than kRescaleThreshold, so O in tensor memory is rarely touched.
+      float alpha = 1.f;
+      if (mx > m_used + kRescaleThreshold || (m_used == -INFINITY && mx > -INFINITY)) {
+        alpha = fast_exp2(m_used - mx);  // 0 when m_used was -inf
+        m_used = mx;
+      }
+      const float base = m_used == -INFINITY ? 0.f : m_used;
+      float sum = 0.f;
+      uint32_t packed[32];
+#pragma unroll
+      for (int c = 0; c < 2; ++c)
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          const float p0 = fast_exp2(__uint_as_float(sr[c][i]) - base);
+          const float p1 = fast_exp2(__uint_as_float(sr[c][i + 1]) - base);
+          sum += p0 + p1;
+          packed[c * 16 + (i >> 1)] = pack_bf16(p0, p1);
+        }
+      l_run = l_run * alpha + sum;
+
+      // P and O may only be touched once the previous PV MMA has drained.
+      if (j > 0 && !mbar_wait_bounded(&bars->pv_done, (j - 1) & 1, abort_flag)) {
+        ok = false;
+        break;
+      }
+      if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
+        tc_fence_after();
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint32_t o[32];
+          tmem_ld32(tmem + lane_addr + c * 32, o);
+          tmem_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+          tmem_st32(tmem + lane_addr + c * 32, o);
+        }
+        tmem_wait_st();
+      }
+      // P as the K-major, 128-byte swizzled A operand: row `row`, 8 chunks of 16 B.
+      {
+        uint8_t* prow = smem + kSmemP + row * 128;
+#pragma unroll
+        for (int c = 0; c < 8; ++c)
+          *reinterpret_cast<uint4*>(prow + ((c ^ (row & 7)) << 4)) =
+              make_uint4(packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
+      }
+      // Last tile: keys past the valid length may hold anything (NaN included);
+      // their P is 0, so their V rows must be finite: zero them.
+      if (pos0 + kBN > kv_end) {
+        if (!mbar_wait_bounded(&bars->v_full[s], (j / kKvStages) & 1, abort_flag)) {
+          ok = false;
+          break;
+        }
+        const int first_bad = kv_end - pos0;  // in [1, 63]
+        uint8_t* vbase = smem + kSmemV + s * 16384;
+        for (int idx = threadIdx.x - 64; idx < (kBN - first_bad) * 16; idx += 128) {
+          const int r = first_bad + idx / 16, c = idx % 16;
+          *reinterpret_cast<uint4*>(vbase + (c >> 3) * 8192 + r * 128 + (((c & 7) ^ (r & 7)) << 4)) =
+              make_uint4(0u, 0u, 0u, 0u);
+        }
+      }
+      fence_proxy_async_smem();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars->p_full);
+    }
+
+    // ---- epilogue: O / l -> bf16, lse
+    if (ok && n_tiles > 0) ok = mbar_wait_bounded(&bars->pv_done, (n_tiles - 1) & 1, abort_flag);
+    if (ok) {
+      tc_fence_after();
+      const int hq = h * p.group + min(g, p.group - 1);
+      const float sink2 = p.sinks ? p.sinks[hq] * kLog2e : -INFINITY;
+      const float m_all = fmaxf(m_used, sink2);
+      float out_scale = 0.f, lse = -INFINITY;
+      if (m_all != -INFINITY) {
+        const float w_keys = m_used == -INFINITY ? 0.f : fast_exp2(m_used - m_all);
+        const float den = l_run * w_keys + (sink2 == -INFINITY ? 0.f : fast_exp2(sink2 - m_all));
+        if (den > 0.f) {
+          out_scale = w_keys * (p.v_descale ? *p.v_descale : 1.0f) / den;
+          lse = (m_all + log2f(den)) * kLn2;
+        }
+      }
+      __nv_bfloat16* orow = p.out + (static_cast<long long>(q_row0) + tl) * p.tok_stride +
+                            static_cast<long long>(hq) * p.head_stride;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t o[32];
+        if (n_tiles > 0) {
+          tmem_ld32(tmem + lane_addr + c * 32, o);
+          tmem_wait_ld();
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] = 0u;
+        }
+        if (row_ok) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 8) {
+            uint4 v;
+            v.x = pack_bf16(__uint_as_float(o[i]) * out_scale, __uint_as_float(o[i + 1]) * out_scale);
+            v.y = pack_bf16(__uint_as_float(o[i + 2]) * out_scale, __uint_as_float(o[i + 3]) * out_scale);
+            v.z = pack_bf16(__uint_as_float(o[i + 4]) * out_scale, __uint_as_float(o[i + 5]) * out_scale);
+            v.w = pack_bf16(__uint_as_float(o[i + 6]) * out_scale, __uint_as_float(o[i + 7]) * out_scale);
+            *reinterpret_cast<uint4*>(orow + c * 32 + i) = v;
+          }
+        }
+      }
+      if (row_ok && p.lse != nullptr) p.lse[static_cast<long long>(hq) * p.total_q + q_row0 + tl] = lse;
+      tc_fence_before();
+    } else if (lane == 0) {
+      *abort_flag = 1;
+      report_status(p.status, FW_STATUS_WAIT_TIMEOUT);
+    }
+  }
+
+  // ---- teardown: everyone meets here, then the allocating warp frees TMEM.
+  __syncthreads();
+  if (warp == 1 && n_tiles > 0) {
+    tc_fence_after();
+    tmem_dealloc(tmem, kTmemCols);
+  }
+}
+
+// ---------------------------------------------------------------- host
+static bool power_of_two(int x) { return x > 0 && (x & (x - 1)) == 0; }
+
+bool tcgen05_prefill_supported(const FwPrefillArgs* a) {
+  if (a->kv_dtype != FW_DTYPE_BF16 || a->head_dim != 128) return false;
+  if (a->nheads_k <= 0 || a->nheads % a->nheads_k) return false;
+  const int group = a->nheads / a->nheads_k;
+  if (!power_of_two(group) || group > 16) return false;  // 128 rows = (128 / group) tokens x group heads
+  if (a->page_size <= 0 || a->page_size % kBN) return false;
+  if (a->batch > 2048) return false;
+  return true;
+}
+
+static int tc05_max_items(const FwPrefillArgs* a) {
+  const int tpb = kBM / (a->nheads / a->nheads_k);
+  return (a->total_q + tpb - 1) / tpb + a->batch;
+}
+
+uint64_t tcgen05_prefill_workspace_bytes(const FwPrefillArgs* a) {
+  return 256 + static_cast<uint64_t>(tc05_max_items(a)) * 8 * sizeof(int);
+}
+
+int tcgen05_prefill(const FwPrefillArgs* a, cudaStream_t stream) {
+  if (a->q == nullptr || a->out == nullptr || a->kv_cache == nullptr || a->cu_seqlens_q == nullptr ||
+      a->seqused_k == nullptr || a->block_table == nullptr) {
+    set_error("q, out, kv_cache, cu_seqlens_q, seqused_k and block_table must not be NULL.");
+    return FW_ERR_BAD_SHAPE;
+  }
+  const uint64_t need = tcgen05_prefill_workspace_bytes(a);
+  if (a->workspace == nullptr || a->workspace_bytes < need || (reinterpret_cast<uintptr_t>(a->workspace) & 255)) {
+    set_error("workspace must be 256-byte aligned and hold %llu bytes; got %llu.",
+              static_cast<unsigned long long>(need), static_cast<unsigned long long>(a->workspace_bytes));
+    return FW_ERR_WORKSPACE;
+  }
+  if ((reinterpret_cast<uintptr_t>(a->kv_cache) & 15) || (reinterpret_cast<uintptr_t>(a->q) & 15) ||
+      (reinterpret_cast<uintptr_t>(a->out) & 15)) {
+    set_error("q, out and the cache must be 16-byte aligned.");
+    return FW_ERR_BAD_SHAPE;
+  }
+  const int group = a->nheads / a->nheads_k;
+  const int tpb = kBM / group;
+  const int max_items = tc05_max_items(a);
+  Tc05Params p;
+  p.items = reinterpret_cast<int*>(static_cast<uint8_t*>(a->workspace) + 256);
+  p.block_table = a->block_table;
+  p.k_descale = a->k_descale;
+  p.v_descale = a->v_descale;
+  p.sinks = a->sinks;
+  p.out = static_cast<__nv_bfloat16*>(a->out);
+  p.lse = a->lse;
+  p.status = static_cast<int*>(a->workspace);
+  if (a->token_major) {
+    p.tok_stride = static_cast<long long>(a->nheads) * 128;
+    p.head_stride = 128;
+  } else {
+    p.tok_stride = 128;
+    p.head_stride = static_cast<long long>(a->total_q) * 128;
+  }
+  p.num_pages = a->num_pages;
+  p.total_q = a->total_q;
+  p.nheads = a->nheads;
+  p.group = group;
+  p.tpb = tpb;
+  p.page_size = a->page_size;
+  p.pages_per_seq = a->pages_per_seq;
+  p.causal = a->causal != 0;
+  p.window_left = a->window_left;
+  p.scale = a->softmax_scale;
+  p.softcap = a->softcap;
+
+  int rc = launch_prefill_plan(a, tpb, max_items, const_cast<int*>(p.items), p.tok_stride, p.head_stride, stream);
+  if (rc != FW_OK) return rc;
+
+  // q viewed as (head_dim, tokens, heads); a box is 64 elements x tpb tokens of one head.
+  CUtensorMap map_q, map_kv;
+  {
+    const uint64_t dims[3] = {128, static_cast<uint64_t>(a->total_q), static_cast<uint64_t>(a->nheads)};
+    const uint64_t strides[2] = {static_cast<uint64_t>(p.tok_stride) * 2, static_cast<uint64_t>(p.head_stride) * 2};
+    const uint32_t box[3] = {64, static_cast<uint32_t>(tpb), 1};
+    rc = encode_tensor_map_bf16(&map_q, 3, a->q, dims, strides, box);
+    if (rc != FW_OK) return rc;
+  }
+  {
+    // pool viewed as (head_dim, head planes [k0,v0,k1,v1,...], tokens in page, pages)
+    const uint64_t planes = 2ull * a->nheads_k;
+    const uint64_t row_bytes = planes * 256;
+    const uint64_t dims[4] = {128, planes, static_cast<uint64_t>(a->page_size), static_cast<uint64_t>(a->num_pages)};
+    const uint64_t strides[3] = {256, row_bytes, row_bytes * a->page_size};
+    const uint32_t box[4] = {64, 1, kBN, 1};
+    rc = encode_tensor_map_bf16(&map_kv, 4, a->kv_cache, dims, strides, box);
+    if (rc != FW_OK) return rc;
+  }
+  cudaError_t err = cudaFuncSetAttribute(prefill_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         kSmemBytes);
+  if (err != cudaSuccess) {
+    set_error("cudaFuncSetAttribute(%d bytes): %s", kSmemBytes, cudaGetErrorString(err));
+    return FW_ERR_LAUNCH;
+  }
+  dim3 grid(max_items, a->nheads_k);
+  prefill_tcgen05_kernel<<<grid, 192, kSmemBytes, stream>>>(map_q, map_kv, p);
+  err = cudaGetLastError();
+  if (err != cudaSuccess) {
+    set_error("tcgen05 prefill kernel launch: %s", cudaGetErrorString(err));
+    return FW_ERR_LAUNCH;
+  }
+  return FW_OK;
+}
+
+}  // namespace fw

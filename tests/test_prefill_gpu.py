@@ -18,6 +18,14 @@ LSE_TOL = dict(rtol=2e-3, atol=4e-3)
 GOLDEN_DIR = pathlib.Path(cases.__file__).resolve().parent
 
 
+@pytest.fixture(autouse=True, params=["splitkv", "tcgen05"])
+def prefill_kernel(request, monkeypatch):
+    """Every case runs once per prefill kernel; shapes the tensor-core kernel
+    does not take (fp8 pools, odd GQA groups) stay on the split-KV kernel."""
+    monkeypatch.setenv("FLYWHEEL_PREFILL_KERNEL", request.param)
+    return request.param
+
+
 def to_cuda(array):
     import torch
     if array.dtype == oracle.BF16:
