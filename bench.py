@@ -133,6 +133,122 @@ def build_workload(seed, device):
             "kv_bytes": kv_bytes, "pool_pages": pool_pages}
 
 
+PF_BATCH, PF_HQ, PF_HK = 16, 32, 8
+
+
+def build_prefill_workload(seed, device):
+    """Chunked prefill over a paged bf16 cache: 16 requests, cached prefix
+    U[0,16384] in 64-token pages (random block table), new chunk U[512,2048]
+    already written to the pool (seqused_k = prefix + chunk), 32 q heads, 8 kv
+    heads, head_dim 128, causal, head-major q."""
+    import torch
+    from flywheel_tpu.testing import workloads
+    rng = np.random.default_rng(1000 + seed)
+    prefix = rng.integers(0, 16384 + 1, PF_BATCH).astype(np.int32)
+    chunk = rng.integers(512, 2048 + 1, PF_BATCH).astype(np.int32)
+    seqused = (prefix + chunk).astype(np.int32)
+    table, pool_pages = workloads.paged_table(rng, seqused, 0, PAGE, slack=0.10)
+    gen = torch.Generator(device=device)
+    gen.manual_seed(1000 + seed)
+    pool = torch.randn((pool_pages, PAGE, 2 * PF_HK, D), generator=gen, device=device,
+                       dtype=torch.float32).to(torch.bfloat16)
+    cu = np.concatenate(([0], np.cumsum(chunk))).astype(np.int32)
+    total_q = int(cu[-1])
+    q_host = torch.randn((PF_HQ, total_q, D), dtype=torch.float32).to(torch.bfloat16).pin_memory()
+    return {"pool": pool, "q_host": q_host, "q": q_host.to(device), "cu": cu, "seqused": seqused,
+            "table": table, "prefix": prefix, "chunk": chunk, "total_q": total_q,
+            "flops": workloads.prefill_flops(prefix, chunk, PF_HQ, D),
+            "cu_dev": torch.from_numpy(cu).to(device), "seqused_dev": torch.from_numpy(seqused).to(device),
+            "table_dev": torch.from_numpy(table).to(device)}
+
+
+def make_prefill_call(work, device):
+    import torch
+    from flywheel_tpu.softmax_attention import _native
+    out = torch.empty_like(work["q"])
+    args = _native.FwPrefillArgs(
+        q=work["q"].data_ptr(), out=out.data_ptr(), kv_cache=work["pool"].data_ptr(),
+        cu_seqlens_q=work["cu_dev"].data_ptr(), seqused_k=work["seqused_dev"].data_ptr(),
+        block_table=work["table_dev"].data_ptr(), num_pages=work["pool"].shape[0], page_size=PAGE,
+        pages_per_seq=work["table_dev"].shape[1], batch=PF_BATCH, total_q=work["total_q"],
+        max_seqlen_q=int(work["chunk"].max()), nheads=PF_HQ, nheads_k=PF_HK, head_dim=D, kv_dtype=0,
+        causal=1, window_left=-1, softmax_scale=D ** -0.5, softcap=0.0, token_major=0)
+    lib = _native.library()
+    nbytes = lib.fw_prefill_workspace_bytes(ctypes.byref(args))
+    if nbytes == 0:
+        raise RuntimeError(_native.last_error())
+    scratch = torch.zeros(nbytes, dtype=torch.uint8, device=device)
+    args.workspace, args.workspace_bytes = scratch.data_ptr(), nbytes
+    stream = torch.cuda.current_stream(device).cuda_stream
+
+    def call():
+        _native.check(lib.fw_prefill_paged(ctypes.byref(args), stream))
+
+    return call, out, scratch
+
+
+def bench_prefill(ns, device, rank, world, barrier):
+    """Times the chunked-prefill workload; returns the per-rank numbers."""
+    import torch
+    from flywheel_tpu import flash_attn_varlen_func
+    from flywheel_tpu.softmax_attention import _native
+    work = build_prefill_workload(rank, device)
+    call, out, scratch = make_prefill_call(work, device)
+    steps = max(5, min(ns.steps, 30))
+    for _ in range(ns.warmup):
+        call()
+    barrier()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(steps):
+        call()
+    end.record()
+    barrier()
+    ms = start.elapsed_time(end) / steps
+    status = _native.read_status(scratch, device)
+    if status != 0:
+        raise RuntimeError(f"prefill kernel reported device status {status}")
+    e2e_ms = None
+    if not ns.skip_e2e:
+        def e2e_step():
+            result = flash_attn_varlen_func(
+                work["q_host"], work["pool"], None, work["cu"], None, int(work["chunk"].max()),
+                int(work["seqused"].max()), causal=True, block_table=work["table"],
+                seqused_k=work["seqused"])
+            return result          # a host tensor: the API copied it back
+
+        for _ in range(2):
+            e2e_step()
+        barrier()
+        start.record()
+        for _ in range(5):
+            e2e_step()
+        end.record()
+        barrier()
+        e2e_ms = start.elapsed_time(end) / 5
+    check = None
+    if rank == 0 and not ns.skip_cpu_baseline:
+        # spot-check the shortest request against the CPU oracle
+        from flywheel_tpu.softmax_attention import _arrays
+        from oracle import paged_attention as oracle
+        r = int(np.argmin(work["seqused"]))
+        pages = work["table"][r, : -(-int(work["seqused"][r]) // PAGE)]
+        sub_pool = _arrays.to_host_numpy(work["pool"][torch.from_numpy(pages).to(device).long()])
+        lo, hi = int(work["cu"][r]), int(work["cu"][r + 1])
+        q_rows = _arrays.to_host_numpy(work["q_host"][:, lo:hi]).transpose(1, 0, 2)
+        t0 = time.perf_counter()
+        want, _ = oracle.ragged_paged_attention(
+            q_rows, sub_pool, np.array([0, hi - lo]), work["seqused"][r:r + 1],
+            np.arange(len(pages), dtype=np.int32)[None], nheads_k=PF_HK, causal=True)
+        cpu_s = time.perf_counter() - t0
+        got = out[:, lo:hi].float().cpu().numpy().transpose(1, 0, 2)
+        flops_r = 4 * int(work["chunk"][r]) * (int(work["prefix"][r]) + (int(work["chunk"][r]) + 1) / 2) * PF_HQ * D
+        check = {"max_abs_err_vs_cpu": float(np.abs(got - want).max()),
+                 "cpu_tflops": flops_r / cpu_s / 1e12, "cpu_sample": f"request {r} of {PF_BATCH}, {cpu_s:.2f} s"}
+    return {"ms": ms, "flops": work["flops"], "e2e_ms": e2e_ms, "total_q": work["total_q"],
+            "h2d": work["q_host"].numel() * 2, "check": check}
+
+
 def make_decode_call(work, device):
     """A closure that enqueues one decode step through the C ABI on device
     buffers (no host traffic), and the output tensor it fills."""
@@ -243,6 +359,9 @@ def main():
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--skip-cpu-baseline", action="store_true")
     parser.add_argument("--skip-e2e", action="store_true")
+    parser.add_argument("--skip-prefill", action="store_true")
+    parser.add_argument("--prefill-only", action="store_true",
+                        help="run only the chunked-prefill workload (profiler captures)")
     parser.add_argument("--batch", type=int, default=128,
                         help="requests per step; smaller than 128 only for profiler captures")
     ns = parser.parse_args()
@@ -268,6 +387,13 @@ def main():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
+
+    if ns.prefill_only:
+        pf = bench_prefill(ns, device, rank, world, barrier)
+        if rank == 0:
+            print(json.dumps({"metric": "chunked_prefill_tflops", "value": pf["flops"] / (pf["ms"] * 1e-3) / 1e12,
+                              "unit": "TFLOP/s", "ms_per_step": pf["ms"], "n_gpus": world}))
+        return
 
     from flywheel_tpu import flash_attn_with_kvcache
     work = build_workload(seed=rank, device=device)
@@ -299,13 +425,12 @@ def main():
 
     # ---- end-to-end arm: host inputs in, host output back, every step
     host = work["host"]
-    out_host = torch.empty_like(host["q"]).pin_memory()
 
     def e2e_step():
         result, _ = flash_attn_with_kvcache(
             host["q"], work["pool"], None, host["k"], host["v"], cache_seqlens=host["lens"],
             block_table=host["table"], causal=True)
-        out_host.copy_(result)      # device -> pinned host, synchronous
+        return result               # a host tensor: the API copied it device -> host and synchronised
 
     e2e_start, e2e_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     if ns.skip_e2e:
@@ -324,7 +449,7 @@ def main():
         barrier()
         e2e_ms = e2e_start.elapsed_time(e2e_end)
     h2d = sum(host[name].numel() * host[name].element_size() for name in ("q", "k", "v", "lens", "table"))
-    d2h = out_host.numel() * out_host.element_size()
+    d2h = host["q"].numel() * host["q"].element_size()
 
     times = torch.tensor([total_ms, e2e_ms, launch_ms], dtype=torch.float64, device=device)
     nbytes = torch.tensor([float(work["kv_bytes"])], dtype=torch.float64, device=device)
@@ -333,6 +458,16 @@ def main():
         dist.all_reduce(nbytes, op=dist.ReduceOp.SUM)
     total_ms, e2e_ms, launch_ms = (float(x) for x in times.tolist())
     job_bytes = float(nbytes.item())
+
+    prefill = None if ns.skip_prefill else bench_prefill(ns, device, rank, world, barrier)
+    if prefill is not None:
+        pf = torch.tensor([prefill["ms"], prefill["e2e_ms"] or 0.0], dtype=torch.float64, device=device)
+        pf_flops = torch.tensor([float(prefill["flops"])], dtype=torch.float64, device=device)
+        if world > 1:
+            dist.all_reduce(pf, op=dist.ReduceOp.MAX)
+            dist.all_reduce(pf_flops, op=dist.ReduceOp.SUM)
+        prefill["ms"], prefill["e2e_ms"] = float(pf[0]), float(pf[1]) or None
+        prefill["job_flops"] = float(pf_flops.item())
 
     if rank == 0:
         hbm_peak, _, peak_kind = measured_peaks()
@@ -357,6 +492,25 @@ def main():
                          "algorithmic_bytes_per_launch": work["kv_bytes"],
                          "frac_of_nominal_8TBs": achieved / 8000.0},
         }
+        if prefill is not None:
+            _, tf_peak, _ = measured_peaks()
+            tflops = prefill["job_flops"] / (prefill["ms"] * 1e-3) / 1e12
+            per_gpu = tflops / world
+            line["prefill"] = {
+                "metric": "chunked_prefill_tflops", "value": tflops, "unit": "TFLOP/s", "per_gpu": per_gpu,
+                "ms_per_step": prefill["ms"],
+                "config": {"workload": "chunked prefill over a paged bf16 cache, 16 requests, prefix U[0,16384], "
+                                       "chunk U[512,2048], 32 q heads, 8 kv heads, head_dim 128, page 64, "
+                                       "causal, head-major q", "total_q": prefill["total_q"]},
+                "e2e": {"value": prefill["job_flops"] / (prefill["e2e_ms"] * 1e-3) / 1e12 if prefill["e2e_ms"]
+                        else None, "unit": "TFLOP/s", "h2d_bytes_per_step": prefill["h2d"],
+                        "d2h_bytes_per_step": prefill["h2d"], "ms_per_step": prefill["e2e_ms"]},
+                "roofline": {"bound": "tensor", "achieved": per_gpu, "peak": tf_peak, "unit": "TFLOP/s",
+                             "frac": per_gpu / tf_peak, "peak_kind": f"of {peak_kind} (bf16 burst)",
+                             "frac_of_nominal_2250": per_gpu / 2250.0,
+                             "algorithmic_flops_per_launch": prefill["flops"]},
+                "check": prefill["check"],
+            }
         if world == 1 and not ns.skip_cpu_baseline:
             base, cpu_out, count = cpu_baseline(work)
             line["cpu_baseline"] = base

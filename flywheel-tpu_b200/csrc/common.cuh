@@ -64,9 +64,10 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
   if (mbar_try_wait(bar, parity)) return true;
   for (uint32_t spin = 0; spin < kWaitSpinLimit; ++spin) {
     if (mbar_try_wait(bar, parity)) return true;
-    if (spin > 64) {
-      if (*abort_flag) return false;
-      __nanosleep(spin > 4096 ? 256 : 32);
+    // A sleeping warp leaves its issue slots to the warps that compute.
+    if (spin > 8) {
+      if ((spin & 63) == 0 && *abort_flag) return false;
+      __nanosleep(spin > 4096 ? 256 : 24);
     }
   }
   return false;

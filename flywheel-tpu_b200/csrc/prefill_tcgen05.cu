@@ -17,6 +17,8 @@
 // softmax with lazy rescale, P written to shared memory as the A operand of
 // the PV MMA).  Two CTAs share an SM (~112 KiB shared memory, 256 TMEM columns
 // each), so one CTA's softmax overlaps the other's MMAs.
+#include <climits>
+
 #include "common.cuh"
 
 namespace fw {
@@ -129,6 +131,39 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes,
 __host__ __device__ constexpr uint32_t instr_desc(int n, bool b_mn_major) {
   return (1u << 4) | (1u << 7) | (1u << 10) | (b_mn_major ? (1u << 16) : 0u) |
          (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(kBM >> 4) << 24);
+}
+
+// Pass 1 of the softmax over one 64-key row: optional softcap (scores become
+// log2-unit logits in place), optional mask (-inf in place), returns the row
+// max of what is left in `sr` (raw scores without a softcap).
+template <bool kSoftcap, bool kMask>
+__device__ __forceinline__ float transform_row(uint32_t (&sr)[2][32], float c1, float c2, int pos0, int kv_end,
+                                               int diag, int causal, int window_left) {
+  float mx0 = -INFINITY, mx1 = -INFINITY;
+  const int hi = causal ? min(kv_end - 1, diag) : kv_end - 1;        // last visible key
+  const int lo = window_left >= 0 ? diag - window_left : INT_MIN;    // first visible key
+#pragma unroll
+  for (int c = 0; c < 2; ++c)
+#pragma unroll
+    for (int i = 0; i < 32; i += 2) {
+      float x0 = __uint_as_float(sr[c][i]), x1 = __uint_as_float(sr[c][i + 1]);
+      if constexpr (kSoftcap) {
+        x0 = accurate_tanh(x0 * c1) * c2;
+        x1 = accurate_tanh(x1 * c1) * c2;
+      }
+      if constexpr (kMask) {
+        const int key = pos0 + c * 32 + i;
+        if (key < lo || key > hi) x0 = -INFINITY;
+        if (key + 1 < lo || key + 1 > hi) x1 = -INFINITY;
+      }
+      if constexpr (kSoftcap || kMask) {
+        sr[c][i] = __float_as_uint(x0);
+        sr[c][i + 1] = __float_as_uint(x1);
+      }
+      mx0 = fmaxf(mx0, x0);
+      mx1 = fmaxf(mx1, x1);
+    }
+  return fmaxf(mx0, mx1);
 }
 
 struct Bars {
@@ -307,22 +342,18 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 
       const bool need_mask = pos0 + kBN > min(diag_base, kv_end) ||
                              (p.window_left >= 0 && pos0 < diag_base + p.tpb - 1 - p.window_left);
-      float mx = -INFINITY;
-#pragma unroll
-      for (int c = 0; c < 2; ++c)
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float x = __uint_as_float(sr[c][i]) * c1;
-          if (p.softcap > 0.f) x = accurate_tanh(x) * c2;
-          if (need_mask) {
-            const int key = pos0 + c * 32 + i;
-            bool vis = key < kv_end && (!p.causal || key <= diag);
-            if (p.window_left >= 0) vis = vis && key >= diag - p.window_left;
-            if (!vis) x = -INFINITY;
-          }
-          sr[c][i] = __float_as_uint(x);
-          mx = fmaxf(mx, x);
-        }
+      // Pass 1 (warp-uniform variants): softcap transform, mask, row max.
+      // Without a softcap the raw scores stay in place and the scale rides in
+      // the exponent's FMA (c1 > 0, so the max commutes with the scale).
+      float mx;
+      if (p.softcap > 0.f) {
+        mx = need_mask ? transform_row<true, true>(sr, c1, c2, pos0, kv_end, diag, p.causal, p.window_left)
+                       : transform_row<true, false>(sr, c1, c2, pos0, kv_end, diag, p.causal, p.window_left);
+      } else {
+        mx = need_mask ? transform_row<false, true>(sr, c1, c2, pos0, kv_end, diag, p.causal, p.window_left)
+                       : transform_row<false, false>(sr, c1, c2, pos0, kv_end, diag, p.causal, p.window_left);
+        mx *= c1;
+      }
       // Lazy rescale: the exponent base only moves when the row max outruns it
       // by more than kRescaleThreshold, so O in tensor memory is rarely touched.
       float alpha = 1.f;
@@ -330,18 +361,21 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         alpha = fast_exp2(m_used - mx);  // 0 when m_used was -inf
         m_used = mx;
       }
-      const float base = m_used == -INFINITY ? 0.f : m_used;
-      float sum = 0.f;
+      const float neg_base = m_used == -INFINITY ? 0.f : -m_used;
+      const float mul = p.softcap > 0.f ? 1.0f : c1;
+      float sum0 = 0.f, sum1 = 0.f;
       uint32_t packed[32];
 #pragma unroll
       for (int c = 0; c < 2; ++c)
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
-          const float p0 = fast_exp2(__uint_as_float(sr[c][i]) - base);
-          const float p1 = fast_exp2(__uint_as_float(sr[c][i + 1]) - base);
-          sum += p0 + p1;
+          const float p0 = fast_exp2(fmaf(__uint_as_float(sr[c][i]), mul, neg_base));
+          const float p1 = fast_exp2(fmaf(__uint_as_float(sr[c][i + 1]), mul, neg_base));
+          sum0 += p0;
+          sum1 += p1;
           packed[c * 16 + (i >> 1)] = pack_bf16(p0, p1);
         }
+      const float sum = sum0 + sum1;
       l_run = l_run * alpha + sum;
 
       // P and O may only be touched once the previous PV MMA has drained.
@@ -457,6 +491,7 @@ bool tcgen05_prefill_supported(const FwPrefillArgs* a) {
   if (!power_of_two(group) || group > 16) return false;  // 128 rows = (128 / group) tokens x group heads
   if (a->page_size <= 0 || a->page_size % kBN) return false;
   if (a->batch > 2048) return false;
+  if (!(a->softmax_scale > 0.f)) return false;  // the row max is taken before scaling
   return true;
 }
 

@@ -131,7 +131,15 @@ def to_host_numpy(tensor: torch.Tensor) -> np.ndarray:
 def like(result: torch.Tensor, template):
     """`result` (a CUDA tensor) in the array kind of `template`."""
     if isinstance(template, torch.Tensor):
-        return result if template.is_cuda else result.cpu()
+        if template.is_cuda:
+            return result
+        if template.is_pinned():
+            # a pinned caller gets a pinned result: one DMA, no staging copy
+            host = torch.empty(result.shape, dtype=result.dtype, pin_memory=True)
+            host.copy_(result, non_blocking=True)
+            torch.cuda.current_stream(result.device).synchronize()
+            return host
+        return result.cpu()
     if isinstance(template, (np.ndarray, np.generic)):
         return to_host_numpy(result)
     if hasattr(template, "__dlpack__"):
