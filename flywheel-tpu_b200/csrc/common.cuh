@@ -65,9 +65,11 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
   for (uint32_t spin = 0; spin < kWaitSpinLimit; ++spin) {
     if (mbar_try_wait(bar, parity)) return true;
     // A sleeping warp leaves its issue slots to the warps that compute.
-    if (spin > 8) {
+    // try_wait already parks the thread for a hardware time slice; back off
+    // further only when the wait is clearly a long one.
+    if (spin > 512) {
       if ((spin & 63) == 0 && *abort_flag) return false;
-      __nanosleep(spin > 4096 ? 256 : 24);
+      __nanosleep(spin > 8192 ? 256 : 32);
     }
   }
   return false;

@@ -14,9 +14,9 @@
 // 64-key tiles (one 64-token page, or a 64-token slice of a larger page).
 // Warp roles: warp 0 issues TMA, warp 1 owns tensor memory and issues the MMAs,
 // warps 2-5 are the softmax group (one thread per row: tcgen05.ld of S, online
-// softmax with lazy rescale, P written to shared memory as the A operand of
-// the PV MMA).  Two CTAs share an SM (~112 KiB shared memory, 256 TMEM columns
-// each), so one CTA's softmax overlaps the other's MMAs.
+// softmax with lazy rescale, P written back over S in tensor memory as the A
+// operand of the PV MMA).  Two CTAs share an SM (~96 KiB shared memory, 256
+// TMEM columns each), so one CTA's softmax overlaps the other's MMAs.
 #include <climits>
 
 #include "common.cuh"
@@ -32,8 +32,7 @@ constexpr float kRescaleThreshold = 8.0f;  // log2 units a row max may drift bef
 constexpr int kSmemQ = 0;                      // 2 halves x [128 rows][128 B]
 constexpr int kSmemK = 32768;                  // stages x 2 halves x [64 keys][128 B]
 constexpr int kSmemV = kSmemK + kKvStages * 16384;
-constexpr int kSmemP = kSmemV + kKvStages * 16384;  // [128 rows][128 B]
-constexpr int kSmemBar = kSmemP + 16384;
+constexpr int kSmemBar = kSmemV + kKvStages * 16384;
 constexpr int kSmemBytes = kSmemBar + 256;
 
 struct Tc05Params {
@@ -73,6 +72,18 @@ __device__ __forceinline__ void tc_fence_after() {
 __device__ __forceinline__ void tc_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
                : "memory");
+}
+// D(tmem) (+)= A(tmem) * B(smem): A is 128 lanes x (K/2) 32-bit columns of packed bf16.
+__device__ __forceinline__ void tc_mma_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc,
+                                          uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t"
+      "}\n" ::"r"(tmem_d),
+      "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
 }
 // D(tmem) (+)= A(smem) * B(smem), bf16 operands, f32 accumulate.
 __device__ __forceinline__ void tc_mma(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
@@ -169,7 +180,7 @@ __device__ __forceinline__ float transform_row(uint32_t (&sr)[2][32], float c1, 
 struct Bars {
   uint64_t q_full;
   uint64_t k_full[kKvStages], v_full[kKvStages], kv_empty[kKvStages];
-  uint64_t s_full[2], s_empty[2];
+  uint64_t s_full[2];
   uint64_t p_full, pv_done;
   uint32_t tmem_base;
   int abort_flag;
@@ -204,7 +215,6 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     }
     for (int s = 0; s < 2; ++s) {
       mbar_init(&bars->s_full[s], 1);
-      mbar_init(&bars->s_empty[s], 4);
     }
     mbar_init(&bars->p_full, 4);
     mbar_init(&bars->pv_done, 1);
@@ -265,7 +275,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     if (lane == 0) {
       constexpr uint32_t idesc_qk = instr_desc(kBN, false);
       constexpr uint32_t idesc_pv = instr_desc(128, true);
-      const uint32_t q_addr = smem_u32(smem + kSmemQ), p_addr = smem_u32(smem + kSmemP);
+      const uint32_t q_addr = smem_u32(smem + kSmemQ);
       bool ok = mbar_wait_bounded(&bars->q_full, 0, abort_flag);
       auto issue_qk = [&](int j) {
         const int s = j % kKvStages, sb = j & 1;
@@ -288,8 +298,9 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         if (j + 1 < n_tiles) {
           const int s1 = (j + 1) % kKvStages, sb1 = (j + 1) & 1;
           ok = mbar_wait_bounded(&bars->k_full[s1], ((j + 1) / kKvStages) & 1, abort_flag);
-          // S buffer sb1 was last read by the softmax of tile j - 1.
-          if (ok && j >= 1) ok = mbar_wait_bounded(&bars->s_empty[sb1], ((j - 1) >> 1) & 1, abort_flag);
+          // S buffer sb1 held S(j-1) and then P(j-1); PV(j-1), issued in the
+          // previous iteration after p_full(j-1), is ahead of this MMA in the
+          // tensor pipe, so the overwrite is ordered behind its reads.
           if (!ok) break;
           issue_qk(j + 1);
         }
@@ -300,7 +311,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         const uint32_t v_addr = smem_u32(smem + kSmemV + s * 16384);
 #pragma unroll
         for (int k = 0; k < 4; ++k)
-          tc_mma(tmem, smem_desc(p_addr + k * 32, 16, 1024), smem_desc(v_addr + k * 2048, 8192, 1024), idesc_pv,
+          tc_mma_ts(tmem, tmem + 128 + (j & 1) * 64 + k * 8, smem_desc(v_addr + k * 2048, 8192, 1024), idesc_pv,
                  (j > 0 || k > 0) ? 1u : 0u);
         tc_commit(&bars->kv_empty[s]);
         tc_commit(&bars->pv_done);
@@ -336,9 +347,6 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       tmem_ld32(tmem + lane_addr + 128 + sb * 64, sr[0]);
       tmem_ld32(tmem + lane_addr + 128 + sb * 64 + 32, sr[1]);
       tmem_wait_ld();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&bars->s_empty[sb]);
 
       const bool need_mask = pos0 + kBN > min(diag_base, kv_end) ||
                              (p.window_left >= 0 && pos0 < diag_base + p.tpb - 1 - p.window_left);
@@ -378,12 +386,12 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       const float sum = sum0 + sum1;
       l_run = l_run * alpha + sum;
 
-      // P and O may only be touched once the previous PV MMA has drained.
-      if (j > 0 && !mbar_wait_bounded(&bars->pv_done, (j - 1) & 1, abort_flag)) {
-        ok = false;
-        break;
-      }
+      // O may only be touched once the previous PV MMA has drained (rare path).
       if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
+        if (!mbar_wait_bounded(&bars->pv_done, (j - 1) & 1, abort_flag)) {
+          ok = false;
+          break;
+        }
         tc_fence_after();
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
@@ -396,14 +404,11 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         }
         tmem_wait_st();
       }
-      // P as the K-major, 128-byte swizzled A operand: row `row`, 8 chunks of 16 B.
-      {
-        uint8_t* prow = smem + kSmemP + row * 128;
-#pragma unroll
-        for (int c = 0; c < 8; ++c)
-          *reinterpret_cast<uint4*>(prow + ((c ^ (row & 7)) << 4)) =
-              make_uint4(packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
-      }
+      // P overwrites the first 32 columns of this tile's S buffer in tensor
+      // memory: row = lane, two bf16 keys per 32-bit column, the A operand of
+      // the PV MMA.  (This thread already holds its S row in registers.)
+      tmem_st32(tmem + lane_addr + 128 + sb * 64, packed);
+      tmem_wait_st();
       // Last tile: keys past the valid length may hold anything (NaN included);
       // their P is 0, so their V rows must be finite: zero them.
       if (pos0 + kBN > kv_end) {
@@ -426,6 +431,11 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     }
 
     // ---- epilogue: O / l -> bf16, lse
+    // pv_done completes once per tile, and only the rescale path waits on it
+    // inside the loop, so up to two phases can still be open here: S(n-1) being
+    // ready only proves PV(n-3) done.  Wait for them in order (a parity wait
+    // is only meaningful for the phase that is currently open).
+    if (ok && n_tiles > 1) ok = mbar_wait_bounded(&bars->pv_done, (n_tiles - 2) & 1, abort_flag);
     if (ok && n_tiles > 0) ok = mbar_wait_bounded(&bars->pv_done, (n_tiles - 1) & 1, abort_flag);
     if (ok) {
       tc_fence_after();
