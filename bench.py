@@ -205,9 +205,10 @@ def bench_prefill(ns, device, rank, world, barrier):
     end.record()
     barrier()
     ms = start.elapsed_time(end) / steps
+    status_words = scratch[:16].view(torch.int32).cpu().tolist()
     status = _native.read_status(scratch, device)
     if status != 0:
-        raise RuntimeError(f"prefill kernel reported device status {status}")
+        raise RuntimeError(f"prefill kernel reported device status {status} (words {status_words})")
     e2e_ms = None
     if not ns.skip_e2e:
         def e2e_step():

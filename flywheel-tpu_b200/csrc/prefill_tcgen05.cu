@@ -8,15 +8,16 @@
 // mask per packed request, softcap before masking, sinks in the denominator,
 // out 0 / lse -inf for padding rows.  Fully masked KV tiles are never loaded.
 //
-// One CTA = one query block of one KV head: 128 rows = (128 / group) tokens x
-// the `group` query heads that share the KV head (rows ordered head-major), so
-// every K/V tile is fetched once for the whole GQA group.  KV advances in
-// 64-key tiles (one 64-token page, or a 64-token slice of a larger page).
-// Warp roles: warp 0 issues TMA, warp 1 owns tensor memory and issues the MMAs,
-// warps 2-5 are the softmax group (one thread per row: tcgen05.ld of S, online
-// softmax with lazy rescale, P written back over S in tensor memory as the A
-// operand of the PV MMA).  Two CTAs share an SM (~96 KiB shared memory, 256
-// TMEM columns each), so one CTA's softmax overlaps the other's MMAs.
+// One CTA = one query block of one KV head: two "streams" of 128 rows, each
+// (128 / group) tokens x the `group` query heads that share the KV head (rows
+// ordered head-major), so every K/V tile is fetched from L2 once per 256 query
+// rows.  KV advances in 64-key tiles (one 64-token page, or a 64-token slice
+// of a larger page) through a 4-stage TMA ring.  Warp roles: warp 0 issues
+// TMA, warp 1 owns tensor memory and issues the MMAs of both streams, warps
+// 2-5 and 6-9 are the two softmax groups (one thread per row: tcgen05.ld of
+// S, online softmax with lazy rescale, P written back over S in tensor memory
+// as the A operand of the PV MMA), so one stream's softmax overlaps the other
+// stream's MMAs.  One CTA per SM (192 KiB shared memory, all 512 TMEM columns).
 #include <climits>
 
 #include "common.cuh"
@@ -25,12 +26,13 @@ namespace fw {
 
 constexpr int kBM = 128;       // query rows per CTA
 constexpr int kBN = 64;        // keys per KV tile
-constexpr int kKvStages = 2;
-constexpr int kTmemCols = 256; // O: [0,128), S double buffer: [128,192), [192,256)
+constexpr int kStreams = 2;     // 128-row query tiles per CTA, one softmax warp group each
+constexpr int kKvStages = 4;
+constexpr int kTmemCols = 512;  // per stream: O 128 columns, S / P double buffer 2 x 64
 constexpr float kRescaleThreshold = 8.0f;  // log2 units a row max may drift before O is rescaled
 
-constexpr int kSmemQ = 0;                      // 2 halves x [128 rows][128 B]
-constexpr int kSmemK = 32768;                  // stages x 2 halves x [64 keys][128 B]
+constexpr int kSmemQ = 0;                      // streams x 2 halves x [128 rows][128 B]
+constexpr int kSmemK = kStreams * 32768;       // stages x 2 halves x [64 keys][128 B]
 constexpr int kSmemV = kSmemK + kKvStages * 16384;
 constexpr int kSmemBar = kSmemV + kKvStages * 16384;
 constexpr int kSmemBytes = kSmemBar + 256;
@@ -177,16 +179,32 @@ __device__ __forceinline__ float transform_row(uint32_t (&sr)[2][32], float c1, 
   return fmaxf(mx0, mx1);
 }
 
+// First waiter that gives up leaves where it was: status[1] = wait site,
+// status[2] = tile index, status[3] = item | kv head << 20.
+__device__ __forceinline__ void record_timeout(int* status, int site, int j) {
+  if (status != nullptr && atomicCAS(status + 1, 0, site) == 0) {
+    status[2] = j;
+    status[3] = static_cast<int>(blockIdx.x | (blockIdx.y << 20));
+  }
+}
+
 struct Bars {
   uint64_t q_full;
   uint64_t k_full[kKvStages], v_full[kKvStages], kv_empty[kKvStages];
-  uint64_t s_full[2];
-  uint64_t p_full, pv_done;
+  uint64_t s_full[kStreams][2];
+  uint64_t p_full[kStreams][2], pv_done[kStreams];
   uint32_t tmem_base;
   int abort_flag;
 };
 
-__global__ void __launch_bounds__(192, 2)
+// Tensor-memory columns of stream t: O at [256 t, 256 t + 128), the two S / P
+// buffers at 256 t + 128 + 64 sb.
+__device__ __forceinline__ uint32_t tmem_o(uint32_t base, int t) { return base + t * 256; }
+__device__ __forceinline__ uint32_t tmem_s(uint32_t base, int t, int sb) { return base + t * 256 + 128 + sb * 64; }
+
+#define FW_WAIT(site, j, bar, parity) (mbar_wait_bounded(bar, parity, abort_flag) || (record_timeout(p.status, site, j), false))
+
+__global__ void __launch_bounds__(64 + kStreams * 128, 1)
 prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv,
                        const Tc05Params p) {
   extern __shared__ __align__(1024) uint8_t smem[];
@@ -195,12 +213,18 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int item = blockIdx.x, h = blockIdx.y;
 
+  // An item is up to kStreams * tpb query tokens of one request; stream t owns
+  // tokens [t * tpb, (t + 1) * tpb) x the `group` heads of KV head h.
   const int4 it = *reinterpret_cast<const int4*>(p.items + 8 * item);
   const int req = it.x, q_row0 = it.y, q_valid = it.z, anchor = it.w;
   const int kv_limit = p.items[8 * item + 4];
   const int kv_end = p.causal ? min(anchor, kv_limit) : kv_limit;
   if (q_valid <= 0) return;  // uniform across the CTA: nothing allocated yet
-  const int diag_base = anchor - p.tpb;  // token t of the block sits on diagonal diag_base + t
+  // Once any CTA has reported a failed wait the launch is void: later CTAs
+  // leave at once instead of each running into its own time limit.
+  if (p.status != nullptr && *reinterpret_cast<volatile int*>(p.status) != FW_STATUS_OK) return;
+  const int n_streams = q_valid > p.tpb ? kStreams : 1;
+  const int diag_base = anchor - kStreams * p.tpb;  // token t of the item sits on diagonal diag_base + t
   const int first_key = p.window_left >= 0 ? max(0, diag_base - p.window_left) : 0;
   const int tile_lo = first_key / kBN;
   const int tile_hi = kv_end > 0 ? (kv_end + kBN - 1) / kBN : 0;  // exclusive
@@ -213,11 +237,13 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       mbar_init(&bars->v_full[s], 1);
       mbar_init(&bars->kv_empty[s], 1);
     }
-    for (int s = 0; s < 2; ++s) {
-      mbar_init(&bars->s_full[s], 1);
+    for (int t = 0; t < kStreams; ++t) {
+      mbar_init(&bars->s_full[t][0], 1);
+      mbar_init(&bars->s_full[t][1], 1);
+      mbar_init(&bars->p_full[t][0], 4);
+      mbar_init(&bars->p_full[t][1], 4);
+      mbar_init(&bars->pv_done[t], 1);
     }
-    mbar_init(&bars->p_full, 4);
-    mbar_init(&bars->pv_done, 1);
     bars->abort_flag = 0;
     fence_barrier_init();
   }
@@ -235,16 +261,17 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     if (lane == 0) {
       tma_prefetch_desc(&map_q);
       tma_prefetch_desc(&map_kv);
-      mbar_arrive_expect_tx(&bars->q_full, kBM * 256);
-      for (int g = 0; g < p.group; ++g)
-        for (int half = 0; half < 2; ++half)
-          tma_load_3d(smem + kSmemQ + half * 16384 + g * p.tpb * 128, &map_q, &bars->q_full, half * 64, q_row0,
-                      h * p.group + g);
+      mbar_arrive_expect_tx(&bars->q_full, n_streams * kBM * 256);
+      for (int t = 0; t < n_streams; ++t)
+        for (int g = 0; g < p.group; ++g)
+          for (int half = 0; half < 2; ++half)
+            tma_load_3d(smem + kSmemQ + t * 32768 + half * 16384 + g * p.tpb * 128, &map_q, &bars->q_full,
+                        half * 64, q_row0 + t * p.tpb, h * p.group + g);
       bool ok = true;
       for (int j = 0; j < n_tiles && ok; ++j) {
         const int s = j % kKvStages;
         const uint32_t round = j / kKvStages;
-        if (!mbar_wait_bounded(&bars->kv_empty[s], (round & 1) ^ 1, abort_flag)) {
+        if (!FW_WAIT(1, j, &bars->kv_empty[s], (round & 1) ^ 1)) {
           ok = false;
           break;
         }
@@ -275,59 +302,70 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     if (lane == 0) {
       constexpr uint32_t idesc_qk = instr_desc(kBN, false);
       constexpr uint32_t idesc_pv = instr_desc(128, true);
-      const uint32_t q_addr = smem_u32(smem + kSmemQ);
-      bool ok = mbar_wait_bounded(&bars->q_full, 0, abort_flag);
-      auto issue_qk = [&](int j) {
+      bool ok = FW_WAIT(2, 0, &bars->q_full, 0);
+      auto issue_qk = [&](int t, int j) {
         const int s = j % kKvStages, sb = j & 1;
+        const uint32_t q_addr = smem_u32(smem + kSmemQ + t * 32768);
         const uint32_t k_addr = smem_u32(smem + kSmemK + s * 16384);
-        tc_fence_after();
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
           const uint32_t off = (k >> 2) * 16384 + (k & 3) * 32;
           const uint32_t koff = (k >> 2) * 8192 + (k & 3) * 32;
-          tc_mma(tmem + 128 + sb * 64, smem_desc(q_addr + off, 16, 1024), smem_desc(k_addr + koff, 16, 1024),
+          tc_mma(tmem_s(tmem, t, sb), smem_desc(q_addr + off, 16, 1024), smem_desc(k_addr + koff, 16, 1024),
                  idesc_qk, k > 0);
         }
-        tc_commit(&bars->s_full[sb]);
+        tc_commit(&bars->s_full[t][sb]);
       };
-      if (ok) ok = mbar_wait_bounded(&bars->k_full[0], 0, abort_flag);
-      if (ok) issue_qk(0);
+      if (ok) ok = FW_WAIT(3, 0, &bars->k_full[0], 0);
+      if (ok) {
+        tc_fence_after();
+        for (int t = 0; t < n_streams; ++t) issue_qk(t, 0);
+      }
       for (int j = 0; j < n_tiles && ok; ++j) {
         const int s = j % kKvStages;
         const uint32_t round = j / kKvStages;
         if (j + 1 < n_tiles) {
-          const int s1 = (j + 1) % kKvStages, sb1 = (j + 1) & 1;
-          ok = mbar_wait_bounded(&bars->k_full[s1], ((j + 1) / kKvStages) & 1, abort_flag);
-          // S buffer sb1 held S(j-1) and then P(j-1); PV(j-1), issued in the
-          // previous iteration after p_full(j-1), is ahead of this MMA in the
-          // tensor pipe, so the overwrite is ordered behind its reads.
+          ok = FW_WAIT(4, j, &bars->k_full[(j + 1) % kKvStages], ((j + 1) / kKvStages) & 1);
           if (!ok) break;
-          issue_qk(j + 1);
+          // S buffer (j+1)&1 of a stream held S(j-1) and then P(j-1); PV(j-1) was
+          // issued in the previous iteration, so it is ahead of this MMA in the
+          // tensor pipe and the overwrite is ordered behind its reads.
+          tc_fence_after();
+          for (int t = 0; t < n_streams; ++t) issue_qk(t, j + 1);
         }
-        ok = mbar_wait_bounded(&bars->p_full, j & 1, abort_flag);
-        if (ok) ok = mbar_wait_bounded(&bars->v_full[s], round & 1, abort_flag);
-        if (!ok) break;
-        tc_fence_after();
+        ok = FW_WAIT(5, j, &bars->v_full[s], round & 1);
         const uint32_t v_addr = smem_u32(smem + kSmemV + s * 16384);
+        for (int t = 0; t < n_streams && ok; ++t) {
+          // p_full is a two-deep ring like S: a softmax group can finish tile j+1
+          // (its QK was issued above) while this thread still waits for the
+          // other stream's tile j, and a single barrier would then be two
+          // phases ahead of this wait.
+          ok = FW_WAIT(6 + t, j, &bars->p_full[t][j & 1], (j >> 1) & 1);
+          if (!ok) break;
+          tc_fence_after();
 #pragma unroll
-        for (int k = 0; k < 4; ++k)
-          tc_mma_ts(tmem, tmem + 128 + (j & 1) * 64 + k * 8, smem_desc(v_addr + k * 2048, 8192, 1024), idesc_pv,
-                 (j > 0 || k > 0) ? 1u : 0u);
+          for (int k = 0; k < 4; ++k)
+            tc_mma_ts(tmem_o(tmem, t), tmem_s(tmem, t, j & 1) + k * 8, smem_desc(v_addr + k * 2048, 8192, 1024),
+                      idesc_pv, (j > 0 || k > 0) ? 1u : 0u);
+          tc_commit(&bars->pv_done[t]);
+        }
+        if (!ok) break;
         tc_commit(&bars->kv_empty[s]);
-        tc_commit(&bars->pv_done);
       }
       if (!ok) {
         *abort_flag = 1;
         report_status(p.status, FW_STATUS_WAIT_TIMEOUT);
       }
     }
-  } else if (warp >= 2) {
-    // ------------------------------------------------------------ softmax group
+  } else if (warp >= 2 && (warp - 2) / 4 < n_streams) {
+    // ------------------------------------------------------------ softmax groups
+    const int t = (warp - 2) >> 2;           // stream of this warp group
     const int quarter = warp & 3;            // TMEM lane quarter this warp may touch
-    const int row = quarter * 32 + lane;     // row of the 128-row tile
-    const int g = row / p.tpb, tl = row - g * p.tpb;
+    const int row = quarter * 32 + lane;     // row of the stream's 128-row tile
+    const int g = row / p.tpb, tl = t * p.tpb + (row - g * p.tpb);  // head in group, token in item
     const bool row_ok = g < p.group && tl < q_valid;
     const int diag = diag_base + tl;
+    const int diag_lo = diag_base + t * p.tpb, diag_hi = diag_lo + p.tpb - 1;  // this stream's diagonals
     const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
     const float kd = p.k_descale ? *p.k_descale : 1.0f;
     const float c1 = p.softcap > 0.f ? p.scale * kd / p.softcap : p.scale * kd * kLog2e;
@@ -338,18 +376,18 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     for (int j = 0; j < n_tiles && ok; ++j) {
       const int sb = j & 1, s = j % kKvStages;
       const int pos0 = (tile_lo + j) * kBN;
-      if (!mbar_wait_bounded(&bars->s_full[sb], (j >> 1) & 1, abort_flag)) {
+      if (!FW_WAIT(8 + t, j, &bars->s_full[t][sb], (j >> 1) & 1)) {
         ok = false;
         break;
       }
       tc_fence_after();
       uint32_t sr[2][32];
-      tmem_ld32(tmem + lane_addr + 128 + sb * 64, sr[0]);
-      tmem_ld32(tmem + lane_addr + 128 + sb * 64 + 32, sr[1]);
+      tmem_ld32(tmem_s(tmem, t, sb) + lane_addr, sr[0]);
+      tmem_ld32(tmem_s(tmem, t, sb) + lane_addr + 32, sr[1]);
       tmem_wait_ld();
 
-      const bool need_mask = pos0 + kBN > min(diag_base, kv_end) ||
-                             (p.window_left >= 0 && pos0 < diag_base + p.tpb - 1 - p.window_left);
+      const bool need_mask = pos0 + kBN > min(diag_lo, kv_end) ||
+                             (p.window_left >= 0 && pos0 < diag_hi - p.window_left);
       // Pass 1 (warp-uniform variants): softcap transform, mask, row max.
       // Without a softcap the raw scores stay in place and the scale rides in
       // the exponent's FMA (c1 > 0, so the max commutes with the scale).
@@ -383,12 +421,11 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           sum1 += p1;
           packed[c * 16 + (i >> 1)] = pack_bf16(p0, p1);
         }
-      const float sum = sum0 + sum1;
-      l_run = l_run * alpha + sum;
+      l_run = l_run * alpha + (sum0 + sum1);
 
       // O may only be touched once the previous PV MMA has drained (rare path).
       if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
-        if (!mbar_wait_bounded(&bars->pv_done, (j - 1) & 1, abort_flag)) {
+        if (!FW_WAIT(10 + t, j, &bars->pv_done[t], (j - 1) & 1)) {
           ok = false;
           break;
         }
@@ -396,38 +433,39 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
           uint32_t o[32];
-          tmem_ld32(tmem + lane_addr + c * 32, o);
+          tmem_ld32(tmem_o(tmem, t) + lane_addr + c * 32, o);
           tmem_wait_ld();
 #pragma unroll
           for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-          tmem_st32(tmem + lane_addr + c * 32, o);
+          tmem_st32(tmem_o(tmem, t) + lane_addr + c * 32, o);
         }
         tmem_wait_st();
       }
       // P overwrites the first 32 columns of this tile's S buffer in tensor
       // memory: row = lane, two bf16 keys per 32-bit column, the A operand of
       // the PV MMA.  (This thread already holds its S row in registers.)
-      tmem_st32(tmem + lane_addr + 128 + sb * 64, packed);
+      tmem_st32(tmem_s(tmem, t, sb) + lane_addr, packed);
       tmem_wait_st();
       // Last tile: keys past the valid length may hold anything (NaN included);
-      // their P is 0, so their V rows must be finite: zero them.
+      // their P is 0, so their V rows must be finite: zero them.  Both streams
+      // write the same zeros, so neither depends on the other.
       if (pos0 + kBN > kv_end) {
-        if (!mbar_wait_bounded(&bars->v_full[s], (j / kKvStages) & 1, abort_flag)) {
+        if (!FW_WAIT(12 + t, j, &bars->v_full[s], (j / kKvStages) & 1)) {
           ok = false;
           break;
         }
         const int first_bad = kv_end - pos0;  // in [1, 63]
         uint8_t* vbase = smem + kSmemV + s * 16384;
-        for (int idx = threadIdx.x - 64; idx < (kBN - first_bad) * 16; idx += 128) {
+        for (int idx = row; idx < (kBN - first_bad) * 16; idx += 128) {
           const int r = first_bad + idx / 16, c = idx % 16;
           *reinterpret_cast<uint4*>(vbase + (c >> 3) * 8192 + r * 128 + (((c & 7) ^ (r & 7)) << 4)) =
               make_uint4(0u, 0u, 0u, 0u);
         }
+        fence_proxy_async_smem();
       }
-      fence_proxy_async_smem();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&bars->p_full);
+      if (lane == 0) mbar_arrive(&bars->p_full[t][sb]);
     }
 
     // ---- epilogue: O / l -> bf16, lse
@@ -435,8 +473,8 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     // inside the loop, so up to two phases can still be open here: S(n-1) being
     // ready only proves PV(n-3) done.  Wait for them in order (a parity wait
     // is only meaningful for the phase that is currently open).
-    if (ok && n_tiles > 1) ok = mbar_wait_bounded(&bars->pv_done, (n_tiles - 2) & 1, abort_flag);
-    if (ok && n_tiles > 0) ok = mbar_wait_bounded(&bars->pv_done, (n_tiles - 1) & 1, abort_flag);
+    if (ok && n_tiles > 1) ok = FW_WAIT(14 + t, n_tiles - 2, &bars->pv_done[t], (n_tiles - 2) & 1);
+    if (ok && n_tiles > 0) ok = FW_WAIT(16 + t, n_tiles - 1, &bars->pv_done[t], (n_tiles - 1) & 1);
     if (ok) {
       tc_fence_after();
       const int hq = h * p.group + min(g, p.group - 1);
@@ -457,7 +495,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       for (int c = 0; c < 4; ++c) {
         uint32_t o[32];
         if (n_tiles > 0) {
-          tmem_ld32(tmem + lane_addr + c * 32, o);
+          tmem_ld32(tmem_o(tmem, t) + lane_addr + c * 32, o);
           tmem_wait_ld();
         } else {
 #pragma unroll
@@ -506,8 +544,8 @@ bool tcgen05_prefill_supported(const FwPrefillArgs* a) {
 }
 
 static int tc05_max_items(const FwPrefillArgs* a) {
-  const int tpb = kBM / (a->nheads / a->nheads_k);
-  return (a->total_q + tpb - 1) / tpb + a->batch;
+  const int qb = kStreams * (kBM / (a->nheads / a->nheads_k));  // query tokens per CTA
+  return (a->total_q + qb - 1) / qb + a->batch;
 }
 
 uint64_t tcgen05_prefill_workspace_bytes(const FwPrefillArgs* a) {
@@ -562,7 +600,8 @@ int tcgen05_prefill(const FwPrefillArgs* a, cudaStream_t stream) {
   p.scale = a->softmax_scale;
   p.softcap = a->softcap;
 
-  int rc = launch_prefill_plan(a, tpb, max_items, const_cast<int*>(p.items), p.tok_stride, p.head_stride, stream);
+  int rc = launch_prefill_plan(a, kStreams * tpb, max_items, const_cast<int*>(p.items), p.tok_stride,
+                               p.head_stride, stream);
   if (rc != FW_OK) return rc;
 
   // q viewed as (head_dim, tokens, heads); a box is 64 elements x tpb tokens of one head.
@@ -591,7 +630,7 @@ int tcgen05_prefill(const FwPrefillArgs* a, cudaStream_t stream) {
     return FW_ERR_LAUNCH;
   }
   dim3 grid(max_items, a->nheads_k);
-  prefill_tcgen05_kernel<<<grid, 192, kSmemBytes, stream>>>(map_q, map_kv, p);
+  prefill_tcgen05_kernel<<<grid, 64 + kStreams * 128, kSmemBytes, stream>>>(map_q, map_kv, p);
   err = cudaGetLastError();
   if (err != cudaSuccess) {
     set_error("tcgen05 prefill kernel launch: %s", cudaGetErrorString(err));
