@@ -68,6 +68,7 @@ struct MergeParams {
   __nv_bfloat16* out;
   float* lse;
   int parts, rows, nheads, lse_head_stride, lse_token_stride;
+  long long stride_out, stride_lse;
 };
 
 // One warp per (token, head) row; head_dim 128 = 32 lanes x float4.
@@ -78,17 +79,17 @@ __global__ void __launch_bounds__(128) merge_kernel(const MergeParams p) {
   const int head = row % p.nheads, tok = row / p.nheads;
   const float sink = p.sinks ? p.sinks[head] : -INFINITY;
   float top = sink;
-  for (int i = 0; i < p.parts; ++i) top = fmaxf(top, p.partial_lse[static_cast<long long>(i) * p.rows + row]);
+  for (int i = 0; i < p.parts; ++i) top = fmaxf(top, p.partial_lse[i * p.stride_lse + row]);
   float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
   float den = 0.f;
   if (top != -INFINITY) {
     for (int i = 0; i < p.parts; ++i) {
-      const float l = p.partial_lse[static_cast<long long>(i) * p.rows + row];
+      const float l = p.partial_lse[i * p.stride_lse + row];
       if (l == -INFINITY) continue;
       const float w = __expf(l - top);
       den += w;
       const float4 o = *reinterpret_cast<const float4*>(
-          p.partial_out + (static_cast<long long>(i) * p.rows + row) * 128 + lane * 4);
+          p.partial_out + i * p.stride_out + static_cast<long long>(row) * 128 + lane * 4);
       acc.x += o.x * w;
       acc.y += o.y * w;
       acc.z += o.z * w;
@@ -181,7 +182,9 @@ extern "C" int fw_lse_combine(const FwCombineArgs* a, void* stream_ptr) {
   }
   if (a->rows == 0) return FW_OK;
   MergeParams p{a->partial_out, a->partial_lse, a->sinks, static_cast<__nv_bfloat16*>(a->out), a->lse,
-                a->parts, a->rows, a->nheads, a->lse_head_stride, a->lse_token_stride};
+                a->parts, a->rows, a->nheads, a->lse_head_stride, a->lse_token_stride,
+                a->part_stride_out ? a->part_stride_out : static_cast<long long>(a->rows) * 128,
+                a->part_stride_lse ? a->part_stride_lse : static_cast<long long>(a->rows)};
   merge_kernel<<<(a->rows + 3) / 4, 128, 0, static_cast<cudaStream_t>(stream_ptr)>>>(p);
   cudaError_t err = cudaGetLastError();
   if (err != cudaSuccess) {

@@ -75,6 +75,13 @@ __device__ __forceinline__ void tc_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
                : "memory");
 }
+// The MMAs are issued by one thread, so every instruction between two of them
+// is on the tensor pipe's critical path: descriptors are built once per tile
+// and advanced by adding a constant to their address field (low 32 bits never
+// carry: shared addresses stay below 2^18), and the accumulate predicate is
+// only materialised where it is not a constant.
+__device__ __forceinline__ uint64_t desc_advance(uint64_t desc, uint32_t bytes) { return desc + (bytes >> 4); }
+
 // D(tmem) (+)= A(tmem) * B(smem): A is 128 lanes x (K/2) 32-bit columns of packed bf16.
 __device__ __forceinline__ void tc_mma_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc,
                                           uint32_t accumulate) {
@@ -302,25 +309,39 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     if (lane == 0) {
       constexpr uint32_t idesc_qk = instr_desc(kBN, false);
       constexpr uint32_t idesc_pv = instr_desc(128, true);
+      const uint64_t q_desc0 = smem_desc(smem_u32(smem + kSmemQ), 16, 1024);
+      const uint64_t k_desc0 = smem_desc(smem_u32(smem + kSmemK), 16, 1024);
+      const uint64_t v_desc0 = smem_desc(smem_u32(smem + kSmemV), 8192, 1024);
       bool ok = FW_WAIT(2, 0, &bars->q_full, 0);
-      auto issue_qk = [&](int t, int j) {
+      // S(j) of every stream.  The streams' MMAs alternate so that consecutive
+      // instructions accumulate into different tensor-memory tiles.
+      auto issue_qk_all = [&](int j) {
         const int s = j % kKvStages, sb = j & 1;
-        const uint32_t q_addr = smem_u32(smem + kSmemQ + t * 32768);
-        const uint32_t k_addr = smem_u32(smem + kSmemK + s * 16384);
+        const uint64_t k_desc = k_desc0 + static_cast<uint32_t>(s * (16384 >> 4));
+        const uint64_t q_desc1 = q_desc0 + static_cast<uint32_t>(32768 >> 4);
+        const uint32_t d0 = tmem_s(tmem, 0, sb), d1 = tmem_s(tmem, 1, sb);
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
-          const uint32_t off = (k >> 2) * 16384 + (k & 3) * 32;
-          const uint32_t koff = (k >> 2) * 8192 + (k & 3) * 32;
-          tc_mma(tmem_s(tmem, t, sb), smem_desc(q_addr + off, 16, 1024), smem_desc(k_addr + koff, 16, 1024),
-                 idesc_qk, k > 0);
+          const uint32_t qoff = (k >> 2) * 16384 + (k & 3) * 32, koff = (k >> 2) * 8192 + (k & 3) * 32;
+          tc_mma(d0, desc_advance(q_desc0, qoff), desc_advance(k_desc, koff), idesc_qk, k > 0 ? 1u : 0u);
+          if (n_streams > 1)
+            tc_mma(d1, desc_advance(q_desc1, qoff), desc_advance(k_desc, koff), idesc_qk, k > 0 ? 1u : 0u);
         }
-        tc_commit(&bars->s_full[t][sb]);
+        tc_commit(&bars->s_full[0][sb]);
+        if (n_streams > 1) tc_commit(&bars->s_full[1][sb]);
       };
       if (ok) ok = FW_WAIT(3, 0, &bars->k_full[0], 0);
       if (ok) {
         tc_fence_after();
-        for (int t = 0; t < n_streams; ++t) issue_qk(t, 0);
+        issue_qk_all(0);
       }
+#ifdef FW_PROFILE_CLOCKS
+      long long mprof[6] = {0, 0, 0, 0, 0, 0};
+      long long mprev = clock64();
+#define FW_MCLK(k) { long long c = clock64(); mprof[k] += c - mprev; mprev = c; }
+#else
+#define FW_MCLK(k)
+#endif
       for (int j = 0; j < n_tiles && ok; ++j) {
         const int s = j % kKvStages;
         const uint32_t round = j / kKvStages;
@@ -330,28 +351,45 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           // S buffer (j+1)&1 of a stream held S(j-1) and then P(j-1); PV(j-1) was
           // issued in the previous iteration, so it is ahead of this MMA in the
           // tensor pipe and the overwrite is ordered behind its reads.
+          FW_MCLK(0)
           tc_fence_after();
-          for (int t = 0; t < n_streams; ++t) issue_qk(t, j + 1);
+          issue_qk_all(j + 1);
+          FW_MCLK(1)
         }
         ok = FW_WAIT(5, j, &bars->v_full[s], round & 1);
-        const uint32_t v_addr = smem_u32(smem + kSmemV + s * 16384);
+        FW_MCLK(2)
+        const uint64_t v_desc = v_desc0 + static_cast<uint32_t>(s * (16384 >> 4));
+        // p_full is a two-deep ring like S: a softmax group can finish tile j+1
+        // (its QK was issued above) while this thread still waits for the other
+        // stream's tile j, and a single barrier would then be two phases ahead
+        // of this wait.
         for (int t = 0; t < n_streams && ok; ++t) {
-          // p_full is a two-deep ring like S: a softmax group can finish tile j+1
-          // (its QK was issued above) while this thread still waits for the
-          // other stream's tile j, and a single barrier would then be two
-          // phases ahead of this wait.
           ok = FW_WAIT(6 + t, j, &bars->p_full[t][j & 1], (j >> 1) & 1);
-          if (!ok) break;
+          FW_MCLK(3 + t)
+        }
+        if (ok) {
           tc_fence_after();
+          const uint32_t o0 = tmem_o(tmem, 0), o1 = tmem_o(tmem, 1);
+          const uint32_t p0 = tmem_s(tmem, 0, j & 1), p1 = tmem_s(tmem, 1, j & 1);
 #pragma unroll
-          for (int k = 0; k < 4; ++k)
-            tc_mma_ts(tmem_o(tmem, t), tmem_s(tmem, t, j & 1) + k * 8, smem_desc(v_addr + k * 2048, 8192, 1024),
-                      idesc_pv, (j > 0 || k > 0) ? 1u : 0u);
-          tc_commit(&bars->pv_done[t]);
+          for (int k = 0; k < 4; ++k) {
+            const uint32_t acc = (j > 0 || k > 0) ? 1u : 0u;
+            tc_mma_ts(o0, p0 + k * 8, desc_advance(v_desc, k * 2048), idesc_pv, acc);
+            if (n_streams > 1) tc_mma_ts(o1, p1 + k * 8, desc_advance(v_desc, k * 2048), idesc_pv, acc);
+          }
+          tc_commit(&bars->pv_done[0]);
+          if (n_streams > 1) tc_commit(&bars->pv_done[1]);
+          FW_MCLK(5)
         }
         if (!ok) break;
         tc_commit(&bars->kv_empty[s]);
       }
+#ifdef FW_PROFILE_CLOCKS
+      if (p.status != nullptr)
+        for (int k = 0; k < 6; ++k)
+          atomicAdd(reinterpret_cast<unsigned long long*>(p.status + 8) + 8 + k,
+                    static_cast<unsigned long long>(mprof[k]));
+#endif
       if (!ok) {
         *abort_flag = 1;
         report_status(p.status, FW_STATUS_WAIT_TIMEOUT);
@@ -373,6 +411,10 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     float m_used = -INFINITY, l_run = 0.f;
     bool ok = true;
 
+#ifdef FW_PROFILE_CLOCKS
+    long long prof[6] = {0, 0, 0, 0, 0, 0};
+    long long tprev = clock64();
+#endif
     for (int j = 0; j < n_tiles && ok; ++j) {
       const int sb = j & 1, s = j % kKvStages;
       const int pos0 = (tile_lo + j) * kBN;
@@ -381,10 +423,16 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         break;
       }
       tc_fence_after();
+#ifdef FW_PROFILE_CLOCKS
+      { long long c = clock64(); prof[0] += c - tprev; tprev = c; }
+#endif
       uint32_t sr[2][32];
       tmem_ld32(tmem_s(tmem, t, sb) + lane_addr, sr[0]);
       tmem_ld32(tmem_s(tmem, t, sb) + lane_addr + 32, sr[1]);
       tmem_wait_ld();
+#ifdef FW_PROFILE_CLOCKS
+      { long long c = clock64(); prof[1] += c - tprev; tprev = c; }
+#endif
 
       const bool need_mask = pos0 + kBN > min(diag_lo, kv_end) ||
                              (p.window_left >= 0 && pos0 < diag_hi - p.window_left);
@@ -402,6 +450,9 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       }
       // Lazy rescale: the exponent base only moves when the row max outruns it
       // by more than kRescaleThreshold, so O in tensor memory is rarely touched.
+#ifdef FW_PROFILE_CLOCKS
+      { long long c = clock64(); prof[2] += c - tprev; tprev = c; }
+#endif
       float alpha = 1.f;
       if (mx > m_used + kRescaleThreshold || (m_used == -INFINITY && mx > -INFINITY)) {
         alpha = fast_exp2(m_used - mx);  // 0 when m_used was -inf
@@ -422,6 +473,9 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           packed[c * 16 + (i >> 1)] = pack_bf16(p0, p1);
         }
       l_run = l_run * alpha + (sum0 + sum1);
+#ifdef FW_PROFILE_CLOCKS
+      { long long c = clock64(); prof[3] += c - tprev; tprev = c; }
+#endif
 
       // O may only be touched once the previous PV MMA has drained (rare path).
       if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
@@ -446,6 +500,9 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       // the PV MMA.  (This thread already holds its S row in registers.)
       tmem_st32(tmem_s(tmem, t, sb) + lane_addr, packed);
       tmem_wait_st();
+#ifdef FW_PROFILE_CLOCKS
+      { long long c = clock64(); prof[4] += c - tprev; tprev = c; }
+#endif
       // Last tile: keys past the valid length may hold anything (NaN included);
       // their P is 0, so their V rows must be finite: zero them.  Both streams
       // write the same zeros, so neither depends on the other.
@@ -466,8 +523,18 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&bars->p_full[t][sb]);
+#ifdef FW_PROFILE_CLOCKS
+      { long long c = clock64(); prof[5] += c - tprev; tprev = c; }
+#endif
     }
 
+#ifdef FW_PROFILE_CLOCKS
+    if (lane == 0 && warp == 2 && p.status != nullptr) {
+      for (int k = 0; k < 6; ++k) atomicAdd(reinterpret_cast<unsigned long long*>(p.status + 8) + k,
+                                            static_cast<unsigned long long>(prof[k]));
+      atomicAdd(reinterpret_cast<unsigned long long*>(p.status + 8) + 6, static_cast<unsigned long long>(n_tiles));
+    }
+#endif
     // ---- epilogue: O / l -> bf16, lse
     // pv_done completes once per tile, and only the rescale path waits on it
     // inside the loop, so up to two phases can still be open here: S(n-1) being

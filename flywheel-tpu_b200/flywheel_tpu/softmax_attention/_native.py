@@ -76,7 +76,8 @@ class FwCombineArgs(ctypes.Structure):
         ("partial_out", c_ptr), ("partial_lse", c_ptr), ("sinks", c_ptr),
         ("out", c_ptr), ("lse", c_ptr), ("parts", i32), ("rows", i32),
         ("nheads", i32), ("head_dim", i32), ("lse_head_stride", i32),
-        ("lse_token_stride", i32),
+        ("lse_token_stride", i32), ("part_stride_out", i64),
+        ("part_stride_lse", i64),
     ]
 
 

@@ -1,0 +1,137 @@
+"""Single-request long-context decode with the KV pages split over GPUs.
+
+The reference library is single-device; its serving patch merges per-device
+attention states with `_merge_states` (patches/tpu-inference.patch:7174-7186 of
+the reference project).  Here one process per GPU holds a contiguous range of
+the request's logical pages in its own pool; every decode step each rank runs
+the split-KV decode kernel over its own pages in partial-state mode, the
+sink-free `(o, lse)` states are all-gathered with NCCL (33 KB per rank for 64
+heads), and every rank merges them with `fw_lse_combine`.  The rank that owns
+the page holding position `cache_len` appends the new token.
+
+Requests and KV heads need none of this: they shard with no communication.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import dataclasses
+
+import torch
+import torch.distributed as dist
+
+from flywheel_tpu.softmax_attention import _arrays, _native
+
+
+def page_range(total_pages: int, world: int, rank: int) -> tuple[int, int]:
+    """[first, last) logical pages of `rank`: contiguous, sizes differ by at
+    most one, earlier ranks take the extra page."""
+    base, extra = divmod(total_pages, world)
+    first = rank * base + min(rank, extra)
+    return first, first + base + (1 if rank < extra else 0)
+
+
+def owner_of_page(total_pages: int, world: int, page: int) -> int:
+    """Rank whose page_range holds logical page `page`."""
+    base, extra = divmod(total_pages, world)
+    boundary = extra * (base + 1)
+    if page < boundary:
+        return page // (base + 1)
+    return extra + (page - boundary) // max(base, 1)
+
+
+def local_length(global_len: int, page_size: int, first_page: int, last_page: int) -> int:
+    """Tokens of a request of `global_len` tokens that live in logical pages
+    [first_page, last_page)."""
+    lo, hi = first_page * page_size, last_page * page_size
+    return max(0, min(global_len, hi) - lo)
+
+
+def pack_state(partial_out: torch.Tensor, partial_lse: torch.Tensor) -> torch.Tensor:
+    """(rows, d) f32 and (rows,) f32 -> one (rows * (d + 1),) buffer: all o rows,
+    then all lse, so the gathered buffer splits back without a copy."""
+    return torch.cat([partial_out.reshape(-1), partial_lse.reshape(-1)])
+
+
+def unpack_states(gathered: torch.Tensor, world: int, rows: int, d: int):
+    """Views of a gathered buffer: (world, rows, d) states and (world, rows)
+    lse.  Consecutive ranks are rows * (d + 1) elements apart in both."""
+    per_rank = gathered.view(world, rows * (d + 1))
+    outs = per_rank[:, : rows * d].unflatten(1, (rows, d))
+    lses = per_rank[:, rows * d:]
+    return outs, lses
+
+
+@dataclasses.dataclass
+class ShardedDecoder:
+    """Per-rank state of a long-context decode whose pages are split over the
+    ranks of `group`.  `pool` holds this rank's pages (any physical order);
+    `table` is this rank's (1, local_pages) block table over its own pool."""
+
+    pool: torch.Tensor
+    table: torch.Tensor
+    total_pages: int
+    nheads: int
+    nheads_k: int
+    group: dist.ProcessGroup | None = None
+    softmax_scale: float | None = None
+    sinks: torch.Tensor | None = None
+
+    def __post_init__(self):
+        self.device = self.pool.device
+        self.world = dist.get_world_size(self.group)
+        self.rank = dist.get_rank(self.group)
+        self.page_size = self.pool.shape[1]
+        self.head_dim = self.pool.shape[3]
+        self.first_page, self.last_page = page_range(self.total_pages, self.world, self.rank)
+        rows = self.nheads
+        f32 = dict(dtype=torch.float32, device=self.device)
+        self.state = torch.empty(rows * (self.head_dim + 1), **f32)
+        self.gathered = torch.empty(self.world * rows * (self.head_dim + 1), **f32)
+        self.local_len = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.out = torch.empty((1, 1, self.nheads, self.head_dim), dtype=torch.bfloat16,
+                               device=self.device)
+        self.lse = torch.empty((1, self.nheads, 1), **f32)
+        self.scale = self.softmax_scale or self.head_dim ** -0.5
+        self.lib = _native.library()
+        self.scratch = None
+
+    def step(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, global_len: int):
+        """One decode step: q (1, 1, nheads, d), new k / v (1, 1, nheads_k, d),
+        `global_len` tokens cached before the step.  Returns (out, lse); the new
+        token is appended on the rank that owns its page."""
+        rows, d = self.nheads, self.head_dim
+        owner = owner_of_page(self.total_pages, self.world, global_len // self.page_size)
+        appends = owner == self.rank
+        self.local_len.fill_(local_length(global_len, self.page_size, self.first_page, self.last_page))
+        partial_out = self.state[: rows * d]
+        partial_lse = self.state[rows * d:]
+        args = _native.FwDecodeArgs(
+            q=q.data_ptr(), out=0, lse=0, kv_cache=self.pool.data_ptr(), v_cache=0,
+            k_new=k.data_ptr() if appends else 0, v_new=v.data_ptr() if appends else 0,
+            cache_seqlens=self.local_len.data_ptr(), block_table=self.table.data_ptr(),
+            partial_out=partial_out.data_ptr(), partial_lse=partial_lse.data_ptr(),
+            num_pages=self.pool.shape[0], page_size=self.page_size,
+            pages_per_seq=self.table.shape[1], batch=1, seqlen_q=1, nheads=self.nheads,
+            nheads_k=self.nheads_k, head_dim=d,
+            kv_dtype=_native.DTYPE_CODE[_arrays.dtype_name(self.pool.dtype)],
+            # one query token on the last position: every local key is visible
+            causal=0, window_left=-1, softmax_scale=self.scale, softcap=0.0, num_ctas=0)
+        stream = _native.current_stream(self.device)
+        if self.scratch is None:
+            nbytes = self.lib.fw_decode_workspace_bytes(ctypes.byref(args))
+            if nbytes == 0:
+                raise RuntimeError(_native.last_error())
+            self.scratch = torch.zeros(nbytes, dtype=torch.uint8, device=self.device)
+        args.workspace, args.workspace_bytes = self.scratch.data_ptr(), self.scratch.numel()
+        _native.check(self.lib.fw_decode_kvcache(ctypes.byref(args), stream))
+        dist.all_gather_into_tensor(self.gathered, self.state, group=self.group)
+        outs, lses = unpack_states(self.gathered, self.world, rows, d)
+        merge = _native.FwCombineArgs(
+            partial_out=outs.data_ptr(), partial_lse=lses.data_ptr(),
+            sinks=_arrays.data_ptr(self.sinks), out=self.out.data_ptr(), lse=self.lse.data_ptr(),
+            parts=self.world, rows=rows, nheads=self.nheads, head_dim=d, lse_head_stride=1,
+            lse_token_stride=self.nheads, part_stride_out=rows * (d + 1),
+            part_stride_lse=rows * (d + 1))
+        _native.check(self.lib.fw_lse_combine(ctypes.byref(merge), stream))
+        return self.out, self.lse

@@ -236,6 +236,11 @@ typedef struct FwCombineArgs {
   int32_t head_dim;
   int32_t lse_head_stride;
   int32_t lse_token_stride;
+  /* Elements between consecutive parts of partial_out / partial_lse; 0 means
+   * contiguous (rows * head_dim and rows).  Lets the merge read an all-gather
+   * buffer whose per-rank slice is [o rows | lse rows] without a repack. */
+  int64_t part_stride_out;
+  int64_t part_stride_lse;
 } FwCombineArgs;
 
 int fw_lse_combine(const FwCombineArgs* args, void* stream);

@@ -31,7 +31,7 @@ def test_struct_sizes_match_header_layout():
     # 17 pointers + u64 + i64 + 11 i32/f32 fields + 1 i32 (padded to 8)
     assert ctypes.sizeof(_native.FwDecodeArgs) == 17 * 8 + 8 + 8 + 14 * 4
     assert ctypes.sizeof(_native.FwAppendArgs) == 7 * 8 + 8 + 7 * 4 + 4
-    assert ctypes.sizeof(_native.FwCombineArgs) == 5 * 8 + 6 * 4
+    assert ctypes.sizeof(_native.FwCombineArgs) == 5 * 8 + 6 * 4 + 2 * 8
 
 
 def test_argument_errors_mirror_reference_exception_types():
