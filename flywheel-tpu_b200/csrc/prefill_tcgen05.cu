@@ -11,8 +11,9 @@
 // One CTA = one query block of one KV head: two "streams" of 128 rows, each
 // (128 / group) tokens x the `group` query heads that share the KV head (rows
 // ordered head-major), so every K/V tile is fetched from L2 once per 256 query
-// rows.  KV advances in 64-key tiles (one 64-token page, or a 64-token slice
-// of a larger page) through a 4-stage TMA ring.  Warp roles: warp 0 issues
+// rows.  KV advances in 128-key tiles (two 64-token boxes: pages of 64, or
+// slices of larger pages) through a 2-stage TMA ring whose K and V halves are
+// released separately.  Warp roles: warp 0 issues
 // TMA, warp 1 owns tensor memory and issues the MMAs of both streams, warps
 // 2-5 and 6-9 are the two softmax groups (one thread per row: tcgen05.ld of
 // S, online softmax with lazy rescale, P written back over S in tensor memory
@@ -25,16 +26,16 @@
 namespace fw {
 
 constexpr int kBM = 128;       // query rows per CTA
-constexpr int kBN = 64;        // keys per KV tile
+constexpr int kBN = 128;       // keys per KV tile
 constexpr int kStreams = 2;     // 128-row query tiles per CTA, one softmax warp group each
-constexpr int kKvStages = 4;
-constexpr int kTmemCols = 512;  // per stream: O 128 columns, S / P double buffer 2 x 64
+constexpr int kKvStages = 2;
+constexpr int kTmemCols = 512;  // per stream: O 128 columns, S 128 columns (P overwrites S)
 constexpr float kRescaleThreshold = 8.0f;  // log2 units a row max may drift before O is rescaled
 
 constexpr int kSmemQ = 0;                      // streams x 2 halves x [128 rows][128 B]
-constexpr int kSmemK = kStreams * 32768;       // stages x 2 halves x [64 keys][128 B]
-constexpr int kSmemV = kSmemK + kKvStages * 16384;
-constexpr int kSmemBar = kSmemV + kKvStages * 16384;
+constexpr int kSmemK = kStreams * 32768;       // stages x 2 halves x [128 keys][128 B]
+constexpr int kSmemV = kSmemK + kKvStages * 32768;
+constexpr int kSmemBar = kSmemV + kKvStages * 32768;
 constexpr int kSmemBytes = kSmemBar + 256;
 
 struct Tc05Params {
@@ -197,19 +198,19 @@ __device__ __forceinline__ void record_timeout(int* status, int site, int j) {
 
 struct Bars {
   uint64_t q_full;
-  uint64_t k_full[kKvStages], v_full[kKvStages], kv_empty[kKvStages];
-  uint64_t s_full[kStreams][2];
-  uint64_t p_full[kStreams][2], pv_done[kStreams];
+  uint64_t k_full[kKvStages], v_full[kKvStages], k_empty[kKvStages], v_empty[kKvStages];
+  uint64_t s_full[kStreams], p_full[kStreams], pv_done[kStreams];
   uint32_t tmem_base;
   int abort_flag;
 };
 
-// Tensor-memory columns of stream t: O at [256 t, 256 t + 128), the two S / P
-// buffers at 256 t + 128 + 64 sb.
+// Tensor-memory columns of stream t: O at [256 t, 256 t + 128), S at
+// [256 t + 128, 256 t + 256); P (bf16 pairs) overwrites the first 64 columns of S.
 __device__ __forceinline__ uint32_t tmem_o(uint32_t base, int t) { return base + t * 256; }
-__device__ __forceinline__ uint32_t tmem_s(uint32_t base, int t, int sb) { return base + t * 256 + 128 + sb * 64; }
+__device__ __forceinline__ uint32_t tmem_s(uint32_t base, int t) { return base + t * 256 + 128; }
 
-#define FW_WAIT(site, j, bar, parity) (mbar_wait_bounded(bar, parity, abort_flag) || (record_timeout(p.status, site, j), false))
+#define FW_WAIT(site, j, bar, parity) \
+  (mbar_wait_bounded(bar, parity, abort_flag) || (record_timeout(p.status, site, j), false))
 
 __global__ void __launch_bounds__(64 + kStreams * 128, 1)
 prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv,
@@ -242,13 +243,12 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     for (int s = 0; s < kKvStages; ++s) {
       mbar_init(&bars->k_full[s], 1);
       mbar_init(&bars->v_full[s], 1);
-      mbar_init(&bars->kv_empty[s], 1);
+      mbar_init(&bars->k_empty[s], 1);
+      mbar_init(&bars->v_empty[s], 1);
     }
     for (int t = 0; t < kStreams; ++t) {
-      mbar_init(&bars->s_full[t][0], 1);
-      mbar_init(&bars->s_full[t][1], 1);
-      mbar_init(&bars->p_full[t][0], 4);
-      mbar_init(&bars->p_full[t][1], 4);
+      mbar_init(&bars->s_full[t], 1);
+      mbar_init(&bars->p_full[t], 4);
       mbar_init(&bars->pv_done[t], 1);
     }
     bars->abort_flag = 0;
@@ -278,26 +278,43 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       for (int j = 0; j < n_tiles && ok; ++j) {
         const int s = j % kKvStages;
         const uint32_t round = j / kKvStages;
-        if (!FW_WAIT(1, j, &bars->kv_empty[s], (round & 1) ^ 1)) {
+        // K of a stage is free once the QK MMAs of its tile are done, V once
+        // the PV MMAs are: K therefore runs further ahead than V.
+        if (!FW_WAIT(1, j, &bars->k_empty[s], (round & 1) ^ 1)) {
           ok = false;
           break;
         }
+        // A 128-key tile is two 64-token boxes per operand half; the second is
+        // left out when it lies wholly past the valid keys (its block-table
+        // entry may not exist).  Rows that are not loaded are masked (K) or
+        // zeroed by the softmax group (V).
         const int pos0 = (tile_lo + j) * kBN;
-        const int page_idx = pos0 / p.page_size;
-        int page = p.block_table[static_cast<long long>(req) * p.pages_per_seq + page_idx];
-        if (page < 0 || page >= p.num_pages) {
-          report_status(p.status, FW_STATUS_BAD_PAGE);
-          page = 0;
+        const int subs = pos0 + 64 < kv_end ? 2 : 1;
+        int page[2], tok[2];
+        for (int sub = 0; sub < subs; ++sub) {
+          const int pos = pos0 + sub * 64;
+          const int page_idx = pos / p.page_size;
+          page[sub] = p.block_table[static_cast<long long>(req) * p.pages_per_seq + page_idx];
+          if (page[sub] < 0 || page[sub] >= p.num_pages) {
+            report_status(p.status, FW_STATUS_BAD_PAGE);
+            page[sub] = 0;
+          }
+          tok[sub] = pos - page_idx * p.page_size;
         }
-        const int tok = pos0 - page_idx * p.page_size;
-        mbar_arrive_expect_tx(&bars->k_full[s], kBN * 256);
-        mbar_arrive_expect_tx(&bars->v_full[s], kBN * 256);
-        for (int half = 0; half < 2; ++half) {
-          tma_load_4d(smem + kSmemK + s * 16384 + half * 8192, &map_kv, &bars->k_full[s], half * 64, 2 * h, tok,
-                      page);
-          tma_load_4d(smem + kSmemV + s * 16384 + half * 8192, &map_kv, &bars->v_full[s], half * 64, 2 * h + 1,
-                      tok, page);
+        mbar_arrive_expect_tx(&bars->k_full[s], subs * 64 * 256);
+        for (int sub = 0; sub < subs; ++sub)
+          for (int half = 0; half < 2; ++half)
+            tma_load_4d(smem + kSmemK + s * 32768 + half * 16384 + sub * 8192, &map_kv, &bars->k_full[s],
+                        half * 64, 2 * h, tok[sub], page[sub]);
+        if (!FW_WAIT(18, j, &bars->v_empty[s], (round & 1) ^ 1)) {
+          ok = false;
+          break;
         }
+        mbar_arrive_expect_tx(&bars->v_full[s], subs * 64 * 256);
+        for (int sub = 0; sub < subs; ++sub)
+          for (int half = 0; half < 2; ++half)
+            tma_load_4d(smem + kSmemV + s * 32768 + half * 16384 + sub * 8192, &map_kv, &bars->v_full[s],
+                        half * 64, 2 * h + 1, tok[sub], page[sub]);
       }
       if (!ok) {
         *abort_flag = 1;
@@ -306,90 +323,59 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     }
   } else if (n_tiles > 0 && warp == 1) {
     // ------------------------------------------------------------ MMA issuer
+    // Per stream the chain is QK(j) -> softmax(j) -> PV(j) -> QK(j+1): S has one
+    // buffer per stream (P overwrites it), so the next QK follows the PV that
+    // read P.  The two streams alternate, which keeps the tensor pipe busy with
+    // one stream's MMAs while the other stream's softmax group works.
     if (lane == 0) {
       constexpr uint32_t idesc_qk = instr_desc(kBN, false);
       constexpr uint32_t idesc_pv = instr_desc(128, true);
       const uint64_t q_desc0 = smem_desc(smem_u32(smem + kSmemQ), 16, 1024);
       const uint64_t k_desc0 = smem_desc(smem_u32(smem + kSmemK), 16, 1024);
-      const uint64_t v_desc0 = smem_desc(smem_u32(smem + kSmemV), 8192, 1024);
-      bool ok = FW_WAIT(2, 0, &bars->q_full, 0);
-      // S(j) of every stream.  The streams' MMAs alternate so that consecutive
-      // instructions accumulate into different tensor-memory tiles.
-      auto issue_qk_all = [&](int j) {
-        const int s = j % kKvStages, sb = j & 1;
-        const uint64_t k_desc = k_desc0 + static_cast<uint32_t>(s * (16384 >> 4));
-        const uint64_t q_desc1 = q_desc0 + static_cast<uint32_t>(32768 >> 4);
-        const uint32_t d0 = tmem_s(tmem, 0, sb), d1 = tmem_s(tmem, 1, sb);
+      const uint64_t v_desc0 = smem_desc(smem_u32(smem + kSmemV), 16384, 1024);
+      auto issue_qk = [&](int t, int j) {
+        const uint64_t q_desc = q_desc0 + static_cast<uint32_t>(t * (32768 >> 4));
+        const uint64_t k_desc = k_desc0 + static_cast<uint32_t>((j % kKvStages) * (32768 >> 4));
+        const uint32_t d_addr = tmem_s(tmem, t);
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
-          const uint32_t qoff = (k >> 2) * 16384 + (k & 3) * 32, koff = (k >> 2) * 8192 + (k & 3) * 32;
-          tc_mma(d0, desc_advance(q_desc0, qoff), desc_advance(k_desc, koff), idesc_qk, k > 0 ? 1u : 0u);
-          if (n_streams > 1)
-            tc_mma(d1, desc_advance(q_desc1, qoff), desc_advance(k_desc, koff), idesc_qk, k > 0 ? 1u : 0u);
+          const uint32_t off = (k >> 2) * 16384 + (k & 3) * 32;  // head_dim half, 16-element step
+          tc_mma(d_addr, desc_advance(q_desc, off), desc_advance(k_desc, off), idesc_qk, k > 0 ? 1u : 0u);
         }
-        tc_commit(&bars->s_full[0][sb]);
-        if (n_streams > 1) tc_commit(&bars->s_full[1][sb]);
+        tc_commit(&bars->s_full[t]);
       };
+      bool ok = FW_WAIT(2, 0, &bars->q_full, 0);
       if (ok) ok = FW_WAIT(3, 0, &bars->k_full[0], 0);
       if (ok) {
         tc_fence_after();
-        issue_qk_all(0);
+        for (int t = 0; t < n_streams; ++t) issue_qk(t, 0);
+        tc_commit(&bars->k_empty[0]);
       }
-#ifdef FW_PROFILE_CLOCKS
-      long long mprof[6] = {0, 0, 0, 0, 0, 0};
-      long long mprev = clock64();
-#define FW_MCLK(k) { long long c = clock64(); mprof[k] += c - mprev; mprev = c; }
-#else
-#define FW_MCLK(k)
-#endif
       for (int j = 0; j < n_tiles && ok; ++j) {
         const int s = j % kKvStages;
         const uint32_t round = j / kKvStages;
-        if (j + 1 < n_tiles) {
-          ok = FW_WAIT(4, j, &bars->k_full[(j + 1) % kKvStages], ((j + 1) / kKvStages) & 1);
-          if (!ok) break;
-          // S buffer (j+1)&1 of a stream held S(j-1) and then P(j-1); PV(j-1) was
-          // issued in the previous iteration, so it is ahead of this MMA in the
-          // tensor pipe and the overwrite is ordered behind its reads.
-          FW_MCLK(0)
-          tc_fence_after();
-          issue_qk_all(j + 1);
-          FW_MCLK(1)
-        }
-        ok = FW_WAIT(5, j, &bars->v_full[s], round & 1);
-        FW_MCLK(2)
-        const uint64_t v_desc = v_desc0 + static_cast<uint32_t>(s * (16384 >> 4));
-        // p_full is a two-deep ring like S: a softmax group can finish tile j+1
-        // (its QK was issued above) while this thread still waits for the other
-        // stream's tile j, and a single barrier would then be two phases ahead
-        // of this wait.
+        const uint64_t v_desc = v_desc0 + static_cast<uint32_t>(s * (32768 >> 4));
         for (int t = 0; t < n_streams && ok; ++t) {
-          ok = FW_WAIT(6 + t, j, &bars->p_full[t][j & 1], (j >> 1) & 1);
-          FW_MCLK(3 + t)
-        }
-        if (ok) {
+          ok = FW_WAIT(6 + t, j, &bars->p_full[t], j & 1);
+          if (ok && t == 0) ok = FW_WAIT(5, j, &bars->v_full[s], round & 1);
+          if (!ok) break;
           tc_fence_after();
-          const uint32_t o0 = tmem_o(tmem, 0), o1 = tmem_o(tmem, 1);
-          const uint32_t p0 = tmem_s(tmem, 0, j & 1), p1 = tmem_s(tmem, 1, j & 1);
+          const uint32_t o_addr = tmem_o(tmem, t), p_addr = tmem_s(tmem, t);
+          tc_mma_ts(o_addr, p_addr, v_desc, idesc_pv, j > 0 ? 1u : 0u);
 #pragma unroll
-          for (int k = 0; k < 4; ++k) {
-            const uint32_t acc = (j > 0 || k > 0) ? 1u : 0u;
-            tc_mma_ts(o0, p0 + k * 8, desc_advance(v_desc, k * 2048), idesc_pv, acc);
-            if (n_streams > 1) tc_mma_ts(o1, p1 + k * 8, desc_advance(v_desc, k * 2048), idesc_pv, acc);
+          for (int k = 1; k < 8; ++k)
+            tc_mma_ts(o_addr, p_addr + k * 8, desc_advance(v_desc, k * 2048), idesc_pv, 1u);
+          tc_commit(&bars->pv_done[t]);
+          if (t == n_streams - 1) tc_commit(&bars->v_empty[s]);
+          if (j + 1 < n_tiles) {
+            if (t == 0) ok = FW_WAIT(4, j, &bars->k_full[(j + 1) % kKvStages], ((j + 1) / kKvStages) & 1);
+            if (!ok) break;
+            tc_fence_after();
+            issue_qk(t, j + 1);
+            if (t == n_streams - 1) tc_commit(&bars->k_empty[(j + 1) % kKvStages]);
           }
-          tc_commit(&bars->pv_done[0]);
-          if (n_streams > 1) tc_commit(&bars->pv_done[1]);
-          FW_MCLK(5)
         }
-        if (!ok) break;
-        tc_commit(&bars->kv_empty[s]);
       }
-#ifdef FW_PROFILE_CLOCKS
-      if (p.status != nullptr)
-        for (int k = 0; k < 6; ++k)
-          atomicAdd(reinterpret_cast<unsigned long long*>(p.status + 8) + 8 + k,
-                    static_cast<unsigned long long>(mprof[k]));
-#endif
       if (!ok) {
         *abort_flag = 1;
         report_status(p.status, FW_STATUS_WAIT_TIMEOUT);
@@ -405,80 +391,65 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     const int diag = diag_base + tl;
     const int diag_lo = diag_base + t * p.tpb, diag_hi = diag_lo + p.tpb - 1;  // this stream's diagonals
     const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
+    const uint32_t s_addr = tmem_s(tmem, t) + lane_addr, o_addr = tmem_o(tmem, t) + lane_addr;
     const float kd = p.k_descale ? *p.k_descale : 1.0f;
     const float c1 = p.softcap > 0.f ? p.scale * kd / p.softcap : p.scale * kd * kLog2e;
     const float c2 = p.softcap * kLog2e;
+    const float mul = p.softcap > 0.f ? 1.0f : c1;
     float m_used = -INFINITY, l_run = 0.f;
     bool ok = true;
 
-#ifdef FW_PROFILE_CLOCKS
-    long long prof[6] = {0, 0, 0, 0, 0, 0};
-    long long tprev = clock64();
-#endif
     for (int j = 0; j < n_tiles && ok; ++j) {
-      const int sb = j & 1, s = j % kKvStages;
+      const int s = j % kKvStages;
       const int pos0 = (tile_lo + j) * kBN;
-      if (!FW_WAIT(8 + t, j, &bars->s_full[t][sb], (j >> 1) & 1)) {
+      if (!FW_WAIT(8 + t, j, &bars->s_full[t], j & 1)) {
         ok = false;
         break;
       }
       tc_fence_after();
-#ifdef FW_PROFILE_CLOCKS
-      { long long c = clock64(); prof[0] += c - tprev; tprev = c; }
-#endif
-      uint32_t sr[2][32];
-      tmem_ld32(tmem_s(tmem, t, sb) + lane_addr, sr[0]);
-      tmem_ld32(tmem_s(tmem, t, sb) + lane_addr + 32, sr[1]);
-      tmem_wait_ld();
-#ifdef FW_PROFILE_CLOCKS
-      { long long c = clock64(); prof[1] += c - tprev; tprev = c; }
-#endif
-
       const bool need_mask = pos0 + kBN > min(diag_lo, kv_end) ||
                              (p.window_left >= 0 && pos0 < diag_hi - p.window_left);
-      // Pass 1 (warp-uniform variants): softcap transform, mask, row max.
-      // Without a softcap the raw scores stay in place and the scale rides in
-      // the exponent's FMA (c1 > 0, so the max commutes with the scale).
-      float mx;
-      if (p.softcap > 0.f) {
-        mx = need_mask ? transform_row<true, true>(sr, c1, c2, pos0, kv_end, diag, p.causal, p.window_left)
-                       : transform_row<true, false>(sr, c1, c2, pos0, kv_end, diag, p.causal, p.window_left);
-      } else {
-        mx = need_mask ? transform_row<false, true>(sr, c1, c2, pos0, kv_end, diag, p.causal, p.window_left)
-                       : transform_row<false, false>(sr, c1, c2, pos0, kv_end, diag, p.causal, p.window_left);
-        mx *= c1;
+      const bool rewrite = need_mask || p.softcap > 0.f;
+      // Pass 1 over the two 64-key halves of the row (warp-uniform variants):
+      // softcap transform and mask, written back to tensor memory only when
+      // they changed something, and the row max.  Without a softcap the raw
+      // scores stay in place and the scale rides in pass 2's FMA (c1 > 0, so the
+      // max commutes with the scale).
+      float mx = -INFINITY;
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        uint32_t sr[2][32];
+        tmem_ld32(s_addr + half * 64, sr[0]);
+        tmem_ld32(s_addr + half * 64 + 32, sr[1]);
+        tmem_wait_ld();
+        const int hpos = pos0 + half * 64;
+        float hm;
+        if (p.softcap > 0.f) {
+          hm = need_mask ? transform_row<true, true>(sr, c1, c2, hpos, kv_end, diag, p.causal, p.window_left)
+                         : transform_row<true, false>(sr, c1, c2, hpos, kv_end, diag, p.causal, p.window_left);
+        } else {
+          hm = need_mask ? transform_row<false, true>(sr, c1, c2, hpos, kv_end, diag, p.causal, p.window_left)
+                         : transform_row<false, false>(sr, c1, c2, hpos, kv_end, diag, p.causal, p.window_left);
+        }
+        if (rewrite) {
+          tmem_st32(s_addr + half * 64, sr[0]);
+          tmem_st32(s_addr + half * 64 + 32, sr[1]);
+        }
+        mx = fmaxf(mx, hm);
       }
+      if (rewrite) tmem_wait_st();
+      if (!(p.softcap > 0.f)) mx *= c1;
       // Lazy rescale: the exponent base only moves when the row max outruns it
       // by more than kRescaleThreshold, so O in tensor memory is rarely touched.
-#ifdef FW_PROFILE_CLOCKS
-      { long long c = clock64(); prof[2] += c - tprev; tprev = c; }
-#endif
       float alpha = 1.f;
       if (mx > m_used + kRescaleThreshold || (m_used == -INFINITY && mx > -INFINITY)) {
         alpha = fast_exp2(m_used - mx);  // 0 when m_used was -inf
         m_used = mx;
       }
       const float neg_base = m_used == -INFINITY ? 0.f : -m_used;
-      const float mul = p.softcap > 0.f ? 1.0f : c1;
-      float sum0 = 0.f, sum1 = 0.f;
-      uint32_t packed[32];
-#pragma unroll
-      for (int c = 0; c < 2; ++c)
-#pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          const float p0 = fast_exp2(fmaf(__uint_as_float(sr[c][i]), mul, neg_base));
-          const float p1 = fast_exp2(fmaf(__uint_as_float(sr[c][i + 1]), mul, neg_base));
-          sum0 += p0;
-          sum1 += p1;
-          packed[c * 16 + (i >> 1)] = pack_bf16(p0, p1);
-        }
-      l_run = l_run * alpha + (sum0 + sum1);
-#ifdef FW_PROFILE_CLOCKS
-      { long long c = clock64(); prof[3] += c - tprev; tprev = c; }
-#endif
-
-      // O may only be touched once the previous PV MMA has drained (rare path).
       if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
+        // PV(j-1) of this stream precedes QK(j) in the tensor pipe, so it has
+        // drained; the wait makes its writes to O visible here.
         if (!FW_WAIT(10 + t, j, &bars->pv_done[t], (j - 1) & 1)) {
           ok = false;
           break;
@@ -487,22 +458,39 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
           uint32_t o[32];
-          tmem_ld32(tmem_o(tmem, t) + lane_addr + c * 32, o);
+          tmem_ld32(o_addr + c * 32, o);
           tmem_wait_ld();
 #pragma unroll
           for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-          tmem_st32(tmem_o(tmem, t) + lane_addr + c * 32, o);
+          tmem_st32(o_addr + c * 32, o);
         }
         tmem_wait_st();
       }
-      // P overwrites the first 32 columns of this tile's S buffer in tensor
-      // memory: row = lane, two bf16 keys per 32-bit column, the A operand of
-      // the PV MMA.  (This thread already holds its S row in registers.)
-      tmem_st32(tmem_s(tmem, t, sb) + lane_addr, packed);
+      // Pass 2: P = 2^(s * mul - m) as bf16 pairs, written over the start of S
+      // (two keys per 32-bit column: the A operand of the PV MMA).  Half 0's P
+      // lands on columns this thread has already read; half 1's S columns
+      // [64, 128) are untouched until read.
+      float sum0 = 0.f, sum1 = 0.f;
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        uint32_t sr[2][32], packed[32];
+        tmem_ld32(s_addr + half * 64, sr[0]);
+        tmem_ld32(s_addr + half * 64 + 32, sr[1]);
+        tmem_wait_ld();
+#pragma unroll
+        for (int c = 0; c < 2; ++c)
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            const float p0 = fast_exp2(fmaf(__uint_as_float(sr[c][i]), mul, neg_base));
+            const float p1 = fast_exp2(fmaf(__uint_as_float(sr[c][i + 1]), mul, neg_base));
+            sum0 += p0;
+            sum1 += p1;
+            packed[c * 16 + (i >> 1)] = pack_bf16(p0, p1);
+          }
+        tmem_st32(s_addr + half * 32, packed);
+      }
+      l_run = l_run * alpha + (sum0 + sum1);
       tmem_wait_st();
-#ifdef FW_PROFILE_CLOCKS
-      { long long c = clock64(); prof[4] += c - tprev; tprev = c; }
-#endif
       // Last tile: keys past the valid length may hold anything (NaN included);
       // their P is 0, so their V rows must be finite: zero them.  Both streams
       // write the same zeros, so neither depends on the other.
@@ -511,36 +499,21 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           ok = false;
           break;
         }
-        const int first_bad = kv_end - pos0;  // in [1, 63]
-        uint8_t* vbase = smem + kSmemV + s * 16384;
+        const int first_bad = kv_end - pos0;  // in [1, kBN - 1]
+        uint8_t* vbase = smem + kSmemV + s * 32768;
         for (int idx = row; idx < (kBN - first_bad) * 16; idx += 128) {
           const int r = first_bad + idx / 16, c = idx % 16;
-          *reinterpret_cast<uint4*>(vbase + (c >> 3) * 8192 + r * 128 + (((c & 7) ^ (r & 7)) << 4)) =
+          *reinterpret_cast<uint4*>(vbase + (c >> 3) * 16384 + r * 128 + (((c & 7) ^ (r & 7)) << 4)) =
               make_uint4(0u, 0u, 0u, 0u);
         }
         fence_proxy_async_smem();
       }
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&bars->p_full[t][sb]);
-#ifdef FW_PROFILE_CLOCKS
-      { long long c = clock64(); prof[5] += c - tprev; tprev = c; }
-#endif
+      if (lane == 0) mbar_arrive(&bars->p_full[t]);
     }
 
-#ifdef FW_PROFILE_CLOCKS
-    if (lane == 0 && warp == 2 && p.status != nullptr) {
-      for (int k = 0; k < 6; ++k) atomicAdd(reinterpret_cast<unsigned long long*>(p.status + 8) + k,
-                                            static_cast<unsigned long long>(prof[k]));
-      atomicAdd(reinterpret_cast<unsigned long long*>(p.status + 8) + 6, static_cast<unsigned long long>(n_tiles));
-    }
-#endif
     // ---- epilogue: O / l -> bf16, lse
-    // pv_done completes once per tile, and only the rescale path waits on it
-    // inside the loop, so up to two phases can still be open here: S(n-1) being
-    // ready only proves PV(n-3) done.  Wait for them in order (a parity wait
-    // is only meaningful for the phase that is currently open).
-    if (ok && n_tiles > 1) ok = FW_WAIT(14 + t, n_tiles - 2, &bars->pv_done[t], (n_tiles - 2) & 1);
     if (ok && n_tiles > 0) ok = FW_WAIT(16 + t, n_tiles - 1, &bars->pv_done[t], (n_tiles - 1) & 1);
     if (ok) {
       tc_fence_after();
@@ -562,7 +535,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       for (int c = 0; c < 4; ++c) {
         uint32_t o[32];
         if (n_tiles > 0) {
-          tmem_ld32(tmem_o(tmem, t) + lane_addr + c * 32, o);
+          tmem_ld32(o_addr + c * 32, o);
           tmem_wait_ld();
         } else {
 #pragma unroll
@@ -604,7 +577,7 @@ bool tcgen05_prefill_supported(const FwPrefillArgs* a) {
   if (a->nheads_k <= 0 || a->nheads % a->nheads_k) return false;
   const int group = a->nheads / a->nheads_k;
   if (!power_of_two(group) || group > 16) return false;  // 128 rows = (128 / group) tokens x group heads
-  if (a->page_size <= 0 || a->page_size % kBN) return false;
+  if (a->page_size <= 0 || a->page_size % 64) return false;  // a tile is two 64-token boxes
   if (a->batch > 2048) return false;
   if (!(a->softmax_scale > 0.f)) return false;  // the row max is taken before scaling
   return true;
@@ -686,7 +659,7 @@ int tcgen05_prefill(const FwPrefillArgs* a, cudaStream_t stream) {
     const uint64_t row_bytes = planes * 256;
     const uint64_t dims[4] = {128, planes, static_cast<uint64_t>(a->page_size), static_cast<uint64_t>(a->num_pages)};
     const uint64_t strides[3] = {256, row_bytes, row_bytes * a->page_size};
-    const uint32_t box[4] = {64, 1, kBN, 1};
+    const uint32_t box[4] = {64, 1, 64, 1};
     rc = encode_tensor_map_bf16(&map_kv, 4, a->kv_cache, dims, strides, box);
     if (rc != FW_OK) return rc;
   }
