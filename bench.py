@@ -250,6 +250,53 @@ def bench_prefill(ns, device, rank, world, barrier):
             "h2d": work["q_host"].numel() * 2, "check": check}
 
 
+def bench_long_context(ns, device, rank, world, barrier):
+    """Single-request long-context decode: one 128K-token paged bf16 cache (page
+    64, random block table), 64 q heads, 8 kv heads, 256 decode steps with the
+    fused append, the pages split evenly over the ranks; per step every rank
+    decodes its pages, the (o, lse) states are all-gathered (NCCL) and merged."""
+    import torch
+    import torch.distributed as dist
+    from flywheel_tpu.softmax_attention import distributed as d
+    context, steps = 131072, 256
+    total_pages = (context + steps) // PAGE + 1
+    first, last = d.page_range(total_pages, world, rank)
+    local_pages = last - first
+    rng = np.random.default_rng(2000 + rank)
+    perm = rng.permutation(local_pages + 4)[:local_pages].astype(np.int32)
+    gen = torch.Generator(device=device)
+    gen.manual_seed(2000 + rank)
+    pool = torch.randn((local_pages + 4, PAGE, 2 * HK, D), generator=gen, device=device,
+                       dtype=torch.float32).to(torch.bfloat16)
+    table = torch.from_numpy(perm[None]).to(device)
+    if world == 1 and not dist.is_initialized():
+        dist.init_process_group("nccl", init_method="tcp://127.0.0.1:29555", rank=0, world_size=1,
+                                device_id=device)
+    decoder = d.ShardedDecoder(pool=pool, table=table, total_pages=total_pages, nheads=HQ, nheads_k=HK)
+    q = torch.randn((1, 1, HQ, D), device=device).to(torch.bfloat16)
+    k = torch.randn((1, 1, HK, D), device=device).to(torch.bfloat16)
+    v = torch.randn((1, 1, HK, D), device=device).to(torch.bfloat16)
+    for step in range(8):
+        decoder.step(q, k, v, context + step)
+    barrier()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for step in range(steps):
+        decoder.step(q, k, v, context + step)
+    end.record()
+    barrier()
+    ms = torch.tensor([start.elapsed_time(end) / steps], dtype=torch.float64, device=device)
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    kv_bytes = sum((context + step + 1) * 2 * HK * D * 2 for step in range(steps)) / steps
+    return {"metric": "long_context_decode_kv_read_bandwidth", "value": kv_bytes / (float(ms) * 1e-3) / 1e9,
+            "unit": "GB/s", "ms_per_step": float(ms), "n_gpus": world, "steps": steps, "scaling": "strong",
+            "config": {"workload": "1 request, 128K-token paged bf16 cache, page 64, 64 q heads, 8 kv heads, "
+                                   "256 decode steps with fused append, pages split evenly over the GPUs, "
+                                   "NCCL all-gather of (o, lse) + merge per step"},
+            "per_step": "decode kernel + combine + all-gather + merge, launched from Python each step"}
+
+
 def make_decode_call(work, device):
     """A closure that enqueues one decode step through the C ABI on device
     buffers (no host traffic), and the output tensor it fills."""
@@ -361,6 +408,8 @@ def main():
     parser.add_argument("--skip-cpu-baseline", action="store_true")
     parser.add_argument("--skip-e2e", action="store_true")
     parser.add_argument("--skip-prefill", action="store_true")
+    parser.add_argument("--long-context", action="store_true",
+                        help="run the single-request 128K-token decode split over the GPUs")
     parser.add_argument("--prefill-only", action="store_true",
                         help="run only the chunked-prefill workload (profiler captures)")
     parser.add_argument("--batch", type=int, default=128,
@@ -389,6 +438,13 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
+    if ns.long_context:
+        result = bench_long_context(ns, device, rank, world, barrier)
+        if rank == 0:
+            print(json.dumps(result))
+        if dist.is_initialized():
+            dist.destroy_process_group()
+        return
     if ns.prefill_only:
         pf = bench_prefill(ns, device, rank, world, barrier)
         if rank == 0:

@@ -1,0 +1,86 @@
+"""Host-side logic of the multi-GPU paths on CPU ranks (gloo, world size 2):
+page partitioning, the packed (o, lse) all-gather layout, and the merge of the
+gathered states, with the CPU oracle standing in for the per-rank kernel."""
+
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+
+def free_port():
+    with socket.socket() as sock:
+        sock.bind(("127.0.0.1", 0))
+        return sock.getsockname()[1]
+
+
+def test_page_ranges_cover_and_balance():
+    from flywheel_tpu.softmax_attention import distributed as d
+    for total in (1, 7, 8, 2049, 2052):
+        for world in (1, 2, 4, 8):
+            ranges = [d.page_range(total, world, r) for r in range(world)]
+            assert ranges[0][0] == 0 and ranges[-1][1] == total
+            assert all(a[1] == b[0] for a, b in zip(ranges, ranges[1:]))
+            sizes = [hi - lo for lo, hi in ranges]
+            assert max(sizes) - min(sizes) <= 1
+            for page in range(0, total, max(1, total // 50)):
+                owner = d.owner_of_page(total, world, page)
+                assert ranges[owner][0] <= page < ranges[owner][1]
+    assert d.local_length(100, 64, 0, 1) == 64
+    assert d.local_length(100, 64, 1, 2) == 36
+    assert d.local_length(100, 64, 2, 3) == 0
+
+
+def _rank_main(rank, world, port, results):
+    import sys
+    import pathlib
+    root = pathlib.Path(__file__).resolve().parent.parent
+    for path in (root, root / "flywheel-tpu_b200"):
+        if str(path) not in sys.path:
+            sys.path.insert(0, str(path))
+    from flywheel_tpu.softmax_attention import distributed as d
+    from oracle import paged_attention as oracle
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        rng = np.random.default_rng(0)            # same draws on every rank
+        heads, kv_heads, dim, page, total_pages = 8, 2, 128, 64, 9
+        length = 500                              # tokens cached; ends inside page 7
+        keys = rng.standard_normal((total_pages * page, kv_heads, dim), dtype=np.float32)
+        values = rng.standard_normal((total_pages * page, kv_heads, dim), dtype=np.float32)
+        q = rng.standard_normal((1, heads, dim), dtype=np.float32)
+        sinks = rng.standard_normal(heads).astype(np.float32)
+        first, last = d.page_range(total_pages, world, rank)
+        local = d.local_length(length, page, first, last)
+        lo = first * page
+        out, lse = oracle.attend_rows(q, keys[lo:lo + local], values[lo:lo + local], total=local,
+                                      causal=False, window_left=None, softcap=0.0,
+                                      scale=dim ** -0.5, sinks=None)
+        state = d.pack_state(torch.from_numpy(out[0]), torch.from_numpy(lse[:, 0].copy()))
+        gathered = torch.empty(world * state.numel())
+        dist.all_gather_into_tensor(gathered, state)
+        outs, lses = d.unpack_states(gathered, world, heads, dim)
+        merged, merged_lse = oracle.merge_states(outs.numpy(), lses.numpy(), sinks=sinks[None, :])
+        want, want_lse = oracle.attend_rows(q, keys[:length], values[:length], total=length,
+                                            causal=False, window_left=None, softcap=0.0,
+                                            scale=dim ** -0.5, sinks=sinks)
+        np.testing.assert_allclose(merged, want[0], rtol=1e-4, atol=1e-6)
+        np.testing.assert_allclose(merged_lse, want_lse[:, 0], rtol=1e-5)
+        owner = d.owner_of_page(total_pages, world, length // page)
+        results[rank] = (int(local), int(owner))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_sharded_state_gather_and_merge_on_two_cpu_ranks():
+    world, port = 2, free_port()
+    manager = mp.Manager()
+    results = manager.dict()
+    mp.spawn(_rank_main, args=(world, port, results), nprocs=world, join=True)
+    assert results[0][0] + results[1][0] == 500
+    assert results[0][1] == results[1][1] == 1      # page 7 of 9 lives on rank 1
