@@ -297,6 +297,92 @@ def bench_long_context(ns, device, rank, world, barrier):
             "per_step": "decode kernel + combine + all-gather + merge, launched from Python each step"}
 
 
+def bench_config(ns, name, device):
+    """Secondary decode configurations (one JSON line each, device-resident):
+    c1 = contiguous bf16 GQA decode (batch 8, 32:8 heads, capacity 2048, lengths
+    U[128,2047], fused append); c3 = paged fp8 e4m3 decode with per-tensor
+    descales, sliding window 4096, softcap 50, sinks, 4-token verify window."""
+    import torch
+    from flywheel_tpu.softmax_attention import _native
+    from flywheel_tpu.testing import workloads
+    rng = np.random.default_rng(0)
+    lib = _native.library()
+    if name == "c1":
+        batch, hq, hk, cap, q_len = 8, 32, 8, 2048, 1
+        lens = rng.integers(128, 2048, batch).astype(np.int32)
+        kc = torch.randn((batch, cap, hk, D), device=device).to(torch.bfloat16)
+        vc = torch.randn((batch, cap, hk, D), device=device).to(torch.bfloat16)
+        q = torch.randn((batch, 1, hq, D), device=device).to(torch.bfloat16)
+        k = torch.randn((batch, 1, hk, D), device=device).to(torch.bfloat16)
+        v = torch.randn((batch, 1, hk, D), device=device).to(torch.bfloat16)
+        lens_t = torch.from_numpy(lens).to(device)
+        out = torch.empty_like(q)
+        args = _native.FwDecodeArgs(
+            q=q.data_ptr(), out=out.data_ptr(), kv_cache=kc.data_ptr(), v_cache=vc.data_ptr(),
+            k_new=k.data_ptr(), v_new=v.data_ptr(), cache_seqlens=lens_t.data_ptr(), num_pages=batch,
+            page_size=cap, pages_per_seq=1, batch=batch, seqlen_q=1, nheads=hq, nheads_k=hk, head_dim=D,
+            kv_dtype=0, causal=1, window_left=-1, softmax_scale=D ** -0.5, softcap=0.0)
+        kv_bytes = workloads.decode_kv_bytes(lens, 1, hk, D, 2)
+        keep = (kc, vc, q, k, v, lens_t, out)
+    else:
+        batch, hq, hk, q_len, window = 128, 64, 8, 4, 4095
+        lens = rng.integers(LEN_LO, LEN_HI + 1, batch).astype(np.int32)
+        table, pool_pages = workloads.paged_table(rng, lens, q_len, PAGE, slack=0.10)
+        pool = torch.empty((pool_pages, PAGE, 2 * hk, D), dtype=torch.float8_e4m3fn, device=device)
+        for lo in range(0, pool_pages, 8192):
+            hi = min(pool_pages, lo + 8192)
+            block = torch.randn((hi - lo, PAGE, 2 * hk, D), device=device)
+            pool[lo:hi] = (block * (448.0 / 5.5)).clamp(-448, 448).to(torch.float8_e4m3fn)
+        descale = torch.tensor([5.5 / 448.0], dtype=torch.float32, device=device)
+        q = torch.randn((batch, q_len, hq, D), device=device).to(torch.bfloat16)
+        k = (torch.randn((batch, q_len, hk, D), device=device) * (448.0 / 5.5)).to(torch.float8_e4m3fn)
+        v = (torch.randn((batch, q_len, hk, D), device=device) * (448.0 / 5.5)).to(torch.float8_e4m3fn)
+        sinks = torch.randn(hq, device=device)
+        lens_t, table_t = torch.from_numpy(lens).to(device), torch.from_numpy(table).to(device)
+        out = torch.empty_like(q)
+        args = _native.FwDecodeArgs(
+            q=q.data_ptr(), out=out.data_ptr(), kv_cache=pool.data_ptr(), k_new=k.data_ptr(),
+            v_new=v.data_ptr(), cache_seqlens=lens_t.data_ptr(), block_table=table_t.data_ptr(),
+            k_descale=descale.data_ptr(), v_descale=descale.data_ptr(), sinks=sinks.data_ptr(),
+            num_pages=pool_pages, page_size=PAGE, pages_per_seq=table.shape[1], batch=batch, seqlen_q=q_len,
+            nheads=hq, nheads_k=hk, head_dim=D, kv_dtype=1, causal=1, window_left=window,
+            softmax_scale=D ** -0.5, softcap=50.0)
+        kv_bytes = workloads.decode_kv_bytes(lens, q_len, hk, D, 1, window_left=window)
+        keep = (pool, descale, q, k, v, sinks, lens_t, table_t, out)
+    nbytes = lib.fw_decode_workspace_bytes(ctypes.byref(args))
+    if nbytes == 0:
+        raise RuntimeError(_native.last_error())
+    scratch = torch.zeros(nbytes, dtype=torch.uint8, device=device)
+    args.workspace, args.workspace_bytes = scratch.data_ptr(), nbytes
+    stream = torch.cuda.current_stream(device).cuda_stream
+    # c1 moves 36 MB per step: rotate nothing, but flush L2 between steps so the
+    # caches are read from HBM like in serving.
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=device) if kv_bytes < (512 << 20) else None
+    steps = max(ns.steps, 20)
+    times = []
+    for i in range(ns.warmup + steps):
+        if flush is not None:
+            flush.zero_()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        _native.check(lib.fw_decode_kvcache(ctypes.byref(args), stream))
+        end.record()
+        torch.cuda.synchronize()
+        if i >= ns.warmup:
+            times.append(start.elapsed_time(end))
+    if _native.read_status(scratch, device) != 0:
+        raise RuntimeError("decode kernel reported a device status")
+    ms = float(np.median(times))
+    hbm_peak, _, kind = measured_peaks()
+    del keep
+    return {"metric": "decode_kv_read_bandwidth", "config": {"workload": name,
+            "l2": "L2 flushed between steps" if flush is not None else "inputs exceed L2"},
+            "value": kv_bytes / (ms * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": ms, "steps": steps,
+            "algorithmic_bytes_per_launch": kv_bytes,
+            "roofline": {"bound": "hbm", "achieved": kv_bytes / (ms * 1e-3) / 1e9, "peak": hbm_peak,
+                         "frac": kv_bytes / (ms * 1e-3) / 1e9 / hbm_peak, "peak_kind": f"of {kind}"}}
+
+
 def make_decode_call(work, device):
     """A closure that enqueues one decode step through the C ABI on device
     buffers (no host traffic), and the output tensor it fills."""
@@ -408,6 +494,8 @@ def main():
     parser.add_argument("--skip-cpu-baseline", action="store_true")
     parser.add_argument("--skip-e2e", action="store_true")
     parser.add_argument("--skip-prefill", action="store_true")
+    parser.add_argument("--config", choices=["c1", "c3"], default=None,
+                        help="run one secondary decode configuration instead of the headline")
     parser.add_argument("--long-context", action="store_true",
                         help="run the single-request 128K-token decode split over the GPUs")
     parser.add_argument("--prefill-only", action="store_true",
@@ -438,6 +526,9 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
+    if ns.config:
+        print(json.dumps(bench_config(ns, ns.config, device)))
+        return
     if ns.long_context:
         result = bench_long_context(ns, device, rank, world, barrier)
         if rank == 0:
