@@ -585,20 +585,26 @@ struct CombineParams {
 
 constexpr int kCombineWarps = 4;
 
-// One block per (request, group of kCombineWarps rows); a warp merges the
-// segments of one (token, head) row.  Reads the tile prefix the decode kernel
-// left in the workspace, so the two agree on which CTAs touched the request.
+// Merges the segments of (token, head) rows.  WPR warps share one row and split
+// its segments between them: 1 when there are many rows with few segments
+// each (serving batches), 4 when few rows have many segments (one long
+// request cut over every SM).  Reads the tile prefix the decode kernel left in
+// the workspace, so the two agree on which CTAs touched the request.
+template <int WPR>
 __global__ void __launch_bounds__(kCombineWarps * 32) combine_kernel(const CombineParams cp) {
   const DecodeParams& p = cp.d;
+  __shared__ float4 red_acc[kCombineWarps][32];
+  __shared__ float red_den[kCombineWarps];
   const int b = blockIdx.x;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int warp_in_block = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int sub = warp_in_block % WPR, warp = warp_in_block / WPR;
   const int n_active = load_num_active(p);
   const int before = p.tile_prefix[b];
   const int total_tiles = p.tile_prefix[p.batch];
   const Span sp = request_span(p, b, n_active);
   const int rq = p.seqlen_q * p.nheads;
-  const int row = blockIdx.y * kCombineWarps + warp;
-  if (row >= rq) return;
+  const int row = blockIdx.y * (kCombineWarps / WPR) + warp;
+  if (row >= rq) return;  // with WPR > 1 a block holds one row: all its warps leave together
   const int t = row / p.nheads, hq = row - t * p.nheads;
   if (t >= sp.q_valid) return;  // not a real query row of this item
 
@@ -632,20 +638,35 @@ __global__ void __launch_bounds__(kCombineWarps * 32) combine_kernel(const Combi
   float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
   float den = 0.f;
   if (m_max != -INFINITY) {
-    for (int c = c_lo; c <= c_hi; ++c) {
+    // Branch-free body so the loads of several segments are in flight at once.
+#pragma unroll 4
+    for (int c = c_lo + sub; c <= c_hi; c += WPR) {
       int f0, f1;
       cta_range(total_tiles, p.ncta, c, f0, f1);
-      if (f1 <= f0) continue;
       const long long prow = (static_cast<long long>(b) + c) * rq + row;
-      const float m = p.part_ml[prow * 2];
-      if (m == -INFINITY) continue;
-      const float w = fast_exp2(m - m_max);
-      den += p.part_ml[prow * 2 + 1] * w;
+      const float2 ml = *reinterpret_cast<const float2*>(p.part_ml + prow * 2);
       const float4 o = *reinterpret_cast<const float4*>(p.part_o + prow * kHeadDim + lane * 4);
-      acc.x += o.x * w;
-      acc.y += o.y * w;
-      acc.z += o.z * w;
-      acc.w += o.w * w;
+      const float w = (f1 > f0 && ml.x != -INFINITY) ? fast_exp2(ml.x - m_max) : 0.f;
+      den += w == 0.f ? 0.f : ml.y * w;
+      acc.x += w == 0.f ? 0.f : o.x * w;
+      acc.y += w == 0.f ? 0.f : o.y * w;
+      acc.z += w == 0.f ? 0.f : o.z * w;
+      acc.w += w == 0.f ? 0.f : o.w * w;
+    }
+  }
+  if constexpr (WPR > 1) {
+    red_acc[warp_in_block][lane] = acc;
+    if (lane == 0) red_den[warp_in_block] = den;
+    __syncthreads();
+    if (sub != 0) return;
+#pragma unroll
+    for (int w = 1; w < WPR; ++w) {
+      const float4 o = red_acc[warp * WPR + w][lane];
+      acc.x += o.x;
+      acc.y += o.y;
+      acc.z += o.z;
+      acc.w += o.w;
+      den += red_den[warp * WPR + w];
     }
   }
 
@@ -902,8 +923,16 @@ static int launch_decode(DecodePlan& plan, void* workspace, cudaStream_t stream,
   cp.partial_lse = partial_lse;
   cp.v_descale = v_descale;
   cp.sinks = sinks;
-  dim3 cgrid(p.batch, (plan.rows_q + kCombineWarps - 1) / kCombineWarps);
-  combine_kernel<<<cgrid, kCombineWarps * 32, 0, stream>>>(cp);
+  // Few rows with many segments each (a long request over every SM): let four
+  // warps share a row.
+  const bool wide = static_cast<long long>(p.batch) * plan.rows_q <= 2048;
+  if (wide) {
+    dim3 cgrid(p.batch, plan.rows_q);
+    combine_kernel<kCombineWarps><<<cgrid, kCombineWarps * 32, 0, stream>>>(cp);
+  } else {
+    dim3 cgrid(p.batch, (plan.rows_q + kCombineWarps - 1) / kCombineWarps);
+    combine_kernel<1><<<cgrid, kCombineWarps * 32, 0, stream>>>(cp);
+  }
   err = cudaGetLastError();
   if (err != cudaSuccess) {
     set_error("combine kernel launch: %s", cudaGetErrorString(err));

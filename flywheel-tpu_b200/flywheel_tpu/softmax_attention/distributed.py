@@ -100,10 +100,41 @@ class ShardedDecoder:
         """One decode step: q (1, 1, nheads, d), new k / v (1, 1, nheads_k, d),
         `global_len` tokens cached before the step.  Returns (out, lse); the new
         token is appended on the rank that owns its page."""
-        rows, d = self.nheads, self.head_dim
         owner = owner_of_page(self.total_pages, self.world, global_len // self.page_size)
-        appends = owner == self.rank
         self.local_len.fill_(local_length(global_len, self.page_size, self.first_page, self.last_page))
+        return self._enqueue(q, k, v, owner == self.rank)
+
+    def capture(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, global_len: int,
+                steps: int) -> torch.cuda.CUDAGraph:
+        """A CUDA graph of one decode step for the next `steps` positions, which
+        must all fall in pages of one rank (so which rank appends is fixed).  The
+        cached length lives on the device and the owning rank advances it inside
+        the graph; q / k / v are read from the given tensors at every replay, so
+        refill them in place between replays.  A step is latency-bound (tens of
+        microseconds of HBM time), so launching it as one graph matters."""
+        first_owner = owner_of_page(self.total_pages, self.world, global_len // self.page_size)
+        last_owner = owner_of_page(self.total_pages, self.world,
+                                   (global_len + steps - 1) // self.page_size)
+        if first_owner != last_owner:
+            raise ValueError("the captured steps must stay within one rank's pages")
+        appends = first_owner == self.rank
+        self.local_len.fill_(local_length(global_len, self.page_size, self.first_page, self.last_page))
+        side = torch.cuda.Stream(self.device)
+        side.wait_stream(torch.cuda.current_stream(self.device))
+        with torch.cuda.stream(side):            # warm-up outside capture
+            self._enqueue(q, k, v, appends)
+        torch.cuda.current_stream(self.device).wait_stream(side)
+        torch.cuda.synchronize(self.device)
+        self.local_len.fill_(local_length(global_len, self.page_size, self.first_page, self.last_page))
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            self._enqueue(q, k, v, appends)
+            if appends:
+                self.local_len.add_(1)
+        return graph
+
+    def _enqueue(self, q, k, v, appends):
+        rows, d = self.nheads, self.head_dim
         partial_out = self.state[: rows * d]
         partial_lse = self.state[rows * d:]
         args = _native.FwDecodeArgs(
