@@ -409,86 +409,81 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       tc_fence_after();
       const bool need_mask = pos0 + kBN > min(diag_lo, kv_end) ||
                              (p.window_left >= 0 && pos0 < diag_hi - p.window_left);
-      const bool rewrite = need_mask || p.softcap > 0.f;
-      // Pass 1 over the two 64-key halves of the row (warp-uniform variants):
-      // softcap transform and mask, written back to tensor memory only when
-      // they changed something, and the row max.  Without a softcap the raw
-      // scores stay in place and the scale rides in pass 2's FMA (c1 > 0, so the
-      // max commutes with the scale).
-      float mx = -INFINITY;
+      // One pass per 64-key half: load S, softcap / mask (warp-uniform code
+      // variants), P = 2^(s * mul - base) against the CURRENT exponent base, and
+      // the row max of the exponents.  The base only has to move when a score
+      // outruns it by more than kRescaleThreshold (or on the first tile): then
+      // the tile is redone against the new base and O is rescaled.  So the
+      // common tile reads S once and needs no separate max pass.
+      uint32_t packed[2][32];
+      float sum0, sum1, top;
+      auto exponentiate = [&](float neg_base) {
+        sum0 = sum1 = 0.f;
+        float top0 = -INFINITY, top1 = -INFINITY;
 #pragma unroll
-      for (int half = 0; half < 2; ++half) {
-        uint32_t sr[2][32];
-        tmem_ld32(s_addr + half * 64, sr[0]);
-        tmem_ld32(s_addr + half * 64 + 32, sr[1]);
-        tmem_wait_ld();
-        const int hpos = pos0 + half * 64;
-        float hm;
-        if (p.softcap > 0.f) {
-          hm = need_mask ? transform_row<true, true>(sr, c1, c2, hpos, kv_end, diag, p.causal, p.window_left)
-                         : transform_row<true, false>(sr, c1, c2, hpos, kv_end, diag, p.causal, p.window_left);
-        } else {
-          hm = need_mask ? transform_row<false, true>(sr, c1, c2, hpos, kv_end, diag, p.causal, p.window_left)
-                         : transform_row<false, false>(sr, c1, c2, hpos, kv_end, diag, p.causal, p.window_left);
-        }
-        if (rewrite) {
-          tmem_st32(s_addr + half * 64, sr[0]);
-          tmem_st32(s_addr + half * 64 + 32, sr[1]);
-        }
-        mx = fmaxf(mx, hm);
-      }
-      if (rewrite) tmem_wait_st();
-      if (!(p.softcap > 0.f)) mx *= c1;
-      // Lazy rescale: the exponent base only moves when the row max outruns it
-      // by more than kRescaleThreshold, so O in tensor memory is rarely touched.
-      float alpha = 1.f;
-      if (mx > m_used + kRescaleThreshold || (m_used == -INFINITY && mx > -INFINITY)) {
-        alpha = fast_exp2(m_used - mx);  // 0 when m_used was -inf
-        m_used = mx;
-      }
-      const float neg_base = m_used == -INFINITY ? 0.f : -m_used;
-      if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
-        // PV(j-1) of this stream precedes QK(j) in the tensor pipe, so it has
-        // drained; the wait makes its writes to O visible here.
-        if (!FW_WAIT(10 + t, j, &bars->pv_done[t], (j - 1) & 1)) {
-          ok = false;
-          break;
-        }
-        tc_fence_after();
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          uint32_t o[32];
-          tmem_ld32(o_addr + c * 32, o);
+        for (int half = 0; half < 2; ++half) {
+          uint32_t sr[2][32];
+          tmem_ld32(s_addr + half * 64, sr[0]);
+          tmem_ld32(s_addr + half * 64 + 32, sr[1]);
           tmem_wait_ld();
-#pragma unroll
-          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-          tmem_st32(o_addr + c * 32, o);
-        }
-        tmem_wait_st();
-      }
-      // Pass 2: P = 2^(s * mul - m) as bf16 pairs, written over the start of S
-      // (two keys per 32-bit column: the A operand of the PV MMA).  Half 0's P
-      // lands on columns this thread has already read; half 1's S columns
-      // [64, 128) are untouched until read.
-      float sum0 = 0.f, sum1 = 0.f;
-#pragma unroll
-      for (int half = 0; half < 2; ++half) {
-        uint32_t sr[2][32], packed[32];
-        tmem_ld32(s_addr + half * 64, sr[0]);
-        tmem_ld32(s_addr + half * 64 + 32, sr[1]);
-        tmem_wait_ld();
-#pragma unroll
-        for (int c = 0; c < 2; ++c)
-#pragma unroll
-          for (int i = 0; i < 32; i += 2) {
-            const float p0 = fast_exp2(fmaf(__uint_as_float(sr[c][i]), mul, neg_base));
-            const float p1 = fast_exp2(fmaf(__uint_as_float(sr[c][i + 1]), mul, neg_base));
-            sum0 += p0;
-            sum1 += p1;
-            packed[c * 16 + (i >> 1)] = pack_bf16(p0, p1);
+          const int hpos = pos0 + half * 64;
+          if (p.softcap > 0.f) {
+            if (need_mask) transform_row<true, true>(sr, c1, c2, hpos, kv_end, diag, p.causal, p.window_left);
+            else transform_row<true, false>(sr, c1, c2, hpos, kv_end, diag, p.causal, p.window_left);
+          } else if (need_mask) {
+            transform_row<false, true>(sr, c1, c2, hpos, kv_end, diag, p.causal, p.window_left);
           }
-        tmem_st32(s_addr + half * 32, packed);
+#pragma unroll
+          for (int c = 0; c < 2; ++c)
+#pragma unroll
+            for (int i = 0; i < 32; i += 2) {
+              const float y0 = fmaf(__uint_as_float(sr[c][i]), mul, neg_base);
+              const float y1 = fmaf(__uint_as_float(sr[c][i + 1]), mul, neg_base);
+              top0 = fmaxf(top0, y0);
+              top1 = fmaxf(top1, y1);
+              const float p0 = fast_exp2(y0), p1 = fast_exp2(y1);
+              sum0 += p0;
+              sum1 += p1;
+              packed[half][c * 16 + (i >> 1)] = pack_bf16(p0, p1);
+            }
+        }
+        top = fmaxf(top0, top1);  // row max minus the base (the row max itself when the base is 0)
+      };
+      float alpha = 1.f;
+      float neg_base = m_used == -INFINITY ? 0.f : -m_used;
+      exponentiate(neg_base);
+      const bool move_base = m_used == -INFINITY ? top > -INFINITY : top > kRescaleThreshold;
+      if (__any_sync(0xffffffffu, move_base)) {
+        if (move_base) {
+          const float mx = top - neg_base;
+          alpha = fast_exp2(m_used - mx);  // 0 when there was no base yet
+          m_used = mx;
+          neg_base = -mx;
+        }
+        exponentiate(neg_base);  // lanes whose base stayed put get the same P again
+        if (j > 0) {
+          // PV(j-1) of this stream precedes QK(j) in the tensor pipe, so it has
+          // drained; the wait makes its writes to O visible here.
+          if (!FW_WAIT(10 + t, j, &bars->pv_done[t], (j - 1) & 1)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            uint32_t o[32];
+            tmem_ld32(o_addr + c * 32, o);
+            tmem_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+            tmem_st32(o_addr + c * 32, o);
+          }
+        }
       }
+      // P over the start of S: two bf16 keys per 32-bit column, the A operand of
+      // the PV MMA.  (All of this thread's S row has been read by now.)
+      tmem_st32(s_addr, packed[0]);
+      tmem_st32(s_addr + 32, packed[1]);
       l_run = l_run * alpha + (sum0 + sum1);
       tmem_wait_st();
       // Last tile: keys past the valid length may hold anything (NaN included);
