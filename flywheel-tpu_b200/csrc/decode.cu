@@ -28,7 +28,7 @@
 
 namespace fw {
 
-constexpr int kTile = 16;          // tokens per pipeline stage
+constexpr int kTile = 16;          // smallest stage: tokens per MMA k-step; page sizes are multiples of it
 constexpr int kMaxStages = 8;
 constexpr int kMaxConsumerWarps = 8;
 constexpr int kHeadDim = 128;
@@ -57,6 +57,7 @@ struct DecodeParams {
   int plane_bytes;  // head_dim * itemsize
   int spp;          // 128-byte segments per head plane
   int stages, stage_bytes;
+  int tile;         // tokens per pipeline stage (16, 32 or 64)
   int has_new, causal, window_left;
   int zero_pad_head;  // fp8 merged pool with an odd nheads_k: append zeroes the pad head
   float scale, softcap;
@@ -91,8 +92,8 @@ __device__ __forceinline__ Span request_span(const DecodeParams& p, int b, int n
     s.diag_base = s.total - p.seqlen_q;
     if (s.q_valid <= 0 || s.kv_end <= 0) return s;
     const int first_key = (p.window_left >= 0) ? max(0, s.diag_base - p.window_left) : 0;
-    s.first_tile = first_key / kTile;
-    s.n_tiles = max(0, (s.kv_end + kTile - 1) / kTile - s.first_tile);
+    s.first_tile = first_key / p.tile;
+    s.n_tiles = max(0, (s.kv_end + p.tile - 1) / p.tile - s.first_tile);
     return s;
   }
   if (b >= n_active) return s;
@@ -103,8 +104,8 @@ __device__ __forceinline__ Span request_span(const DecodeParams& p, int b, int n
   s.diag_base = s.total - p.seqlen_q;
   if (s.total <= 0) return s;
   int first_key = (p.window_left >= 0) ? max(0, s.total - p.seqlen_q - p.window_left) : 0;
-  s.first_tile = first_key / kTile;
-  s.n_tiles = (s.total + kTile - 1) / kTile - s.first_tile;
+  s.first_tile = first_key / p.tile;
+  s.n_tiles = (s.total + p.tile - 1) / p.tile - s.first_tile;
   return s;
 }
 
@@ -160,11 +161,12 @@ __device__ __forceinline__ int v_seg(const DecodeParams& p, int hl) {
   return p.merged ? (2 * hl + 1) * p.spp : (p.hpc + hl) * p.spp;
 }
 
-template <int KVT>
+template <int KVT, int TILE>
 __global__ void __launch_bounds__((kMaxConsumerWarps + 1) * 32, 1)
 decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
               const DecodeParams p) {
   constexpr bool kFp8 = KVT != FW_DTYPE_BF16;
+  constexpr int NU = TILE / 16;  // 16-key MMA sub-tiles per stage
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
@@ -214,7 +216,7 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
       const int seg_end = min(f1, pre[b + 1]);
       int cur_page_idx = -1, cur_page = 0;
       for (; f < seg_end; ++f) {
-        const int pos0 = (f - pre[b] + sp.first_tile) * kTile;
+        const int pos0 = (f - pre[b] + sp.first_tile) * TILE;
         const int page_idx = pos0 / p.page_size;
         if (page_idx != cur_page_idx) {
           cur_page_idx = page_idx;
@@ -278,7 +280,7 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
   const int t0 = row0 / p.group, g0 = row0 - t0 * p.group;
   const int t1 = row1 / p.group, g1 = row1 - t1 * p.group;
   const int rq = p.seqlen_q * p.nheads;      // partial rows per slot
-  const int seg_bytes = kTile * 128;
+  const int seg_bytes = TILE * 128;
   const uint32_t stage_u32 = smem_u32(stage_base);
   const int kseg = k_seg(p, hl), vseg = v_seg(p, hl);
 
@@ -337,7 +339,7 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
     const int diag0 = sp.diag_base + t0, diag1 = sp.diag_base + t1;
 
     for (; f < seg_end; ++f) {
-      const int pos0 = (f - pre[b] + sp.first_tile) * kTile;
+      const int pos0 = (f - pre[b] + sp.first_tile) * TILE;
       if (!mbar_wait_bounded(&full_bar[stage], phase, abort_flag)) {
         ok = false;
         break;
@@ -347,9 +349,9 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
 
       // ---- boundary tile: patch in the new tokens (and write them to their
       // page), and zero V rows past the valid length so 0 * NaN never forms.
-      if (pos0 + kTile > sp.cache_len) {
+      if (pos0 + TILE > sp.cache_len) {
         const int chunks = p.plane_bytes >> 4;  // 16-byte chunks per head plane
-        for (int tk = 0; tk < kTile; ++tk) {
+        for (int tk = 0; tk < TILE; ++tk) {
           const int pos = pos0 + tk;
           if (pos < sp.cache_len) continue;
           const bool is_new = p.has_new && pos < sp.total;
@@ -398,11 +400,18 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
         __syncwarp();
       }
 
-      // ---- S = Q K^T for 16 keys (two 8-key n-tiles)
-      float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+      // ---- S = Q K^T: NU sub-tiles of 16 keys (two 8-key n-tiles each), all
+      // independent accumulators, so the MMAs of a stage pipeline.
+      float s[NU][2][4];
+#pragma unroll
+      for (int u = 0; u < NU; ++u)
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt) s[u][nt][0] = s[u][nt][1] = s[u][nt][2] = s[u][nt][3] = 0.f;
+#pragma unroll
+      for (int u = 0; u < NU; ++u) {
       if constexpr (!kFp8) {
         const int mi = lane >> 3;
-        const int key = ((mi >> 1) << 3) + (lane & 7);
+        const int key = u * 16 + ((mi >> 1) << 3) + (lane & 7);
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks) {
           const int chunk = ks * 2 + (mi & 1);
@@ -410,46 +419,51 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
                                 (((chunk & 7) ^ (key & 7)) << 4);
           uint32_t r0, r1, r2, r3;
           ldmatrix_x4(addr, r0, r1, r2, r3);
-          mma_bf16(s[0], qa[ks], r0, r1);
-          mma_bf16(s[1], qa[ks], r2, r3);
+          mma_bf16(s[u][0], qa[ks], r0, r1);
+          mma_bf16(s[u][1], qa[ks], r2, r3);
         }
       } else {
         const int mi = lane >> 3;
-        const int key = ((mi & 1) << 3) + (lane & 7);
+        const int key = u * 16 + ((mi & 1) << 3) + (lane & 7);
 #pragma unroll
         for (int kp = 0; kp < 4; ++kp) {
           const int chunk = kp * 2 + (mi >> 1);
           const uint32_t addr = st + kseg * seg_bytes + key * 128 + (((chunk & 7) ^ (key & 7)) << 4);
           uint32_t r0, r1, r2, r3;  // (keys 0-7, c), (keys 8-15, c), (keys 0-7, c+1), (keys 8-15, c+1)
           ldmatrix_x4(addr, r0, r1, r2, r3);
-          mma_f16(s[0], qa[2 * kp], fp8x2_to_f16x2<KVT>(r0 & 0xffff), fp8x2_to_f16x2<KVT>(r0 >> 16));
-          mma_f16(s[1], qa[2 * kp], fp8x2_to_f16x2<KVT>(r1 & 0xffff), fp8x2_to_f16x2<KVT>(r1 >> 16));
-          mma_f16(s[0], qa[2 * kp + 1], fp8x2_to_f16x2<KVT>(r2 & 0xffff), fp8x2_to_f16x2<KVT>(r2 >> 16));
-          mma_f16(s[1], qa[2 * kp + 1], fp8x2_to_f16x2<KVT>(r3 & 0xffff), fp8x2_to_f16x2<KVT>(r3 >> 16));
+          mma_f16(s[u][0], qa[2 * kp], fp8x2_to_f16x2<KVT>(r0 & 0xffff), fp8x2_to_f16x2<KVT>(r0 >> 16));
+          mma_f16(s[u][1], qa[2 * kp], fp8x2_to_f16x2<KVT>(r1 & 0xffff), fp8x2_to_f16x2<KVT>(r1 >> 16));
+          mma_f16(s[u][0], qa[2 * kp + 1], fp8x2_to_f16x2<KVT>(r2 & 0xffff), fp8x2_to_f16x2<KVT>(r2 >> 16));
+          mma_f16(s[u][1], qa[2 * kp + 1], fp8x2_to_f16x2<KVT>(r3 & 0xffff), fp8x2_to_f16x2<KVT>(r3 >> 16));
         }
+      }
       }
 
       // ---- scale (+ softcap), mask
 #pragma unroll
+      for (int u = 0; u < NU; ++u)
+#pragma unroll
       for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-          float x = s[nt][i] * c1;
+          float x = s[u][nt][i] * c1;
           if (p.softcap > 0.f) x = accurate_tanh(x) * c2;
-          s[nt][i] = x;
+          s[u][nt][i] = x;
         }
-      const bool mask_right = pos0 + kTile > min(sp.diag_base, sp.kv_end);
+      const bool mask_right = pos0 + TILE > min(sp.diag_base, sp.kv_end);
       const bool mask_left = p.window_left >= 0 && pos0 < sp.total - 1 - p.window_left;
       if (mask_right || mask_left) {
+#pragma unroll
+        for (int u = 0; u < NU; ++u)
 #pragma unroll
         for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
-            const int j = pos0 + nt * 8 + 2 * tq + (i & 1);
+            const int j = pos0 + u * 16 + nt * 8 + 2 * tq + (i & 1);
             const int diag = (i < 2) ? diag0 : diag1;
             bool vis = j < sp.kv_end && (!p.causal || j <= diag);
             if (p.window_left >= 0) vis = vis && (j >= diag - p.window_left);
-            if (!vis) s[nt][i] = -INFINITY;
+            if (!vis) s[u][nt][i] = -INFINITY;
           }
       }
 
@@ -457,7 +471,10 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
       float alpha[2];
 #pragma unroll
       for (int r = 0; r < 2; ++r) {
-        float mx = fmaxf(fmaxf(s[0][2 * r], s[0][2 * r + 1]), fmaxf(s[1][2 * r], s[1][2 * r + 1]));
+        float mx = -INFINITY;
+#pragma unroll
+        for (int u = 0; u < NU; ++u)
+          mx = fmaxf(mx, fmaxf(fmaxf(s[u][0][2 * r], s[u][0][2 * r + 1]), fmaxf(s[u][1][2 * r], s[u][1][2 * r + 1])));
         mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
         mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
         const float m_new = fmaxf(m_run[r], mx);
@@ -466,10 +483,12 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
         m_run[r] = m_new;
         float sum = 0.f;
 #pragma unroll
+        for (int u = 0; u < NU; ++u)
+#pragma unroll
         for (int nt = 0; nt < 2; ++nt) {
-          s[nt][2 * r] = fast_exp2(s[nt][2 * r] - base);
-          s[nt][2 * r + 1] = fast_exp2(s[nt][2 * r + 1] - base);
-          sum += s[nt][2 * r] + s[nt][2 * r + 1];
+          s[u][nt][2 * r] = fast_exp2(s[u][nt][2 * r] - base);
+          s[u][nt][2 * r + 1] = fast_exp2(s[u][nt][2 * r + 1] - base);
+          sum += s[u][nt][2 * r] + s[u][nt][2 * r + 1];
         }
         l_run[r] = l_run[r] * alpha[r] + sum;
       }
@@ -483,15 +502,17 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
         }
       }
 
-      // ---- O += P V
+      // ---- O += P V, one 16-key k-step per sub-tile
+#pragma unroll
+      for (int u = 0; u < NU; ++u) {
       uint32_t pa[4];
       if constexpr (!kFp8) {
-        pa[0] = pack_bf16(s[0][0], s[0][1]);
-        pa[1] = pack_bf16(s[0][2], s[0][3]);
-        pa[2] = pack_bf16(s[1][0], s[1][1]);
-        pa[3] = pack_bf16(s[1][2], s[1][3]);
+        pa[0] = pack_bf16(s[u][0][0], s[u][0][1]);
+        pa[1] = pack_bf16(s[u][0][2], s[u][0][3]);
+        pa[2] = pack_bf16(s[u][1][0], s[u][1][1]);
+        pa[3] = pack_bf16(s[u][1][2], s[u][1][3]);
         const int mi = lane >> 3;
-        const int key = ((mi & 1) << 3) + (lane & 7);
+        const int key = u * 16 + ((mi & 1) << 3) + (lane & 7);
 #pragma unroll
         for (int cp = 0; cp < 8; ++cp) {
           const int chunk = cp * 2 + (mi >> 1);
@@ -503,12 +524,12 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
           mma_bf16(o[2 * cp + 1], pa, r2, r3);
         }
       } else {
-        pa[0] = pack_f16(s[0][0], s[0][1]);
-        pa[1] = pack_f16(s[0][2], s[0][3]);
-        pa[2] = pack_f16(s[1][0], s[1][1]);
-        pa[3] = pack_f16(s[1][2], s[1][3]);
+        pa[0] = pack_f16(s[u][0][0], s[u][0][1]);
+        pa[1] = pack_f16(s[u][0][2], s[u][0][3]);
+        pa[2] = pack_f16(s[u][1][0], s[u][1][1]);
+        pa[3] = pack_f16(s[u][1][2], s[u][1][3]);
         const int mi = lane >> 3;
-        const int key = ((mi & 1) << 3) + (lane & 7);
+        const int key = u * 16 + ((mi & 1) << 3) + (lane & 7);
 #pragma unroll
         for (int cp = 0; cp < 4; ++cp) {
           const int chunk = cp * 2 + (mi >> 1);
@@ -526,6 +547,7 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
           mma_f16(o[4 * cp + 2], pa, fp8x2_to_f16x2<KVT>(r2 & 0xffff), fp8x2_to_f16x2<KVT>(r3 & 0xffff));
           mma_f16(o[4 * cp + 3], pa, fp8x2_to_f16x2<KVT>(r2 >> 16), fp8x2_to_f16x2<KVT>(r3 >> 16));
         }
+      }
       }
 
       __syncwarp();
@@ -817,8 +839,19 @@ static int plan_decode(const FwDecodeArgs* a, DecodePlan* plan, int max_batch = 
   p.zero_pad_head = paged && cache_heads != 2 * a->nheads_k;
   p.row_bytes = cache_heads * p.plane_bytes;
   const int segs_per_stage = p.hpc * 2 * p.spp;
-  p.stage_bytes = segs_per_stage * kTile * 128;
+  // Stage size: 16 tokens for bf16 rows (64 KiB for 8 heads).  fp8 rows are half
+  // as wide and cost twice the conversion work per byte, which makes the kernel
+  // latency-bound rather than bound by bytes in flight: they take as many
+  // tokens per stage as fit 64 KiB (up to 64) so each warp has independent
+  // MMAs to pipeline.  (Registers allow one CTA per SM either way.)  The stage
+  // must divide the page.
+  p.tile = kTile;
   const int smem_budget = 200 * 1024;
+  if (itemsize == 1) {
+    while (p.tile < 64 && segs_per_stage * (p.tile * 2) * 128 <= 64 * 1024 && a->page_size % (p.tile * 2) == 0)
+      p.tile *= 2;
+  }
+  p.stage_bytes = segs_per_stage * p.tile * 128;
   p.stages = min(kMaxStages, smem_budget / p.stage_bytes);
   if (p.stages < 2) {
     set_error("stage of %d bytes leaves fewer than two pipeline stages.", p.stage_bytes);
@@ -892,15 +925,26 @@ static int launch_decode(DecodePlan& plan, void* workspace, cudaStream_t stream,
   const uint64_t dims[4] = {128, static_cast<uint64_t>(p.page_size), segs, static_cast<uint64_t>(p.num_pages)};
   const uint64_t strides[3] = {static_cast<uint64_t>(p.row_bytes), 128,
                                static_cast<uint64_t>(p.page_size) * p.row_bytes};
-  const uint32_t box[4] = {128, kTile, static_cast<uint32_t>(p.merged ? p.hpc * 2 * p.spp : p.hpc * p.spp), 1};
+  const uint32_t box[4] = {128, static_cast<uint32_t>(p.tile),
+                           static_cast<uint32_t>(p.merged ? p.hpc * 2 * p.spp : p.hpc * p.spp), 1};
   rc = encode_tensor_map_u8_4d(&map_k, p.k_base, dims, strides, box);
   if (rc != FW_OK) return rc;
   rc = encode_tensor_map_u8_4d(&map_v, p.v_base, dims, strides, box);
   if (rc != FW_OK) return rc;
 
-  auto kernel = kv_dtype == FW_DTYPE_BF16   ? decode_kernel<FW_DTYPE_BF16>
-                : kv_dtype == FW_DTYPE_E4M3 ? decode_kernel<FW_DTYPE_E4M3>
-                                               : decode_kernel<FW_DTYPE_E5M2>;
+  using Kernel = void (*)(const CUtensorMap, const CUtensorMap, const DecodeParams);
+  Kernel kernel = nullptr;
+  if (kv_dtype == FW_DTYPE_BF16) {
+    kernel = decode_kernel<FW_DTYPE_BF16, 16>;
+  } else if (kv_dtype == FW_DTYPE_E4M3) {
+    kernel = p.tile == 64   ? decode_kernel<FW_DTYPE_E4M3, 64>
+             : p.tile == 32 ? decode_kernel<FW_DTYPE_E4M3, 32>
+                            : decode_kernel<FW_DTYPE_E4M3, 16>;
+  } else {
+    kernel = p.tile == 64   ? decode_kernel<FW_DTYPE_E5M2, 64>
+             : p.tile == 32 ? decode_kernel<FW_DTYPE_E5M2, 32>
+                            : decode_kernel<FW_DTYPE_E5M2, 16>;
+  }
   cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          static_cast<int>(plan.smem));
   if (err != cudaSuccess) {
