@@ -61,6 +61,43 @@ __global__ void __launch_bounds__(256) append_kernel(const AppendParams p) {
   }
 }
 
+struct WritePagesParams {
+  uint8_t* pool;
+  const uint8_t* k_new;
+  const uint8_t* v_new;
+  const int* slices;
+  const int* num_slices;
+  long long cache_rows;
+  int num_columns, total_tokens, nheads_k, plane_bytes, row_bytes;
+};
+
+// One block column per slice-table column; the blocks of a column stride over
+// its (row, 16-byte chunk) pairs.
+__global__ void __launch_bounds__(256) write_pages_kernel(const WritePagesParams p) {
+  const int column = blockIdx.x;
+  if (column >= min(*p.num_slices, p.num_columns)) return;
+  const int cache_row0 = p.slices[column];
+  const int new_row0 = p.slices[p.num_columns + column];
+  const int length = p.slices[2 * p.num_columns + column];
+  const int chunks_per_row = p.row_bytes >> 4, chunks_per_plane = p.plane_bytes >> 4;
+  const long long total = static_cast<long long>(max(length, 0)) * chunks_per_row;
+  for (long long idx = blockIdx.y * static_cast<long long>(blockDim.x) + threadIdx.x; idx < total;
+       idx += static_cast<long long>(gridDim.y) * blockDim.x) {
+    const int r = static_cast<int>(idx / chunks_per_row);
+    const int within = static_cast<int>(idx - static_cast<long long>(r) * chunks_per_row);
+    const long long cache_row = static_cast<long long>(cache_row0) + r;
+    const int tok = new_row0 + r;
+    if (cache_row < 0 || cache_row >= p.cache_rows || tok < 0 || tok >= p.total_tokens) continue;
+    const int plane = within / chunks_per_plane, c = within - plane * chunks_per_plane;
+    const int h = plane >> 1, is_v = plane & 1;
+    uint4 val = make_uint4(0u, 0u, 0u, 0u);
+    if (h < p.nheads_k)
+      val = *reinterpret_cast<const uint4*>((is_v ? p.v_new : p.k_new) +
+                                            (static_cast<long long>(tok) * p.nheads_k + h) * p.plane_bytes + (c << 4));
+    *reinterpret_cast<uint4*>(p.pool + cache_row * p.row_bytes + (static_cast<long long>(within) << 4)) = val;
+  }
+}
+
 struct MergeParams {
   const float* partial_out;
   const float* partial_lse;
@@ -162,6 +199,57 @@ extern "C" int fw_append_ragged(const FwAppendArgs* a, void* stream_ptr) {
   cudaError_t err = cudaGetLastError();
   if (err != cudaSuccess) {
     set_error("append kernel launch: %s", cudaGetErrorString(err));
+    return FW_ERR_LAUNCH;
+  }
+  return FW_OK;
+}
+
+extern "C" int fw_write_kv_pages(const FwWritePagesArgs* a, void* stream_ptr) {
+  if (a == nullptr || a->kv_cache == nullptr || a->k_new == nullptr || a->v_new == nullptr ||
+      a->slices == nullptr || a->num_slices == nullptr) {
+    set_error("kv_cache, k, v, slices and num_slices must not be NULL.");
+    return FW_ERR_BAD_SHAPE;
+  }
+  if (a->kv_dtype != FW_DTYPE_BF16 && a->kv_dtype != FW_DTYPE_E4M3 && a->kv_dtype != FW_DTYPE_E5M2) {
+    set_error("kv_dtype must be bf16, e4m3 or e5m2; got %d", a->kv_dtype);
+    return FW_ERR_BAD_DTYPE;
+  }
+  if (a->nheads_k <= 0 || a->page_size <= 0 || a->num_pages <= 0 || a->num_columns < 0 || a->total_tokens < 0) {
+    set_error("nheads_k, page_size and num_pages must be positive.");
+    return FW_ERR_BAD_SHAPE;
+  }
+  const int itemsize = a->kv_dtype == FW_DTYPE_BF16 ? 2 : 1;
+  if ((a->head_dim * itemsize) % 16) {
+    set_error("head_dim * itemsize must be a multiple of 16 bytes; got head_dim %d.", a->head_dim);
+    return FW_ERR_BAD_SHAPE;
+  }
+  if ((reinterpret_cast<uintptr_t>(a->kv_cache) & 15) || (reinterpret_cast<uintptr_t>(a->k_new) & 15) ||
+      (reinterpret_cast<uintptr_t>(a->v_new) & 15)) {
+    set_error("kv_cache, k and v must be 16-byte aligned.");
+    return FW_ERR_BAD_SHAPE;
+  }
+  if (a->num_columns == 0 || a->total_tokens == 0) return FW_OK;
+  WritePagesParams p;
+  p.pool = static_cast<uint8_t*>(a->kv_cache);
+  p.k_new = static_cast<const uint8_t*>(a->k_new);
+  p.v_new = static_cast<const uint8_t*>(a->v_new);
+  p.slices = a->slices;
+  p.num_slices = a->num_slices;
+  p.cache_rows = a->num_pages * a->page_size;
+  p.num_columns = a->num_columns;
+  p.total_tokens = a->total_tokens;
+  p.nheads_k = a->nheads_k;
+  const int heads_per_word = itemsize == 1 ? 2 : 1;
+  const int cache_heads = 2 * ((a->nheads_k + heads_per_word - 1) / heads_per_word * heads_per_word);
+  p.plane_bytes = a->head_dim * itemsize;
+  p.row_bytes = cache_heads * p.plane_bytes;
+  const long long chunks = static_cast<long long>(a->page_size) * (p.row_bytes >> 4);
+  const int per_column = static_cast<int>(chunks / 1024 < 1 ? 1 : (chunks / 1024 > 16 ? 16 : chunks / 1024));
+  dim3 grid(a->num_columns, per_column);
+  write_pages_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream_ptr)>>>(p);
+  cudaError_t err = cudaGetLastError();
+  if (err != cudaSuccess) {
+    set_error("page writer launch: %s", cudaGetErrorString(err));
     return FW_ERR_LAUNCH;
   }
   return FW_OK;

@@ -25,7 +25,103 @@ static int check_prefill_args(const FwPrefillArgs* a) {
     set_error("batch must be positive and total_q non-negative.");
     return FW_ERR_BAD_SHAPE;
   }
+  if ((a->rotary_cos == nullptr) != (a->rotary_sin == nullptr)) {
+    set_error("rotary_cos and rotary_sin must be provided together.");
+    return FW_ERR_BAD_SHAPE;
+  }
+  if (a->rotary_cos != nullptr && a->rotary_len <= 0) {
+    set_error("rotary tables need a positive rotary_len.");
+    return FW_ERR_BAD_SHAPE;
+  }
   return FW_OK;
+}
+
+// ---------------------------------------------------------------- Q-only RoPE
+// Rotates packed q into a scratch copy before attention: token t of request r
+// sits at position seqused_k[r] - len_q(r) + t (its own K/V position), the
+// rotation runs in f32 and rounds once to bf16.  Rows outside every request
+// and positions past the table are copied unrotated.
+struct RopeParams {
+  const __nv_bfloat16* q;
+  __nv_bfloat16* q_out;
+  const void* cos;
+  const void* sin;
+  const int* cu;
+  const int* seqused;
+  long long tok_stride, head_stride;
+  int batch, total_q, nheads, rotary_len, interleaved, table_bf16;
+};
+
+__device__ __forceinline__ float table_value(const void* table, long long index, int is_bf16) {
+  return is_bf16 ? __bfloat162float(static_cast<const __nv_bfloat16*>(table)[index])
+                 : static_cast<const float*>(table)[index];
+}
+
+// One thread per (token, head, pair of 8 elements): 128 / 16 = 8 threads per row.
+__global__ void __launch_bounds__(256) rope_q_kernel(const RopeParams p) {
+  const long long total = static_cast<long long>(p.total_q) * p.nheads * 8;
+  for (long long idx = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; idx < total;
+       idx += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int part = static_cast<int>(idx & 7);
+    const long long th = idx >> 3;
+    const int hq = static_cast<int>(th % p.nheads);
+    const int tok = static_cast<int>(th / p.nheads);
+    const long long base = static_cast<long long>(tok) * p.tok_stride + static_cast<long long>(hq) * p.head_stride;
+    // request owning the token: largest r with cu[r] <= tok
+    int lo = 0, hi = p.batch;
+    while (hi - lo > 1) {
+      const int mid = (lo + hi) >> 1;
+      if (p.cu[mid] <= tok) lo = mid; else hi = mid;
+    }
+    int pos = -1;
+    if (tok >= p.cu[lo] && tok < p.cu[lo + 1]) pos = p.seqused[lo] - (p.cu[lo + 1] - p.cu[lo]) + (tok - p.cu[lo]);
+    const bool rotate = pos >= 0 && pos < p.rotary_len;
+    // This thread's 8 pairs: split halves pair element i with i + 64;
+    // interleaved pairs (2i, 2i + 1).
+    if (!p.interleaved) {
+      const int i0 = part * 8;
+      uint4 a = *reinterpret_cast<const uint4*>(p.q + base + i0);
+      uint4 b = *reinterpret_cast<const uint4*>(p.q + base + 64 + i0);
+      if (rotate) {
+        __nv_bfloat16* x1 = reinterpret_cast<__nv_bfloat16*>(&a);
+        __nv_bfloat16* x2 = reinterpret_cast<__nv_bfloat16*>(&b);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const float c = table_value(p.cos, static_cast<long long>(pos) * 64 + i0 + i, p.table_bf16);
+          const float s = table_value(p.sin, static_cast<long long>(pos) * 64 + i0 + i, p.table_bf16);
+          const float u = __bfloat162float(x1[i]), w = __bfloat162float(x2[i]);
+          x1[i] = __float2bfloat16_rn(u * c - w * s);
+          x2[i] = __float2bfloat16_rn(u * s + w * c);
+        }
+      }
+      *reinterpret_cast<uint4*>(p.q_out + base + i0) = a;
+      *reinterpret_cast<uint4*>(p.q_out + base + 64 + i0) = b;
+    } else {
+      const int e0 = part * 16;
+      uint4 a = *reinterpret_cast<const uint4*>(p.q + base + e0);
+      uint4 b = *reinterpret_cast<const uint4*>(p.q + base + e0 + 8);
+      if (rotate) {
+        __nv_bfloat16* x = reinterpret_cast<__nv_bfloat16*>(&a);
+        __nv_bfloat16* y = reinterpret_cast<__nv_bfloat16*>(&b);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          __nv_bfloat16* pair = i < 4 ? x + 2 * i : y + 2 * (i - 4);
+          const float c = table_value(p.cos, static_cast<long long>(pos) * 64 + part * 8 + i, p.table_bf16);
+          const float s = table_value(p.sin, static_cast<long long>(pos) * 64 + part * 8 + i, p.table_bf16);
+          const float u = __bfloat162float(pair[0]), w = __bfloat162float(pair[1]);
+          pair[0] = __float2bfloat16_rn(u * c - w * s);
+          pair[1] = __float2bfloat16_rn(u * s + w * c);
+        }
+      }
+      *reinterpret_cast<uint4*>(p.q_out + base + e0) = a;
+      *reinterpret_cast<uint4*>(p.q_out + base + e0 + 8) = b;
+    }
+  }
+}
+
+static uint64_t rope_bytes(const FwPrefillArgs* a) {
+  if (a->rotary_cos == nullptr) return 0;
+  return (static_cast<uint64_t>(a->total_q) * a->nheads * 128 * 2 + 255) & ~255ull;
 }
 
 // Chunks of at least this many tokens go to the tensor-core kernel; shorter
@@ -42,16 +138,65 @@ static bool use_tensor_core_kernel(const FwPrefillArgs* a) {
   return a->max_seqlen_q >= kTensorCoreMinChunk;
 }
 
-extern "C" uint64_t fw_prefill_workspace_bytes(const FwPrefillArgs* a) {
-  if (check_prefill_args(a) != FW_OK) return 0;
-  if (use_tensor_core_kernel(a)) return tcgen05_prefill_workspace_bytes(a);
-  return splitkv_prefill_workspace_bytes(a);
+static uint64_t attention_workspace_bytes(const FwPrefillArgs* a) {
+  const uint64_t n = use_tensor_core_kernel(a) ? tcgen05_prefill_workspace_bytes(a)
+                                               : splitkv_prefill_workspace_bytes(a);
+  return n == 0 ? 0 : (n + 255) & ~255ull;
 }
 
-extern "C" int fw_prefill_paged(const FwPrefillArgs* a, void* stream) {
+extern "C" uint64_t fw_prefill_workspace_bytes(const FwPrefillArgs* a) {
+  if (check_prefill_args(a) != FW_OK) return 0;
+  const uint64_t n = attention_workspace_bytes(a);
+  return n == 0 ? 0 : n + rope_bytes(a);
+}
+
+extern "C" int fw_prefill_paged(const FwPrefillArgs* a, void* stream_ptr) {
   int rc = check_prefill_args(a);
   if (rc != FW_OK) return rc;
   if (a->total_q == 0) return FW_OK;
-  if (use_tensor_core_kernel(a)) return tcgen05_prefill(a, static_cast<cudaStream_t>(stream));
-  return splitkv_prefill(a, static_cast<cudaStream_t>(stream));
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
+  FwPrefillArgs local = *a;
+  if (a->rotary_cos != nullptr) {
+    // The rotated copy of q lives behind the attention kernels' own scratch.
+    const uint64_t head = attention_workspace_bytes(a);
+    if (head == 0) return FW_ERR_UNSUPPORTED;
+    if (a->workspace == nullptr || a->workspace_bytes < head + rope_bytes(a) ||
+        (reinterpret_cast<uintptr_t>(a->workspace) & 255)) {
+      set_error("workspace must be 256-byte aligned and hold %llu bytes; got %llu.",
+                static_cast<unsigned long long>(head + rope_bytes(a)),
+                static_cast<unsigned long long>(a->workspace_bytes));
+      return FW_ERR_WORKSPACE;
+    }
+    if (a->q == nullptr || a->cu_seqlens_q == nullptr || a->seqused_k == nullptr) {
+      set_error("q, cu_seqlens_q and seqused_k must not be NULL.");
+      return FW_ERR_BAD_SHAPE;
+    }
+    RopeParams rp;
+    rp.q = static_cast<const __nv_bfloat16*>(a->q);
+    rp.q_out = reinterpret_cast<__nv_bfloat16*>(static_cast<uint8_t*>(a->workspace) + head);
+    rp.cos = a->rotary_cos;
+    rp.sin = a->rotary_sin;
+    rp.cu = a->cu_seqlens_q;
+    rp.seqused = a->seqused_k;
+    rp.tok_stride = a->token_major ? static_cast<long long>(a->nheads) * 128 : 128;
+    rp.head_stride = a->token_major ? 128 : static_cast<long long>(a->total_q) * 128;
+    rp.batch = a->batch;
+    rp.total_q = a->total_q;
+    rp.nheads = a->nheads;
+    rp.rotary_len = a->rotary_len;
+    rp.interleaved = a->rotary_interleaved;
+    rp.table_bf16 = a->rotary_bf16;
+    const long long threads = static_cast<long long>(a->total_q) * a->nheads * 8;
+    const long long want = (threads + 255) / 256, cap = static_cast<long long>(sm_count()) * 32;
+    rope_q_kernel<<<static_cast<int>(want < cap ? want : cap), 256, 0, stream>>>(rp);
+    cudaError_t err = cudaGetLastError();
+    if (err != cudaSuccess) {
+      set_error("rope kernel launch: %s", cudaGetErrorString(err));
+      return FW_ERR_LAUNCH;
+    }
+    local.q = rp.q_out;
+    local.workspace_bytes = head;
+  }
+  if (use_tensor_core_kernel(&local)) return tcgen05_prefill(&local, stream);
+  return splitkv_prefill(&local, stream);
 }

@@ -31,6 +31,7 @@ INTERNAL_EXPORTS = {
     "PAGE_SIZE_MULTIPLE": "flywheel_tpu.softmax_attention.config",
     "NUM_LANES": "flywheel_tpu.core.tiling",
     "merged_cache_heads": "flywheel_tpu.softmax_attention.kv_layout",
+    "write_kv_cache_pages": "flywheel_tpu.softmax_attention.page",
 }
 
 

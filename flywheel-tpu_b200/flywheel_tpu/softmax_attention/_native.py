@@ -57,6 +57,15 @@ class FwAppendArgs(ctypes.Structure):
     ]
 
 
+class FwWritePagesArgs(ctypes.Structure):
+    _fields_ = [
+        ("kv_cache", c_ptr), ("k_new", c_ptr), ("v_new", c_ptr), ("slices", c_ptr),
+        ("num_slices", c_ptr), ("num_pages", i64), ("page_size", i32),
+        ("num_columns", i32), ("total_tokens", i32), ("nheads_k", i32),
+        ("head_dim", i32), ("kv_dtype", i32),
+    ]
+
+
 class FwPrefillArgs(ctypes.Structure):
     _fields_ = [
         ("q", c_ptr), ("out", c_ptr), ("lse", c_ptr), ("kv_cache", c_ptr),
@@ -68,6 +77,8 @@ class FwPrefillArgs(ctypes.Structure):
         ("nheads", i32), ("nheads_k", i32), ("head_dim", i32),
         ("kv_dtype", i32), ("causal", i32), ("window_left", i32),
         ("softmax_scale", f32), ("softcap", f32), ("token_major", i32),
+        ("rotary_cos", c_ptr), ("rotary_sin", c_ptr), ("rotary_len", i32),
+        ("rotary_interleaved", i32), ("rotary_bf16", i32),
     ]
 
 
@@ -86,6 +97,7 @@ EXPORTS = {
     "fw_decode_kvcache": (ctypes.c_int, [ctypes.POINTER(FwDecodeArgs), c_ptr]),
     "fw_decode_kvcache_static": (ctypes.c_int, [ctypes.POINTER(FwDecodeArgs), c_ptr]),
     "fw_append_ragged": (ctypes.c_int, [ctypes.POINTER(FwAppendArgs), c_ptr]),
+    "fw_write_kv_pages": (ctypes.c_int, [ctypes.POINTER(FwWritePagesArgs), c_ptr]),
     "fw_prefill_workspace_bytes": (u64, [ctypes.POINTER(FwPrefillArgs)]),
     "fw_prefill_paged": (ctypes.c_int, [ctypes.POINTER(FwPrefillArgs), c_ptr]),
     "fw_lse_combine": (ctypes.c_int, [ctypes.POINTER(FwCombineArgs), c_ptr]),

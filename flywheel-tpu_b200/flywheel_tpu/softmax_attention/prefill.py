@@ -39,7 +39,7 @@ def flash_attn_func(*args, **kwargs):
 def paged_prefill_device(q, kv_cache, cu_seqlens_q, seqused_k, block_table,
                          num_active, *, max_seqlen_q, nheads_k, softmax_scale,
                          causal, window_left, softcap, return_lse, k_scale,
-                         v_scale, sinks, token_major):
+                         v_scale, sinks, token_major, rotary=None):
     """Launches the paged prefill kernel on CUDA tensors; returns (out, lse or
     None).  q is (nheads, total_q, d), or (total_q, nheads, d) when
     token_major; lse is (nheads, total_q) either way."""
@@ -69,6 +69,12 @@ def paged_prefill_device(q, kv_cache, cu_seqlens_q, seqused_k, block_table,
         window_left=-1 if window_left is None else int(window_left),
         softmax_scale=float(softmax_scale), softcap=float(softcap),
         token_major=int(bool(token_major)))
+    if rotary is not None:
+        cos, sin, interleaved = rotary
+        args.rotary_cos, args.rotary_sin = cos.data_ptr(), sin.data_ptr()
+        args.rotary_len = cos.shape[0]
+        args.rotary_interleaved = int(bool(interleaved))
+        args.rotary_bf16 = int(cos.dtype == torch.bfloat16)
     lib = _native.library()
     stream = _native.current_stream(device)
     nbytes = lib.fw_prefill_workspace_bytes(ctypes.byref(args))
@@ -129,8 +135,12 @@ def flash_attn_varlen_func(
     past cu_seqlens_q[-1], return out = 0 and lse = -inf.  learnable_sink:
     (nheads,) sink logits.  max_seqlen_q / max_seqlen_k must be concrete
     positive ints.  Returns out (nheads, total_q, headdim), or (out, lse) with
-    lse (nheads, total_q) float32 when return_softmax_lse.  block_sizes and
-    interpret are accepted and ignored.  Forward-only.
+    lse (nheads, total_q) float32 when return_softmax_lse.  rotary_cos /
+    rotary_sin ((seqlen_ro, headdim / 2), q's dtype or float32) with
+    rotary_k=False rotate Q only, token t of a sequence at position seqused_k -
+    len_q + t (the cache holds K already rotated); the table must cover
+    max_seqlen_k.  block_sizes and interpret are accepted and ignored.
+    Forward-only.
     """
     del interpret, block_sizes
     window_size = check_common_kwargs(
@@ -170,10 +180,14 @@ def flash_attn_varlen_func(
         raise ValueError(
             "block_table needs seqused_k, the (batch,) kv length of each"
             " sequence (its new tokens included).")
-    if rotary_cos is not None or rotary_sin is not None:
+    if rotary_cos is not None and rotary_k:
         raise NotImplementedError(
-            "fused RoPE on the paged path is not built yet; rotate q before"
-            " the call.")
+            "a paged KV cache holds K already rotated; pass rotary_k=False to"
+            " rotate Q only.")
+    if type(rotary_interleaved) is not bool:
+        raise ValueError("rotary_interleaved must be a static bool.")
+    if (rotary_cos is None) != (rotary_sin is None):
+        raise ValueError("rotary_cos and rotary_sin must be provided together.")
     for arg_name, bound in (("max_seqlen_q", max_seqlen_q),
                             ("max_seqlen_k", max_seqlen_k)):
         if not isinstance(bound, int):
@@ -247,6 +261,22 @@ def flash_attn_varlen_func(
     pool = _arrays.to_device(k, device)
     if not pool.is_contiguous():
         raise ValueError("the KV cache must be contiguous.")
+    rotary = None
+    if rotary_cos is not None:
+        cos_shape, sin_shape = _arrays.shape(rotary_cos), _arrays.shape(rotary_sin)
+        if len(cos_shape) != 2 or sin_shape != cos_shape:
+            raise ValueError("rotary_cos and rotary_sin must have the same 2-D shape.")
+        if 2 * cos_shape[1] != head_dim_qk:
+            raise ValueError(
+                f"rotary_dim ({2 * cos_shape[1]}) must equal head_dim ({head_dim_qk});"
+                " partial rotary is not supported.")
+        names = (_arrays.dtype_name(rotary_cos.dtype), _arrays.dtype_name(rotary_sin.dtype))
+        if names[0] != names[1] or names[0] not in ("bfloat16", "float32"):
+            raise ValueError("rotary_cos and rotary_sin must share Q's dtype or be float32.")
+        if cos_shape[0] < max_seqlen_k:
+            raise ValueError("rotary table is shorter than the KV sequence bound.")
+        rotary = (_arrays.to_device(rotary_cos, device).contiguous(),
+                  _arrays.to_device(rotary_sin, device).contiguous(), rotary_interleaved)
     out, lse = paged_prefill_device(
         q_dev, pool,
         _arrays.to_device(cu_seqlens_q, device, dtype="int32").contiguous(),
@@ -256,7 +286,7 @@ def flash_attn_varlen_func(
         softmax_scale=softmax_scale, causal=window[1] == 0,
         window_left=window[0], softcap=float(softcap),
         return_lse=bool(return_softmax_lse), k_scale=k_scale, v_scale=v_scale,
-        sinks=sinks, token_major=False)
+        sinks=sinks, token_major=False, rotary=rotary)
     if return_softmax_lse:
         return _arrays.like(out, q), _arrays.like(lse, q)
     return _arrays.like(out, q)

@@ -15,6 +15,8 @@
  *                          (flash_attn_with_kvcache) and the custom call it
  *                          lowers to, kernels/decode.py:2046-2475
  *   fw_append_ragged    <- kernels/kv_append.py:116-184 (append_ragged)
+ *   fw_write_kv_pages   <- flywheel_tpu/softmax_attention/page.py:35-73
+ *                          (write_kv_cache_pages)
  *   fw_prefill_paged    <- flywheel_tpu/softmax_attention/prefill.py:437-661
  *                          (flash_attn_varlen_func with block_table) and
  *                          kernels/fwd_paged.py:1351-1491
@@ -174,6 +176,34 @@ typedef struct FwAppendArgs {
 int fw_append_ragged(const FwAppendArgs* args, void* stream);
 
 /*
+ * Slice-table page writer (write_kv_cache_pages,
+ * flywheel_tpu/softmax_attention/page.py:35-73 and
+ * kernels/kv_cache_write.py:66-227): the serving caller's prefill cache fill.
+ * k_new / v_new: (total_tokens, nheads_k, head_dim) in the pool dtype.
+ * slices: i32[3, num_columns] row-major; column j < *num_slices is
+ * (cache_row_start, new_row_start, length) in rows of the flat
+ * (num_pages * page_size) cache view and of k / v, each piece inside one page;
+ * later columns are ignored.  Whole merged rows are written (bits, not values;
+ * an fp8 pad head as zeros); rows outside the cache or k / v are skipped.
+ */
+typedef struct FwWritePagesArgs {
+  void* kv_cache;
+  const void* k_new;
+  const void* v_new;
+  const int32_t* slices;
+  const int32_t* num_slices;
+  int64_t num_pages;
+  int32_t page_size;
+  int32_t num_columns;
+  int32_t total_tokens;
+  int32_t nheads_k;
+  int32_t head_dim;
+  int32_t kv_dtype;
+} FwWritePagesArgs;
+
+int fw_write_kv_pages(const FwWritePagesArgs* args, void* stream);
+
+/*
  * Read-only chunked prefill over the merged pool (flash_attn_varlen_func with
  * block_table, prefill.py:437-661).  q / out: head-major (nheads, total_q,
  * head_dim) bf16; lse: NULL or (nheads, total_q) f32.  seqused_k[r] is request
@@ -209,6 +239,15 @@ typedef struct FwPrefillArgs {
   float softmax_scale;
   float softcap;
   int32_t token_major;  /* 1: q/out are (total_q, nheads, head_dim) */
+  /* Q-only rotary embedding (prefill.py:494-498, rotary.py:27-215): NULL, or
+   * (rotary_len, head_dim / 2) cos / sin tables, f32 (rotary_bf16 = 0) or bf16.
+   * Token t of request r is rotated at position seqused_k[r] - len_q(r) + t in
+   * f32 and rounded once to bf16; the cache holds K already rotated. */
+  const void* rotary_cos;
+  const void* rotary_sin;
+  int32_t rotary_len;
+  int32_t rotary_interleaved;
+  int32_t rotary_bf16;
 } FwPrefillArgs;
 
 uint64_t fw_prefill_workspace_bytes(const FwPrefillArgs* args);

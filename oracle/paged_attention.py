@@ -105,6 +105,22 @@ def append_to_pool(pool, k, v, cu_seqlens_q, cache_seqlens, block_table,
     return pool
 
 
+def write_kv_cache_pages(pool, k, v, slices, num_slices):
+    """A copy of the merged pool with the slice-table pieces written: column
+    j < num_slices of slices (i32[3, n]) is (cache_row_start, new_row_start,
+    length) in rows of the flat (pages * page_size) view and of k / v
+    (flywheel_tpu/softmax_attention/page.py:35-73; the reference's own check is
+    tests/softmax_attention/test_page.py:32-69)."""
+    pool = pool.copy()
+    flat = pool.reshape(-1, *pool.shape[2:])
+    rows = merge_kv_heads(np.asarray(k), np.asarray(v))
+    slices = np.asarray(slices)
+    for column in range(int(np.asarray(num_slices).reshape(-1)[0])):
+        cache_row, new_row, length = (int(x) for x in slices[:, column])
+        flat[cache_row:cache_row + length] = rows[new_row:new_row + length]
+    return pool
+
+
 def append_contiguous(k_cache, v_cache, k, v, cache_seqlens, cache_batch_idx,
                       num_active=None):
     """Contiguous pair: k_cache[cache_batch_idx[b], cache_seqlens[b]] = k[b, 0]
@@ -302,6 +318,36 @@ def kvcache_contiguous(q, k_cache, v_cache, k, v, cache_seqlens,
                            softcap=softcap, scale=scale, sinks=sinks)
         out[b], lse[b] = o, l
     return out, lse, k_cache, v_cache
+
+
+def rotate_packed_q(q, cos, sin, cu_seqlens_q, seqused_k, interleaved=False):
+    """RoPE on packed token-major q (total_q, heads, d): token t of request r at
+    position seqused_k[r] - len_q(r) + t, f32 rotation rounded once to q's
+    dtype; rows outside every request and positions past the table stay as they
+    are (tests/softmax_attention/util.py:105-150 of the reference; positions:
+    flywheel_tpu/softmax_attention/prefill.py:494-498)."""
+    q = np.asarray(q)
+    out = q.copy()
+    cu = np.asarray(cu_seqlens_q).astype(np.int64)
+    cos32, sin32 = np.asarray(cos).astype(np.float32), np.asarray(sin).astype(np.float32)
+    for r in range(len(cu) - 1):
+        start, end = int(cu[r]), int(cu[r + 1])
+        if end <= start:
+            continue
+        pos = int(seqused_k[r]) - (end - start) + np.arange(end - start)
+        ok = (pos >= 0) & (pos < cos32.shape[0])
+        rows = np.arange(start, end)[ok]
+        c, s_ = cos32[pos[ok]][:, None, :], sin32[pos[ok]][:, None, :]
+        x = q[rows].astype(np.float32)
+        if interleaved:
+            x1, x2 = x[..., 0::2], x[..., 1::2]
+            y = np.stack((x1 * c - x2 * s_, x1 * s_ + x2 * c), axis=-1).reshape(x.shape)
+        else:
+            half = x.shape[-1] // 2
+            x1, x2 = x[..., :half], x[..., half:]
+            y = np.concatenate((x1 * c - x2 * s_, x1 * s_ + x2 * c), axis=-1)
+        out[rows] = y.astype(q.dtype)
+    return out
 
 
 # ----------------------------------------------------------------------------

@@ -164,3 +164,35 @@ def test_contiguous_decode_matches_paged_view():
     k2, v2 = oracle.split_kv_heads(pool2, hk)
     np.testing.assert_array_equal(k2.view(np.uint16), kc2.view(np.uint16))
     np.testing.assert_array_equal(v2.view(np.uint16), vc2.view(np.uint16))
+
+
+def test_write_kv_cache_pages_oracle():
+    pool = np.zeros((3, 4, 4, 8), oracle.BF16)
+    k = np.arange(5 * 2 * 8, dtype=np.float32).reshape(5, 2, 8).astype(oracle.BF16)
+    v = (-k.astype(np.float32)).astype(oracle.BF16)
+    slices = np.array([[9, 2], [0, 3], [3, 2]], np.int32)      # two pieces
+    out = oracle.write_kv_cache_pages(pool, k, v, slices, [2])
+    flat = out.reshape(12, 4, 8)
+    np.testing.assert_array_equal(flat[9:12, 0::2].astype(np.float32), k[0:3].astype(np.float32))
+    np.testing.assert_array_equal(flat[2:4, 1::2].astype(np.float32), v[3:5].astype(np.float32))
+    untouched = np.ones(12, bool)
+    untouched[[9, 10, 11, 2, 3]] = False
+    assert not flat[untouched].view(np.uint16).any()
+    assert not oracle.write_kv_cache_pages(pool, k, v, slices, [0]).view(np.uint16).any()
+
+
+def test_rotate_packed_q_positions_and_norm():
+    rng = np.random.default_rng(9)
+    q = rng.standard_normal((6, 2, 128), dtype=np.float32)
+    angle = rng.random((40, 64)) * 2 * np.pi
+    cos, sin = np.cos(angle).astype(np.float32), np.sin(angle).astype(np.float32)
+    cu, seqused = np.array([0, 2, 5]), np.array([10, 3])
+    for interleaved in (False, True):
+        out = oracle.rotate_packed_q(q, cos, sin, cu, seqused, interleaved)
+        np.testing.assert_allclose(np.linalg.norm(out[:5], axis=-1), np.linalg.norm(q[:5], axis=-1), rtol=1e-5)
+        np.testing.assert_array_equal(out[5], q[5])            # row of no request
+    out = oracle.rotate_packed_q(q, cos, sin, cu, seqused, False)
+    pos = 8                                                    # token 0 of request 0: 10 - 2 + 0
+    x1, x2 = q[0, 0, :64], q[0, 0, 64:]
+    np.testing.assert_allclose(out[0, 0, :64], x1 * cos[pos] - x2 * sin[pos], rtol=1e-6)
+    np.testing.assert_allclose(out[0, 0, 64:], x1 * sin[pos] + x2 * cos[pos], rtol=1e-6)

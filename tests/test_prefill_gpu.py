@@ -188,3 +188,27 @@ def test_zero_row_packed_buffer():
         block_table=np.arange(4, dtype=np.int32).reshape(2, 2),
         cu_seqlens_q=np.zeros(3, np.int32), max_seqlen_q=1, causal=True, return_softmax_lse=True)
     assert not out.astype(np.float32).any() and np.isneginf(lse).all()
+
+
+@pytest.mark.parametrize("rotary_interleaved", [False, True])
+@pytest.mark.parametrize("table_dtype", ["float32", "bfloat16"])
+def test_varlen_func_rotary_q_at_cache_positions(rotary_interleaved, table_dtype):
+    """Q-only RoPE (rotary_k=False): token t of a request is rotated at
+    seqused_k - len_q + t; the cache holds K already rotated."""
+    from flywheel_tpu import flash_attn_varlen_func
+    c = random_prefill_case(6, prefixes=(127, 0, 251), chunks=(3, 1, 130), hq=8, hk=2, page_size=64)
+    angle = np.random.default_rng(23).random((448, 64)) * 2 * np.pi
+    dt = np.float32 if table_dtype == "float32" else oracle.BF16
+    cos, sin = np.cos(angle).astype(dt), np.sin(angle).astype(dt)
+    out, lse = flash_attn_varlen_func(
+        np.ascontiguousarray(c["q"].transpose(1, 0, 2)), to_cuda(c["pool"]), None, c["cu"], None, 130,
+        448, causal=True, return_softmax_lse=True, block_table=c["table"], seqused_k=c["seqused"],
+        rotary_cos=cos, rotary_sin=sin, rotary_interleaved=rotary_interleaved, rotary_k=False)
+    q_ro = oracle.rotate_packed_q(c["q"], cos, sin, c["cu"], c["seqused"], rotary_interleaved)
+    want, want_lse = oracle.ragged_paged_attention(
+        q_ro, c["pool"], c["cu"], c["seqused"], c["table"], nheads_k=2, causal=True)
+    check_rows(out.astype(np.float32).transpose(1, 0, 2), lse, want, want_lse, OUT_TOL)
+    with pytest.raises(NotImplementedError, match="rotary_k=False"):
+        flash_attn_varlen_func(
+            np.ascontiguousarray(c["q"].transpose(1, 0, 2)), to_cuda(c["pool"]), None, c["cu"], None, 130,
+            448, block_table=c["table"], seqused_k=c["seqused"], rotary_cos=cos, rotary_sin=sin)
