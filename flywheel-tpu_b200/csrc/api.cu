@@ -107,6 +107,43 @@ extern "C" const char* fw_last_error(void) { return fw::g_error; }
 
 extern "C" int fw_version(void) { return 3; }
 
+namespace fw {
+// A CTA that waits on a barrier nobody will ever arrive on: the wait must give
+// up after `limit` polls, record FW_STATUS_WAIT_TIMEOUT and return, leaving the
+// context usable.  This is the path every kernel's waits take when a producer
+// or a peer never shows up.
+__global__ void wait_timeout_probe_kernel(int* status, uint32_t limit) {
+  __shared__ uint64_t bar;
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) {
+    mbar_init(&bar, 1);
+    abort_flag = 0;
+    fence_barrier_init();
+  }
+  __syncthreads();
+  if (threadIdx.x == 0 && !mbar_wait_bounded(&bar, 0, &abort_flag, limit)) {
+    abort_flag = 1;
+    report_status(status, FW_STATUS_WAIT_TIMEOUT);
+  }
+}
+}  // namespace fw
+
+extern "C" int fw_selftest_wait_timeout(void* workspace, uint32_t spin_limit, void* stream) {
+  if (workspace == nullptr || (reinterpret_cast<uintptr_t>(workspace) & 3)) {
+    fw::set_error("workspace must be a 4-byte aligned device pointer.");
+    return FW_ERR_WORKSPACE;
+  }
+  if (spin_limit > (1u << 20)) spin_limit = 1u << 20;  // a fraction of a second at most
+  fw::wait_timeout_probe_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<int*>(workspace), spin_limit);
+  cudaError_t err = cudaGetLastError();
+  if (err != cudaSuccess) {
+    fw::set_error("probe launch: %s", cudaGetErrorString(err));
+    return FW_ERR_LAUNCH;
+  }
+  return FW_OK;
+}
+
 extern "C" int fw_read_status(const void* workspace, void* stream, int32_t* status) {
   if (workspace == nullptr || status == nullptr) {
     fw::set_error("workspace and status must not be NULL.");

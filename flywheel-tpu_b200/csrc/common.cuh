@@ -57,12 +57,13 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "memory");
   return done != 0;
 }
-// Bounded wait.  Returns false after kWaitSpinLimit failed polls or as soon as
+// Bounded wait.  Returns false after `limit` failed polls or as soon as
 // *abort_flag (shared memory) is set by another waiter of the same CTA.
 __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity,
-                                                  volatile int* abort_flag) {
+                                                  volatile int* abort_flag,
+                                                  uint32_t limit = kWaitSpinLimit) {
   if (mbar_try_wait(bar, parity)) return true;
-  for (uint32_t spin = 0; spin < kWaitSpinLimit; ++spin) {
+  for (uint32_t spin = 0; spin < limit; ++spin) {
     if (mbar_try_wait(bar, parity)) return true;
     // A sleeping warp leaves its issue slots to the warps that compute.
     // try_wait already parks the thread for a hardware time slice; back off

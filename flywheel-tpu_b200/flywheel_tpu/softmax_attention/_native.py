@@ -101,6 +101,7 @@ EXPORTS = {
     "fw_prefill_workspace_bytes": (u64, [ctypes.POINTER(FwPrefillArgs)]),
     "fw_prefill_paged": (ctypes.c_int, [ctypes.POINTER(FwPrefillArgs), c_ptr]),
     "fw_lse_combine": (ctypes.c_int, [ctypes.POINTER(FwCombineArgs), c_ptr]),
+    "fw_selftest_wait_timeout": (ctypes.c_int, [c_ptr, ctypes.c_uint32, c_ptr]),
     "fw_read_status": (ctypes.c_int, [c_ptr, c_ptr, ctypes.POINTER(i32)]),
     "fw_last_error": (ctypes.c_char_p, []),
     "fw_version": (ctypes.c_int, []),

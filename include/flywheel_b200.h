@@ -288,6 +288,14 @@ int fw_lse_combine(const FwCombineArgs* args, void* stream);
  * Synchronises `stream`; meant for tests and debugging, not the hot path. */
 int fw_read_status(const void* workspace, void* stream, int32_t* status);
 
+/* Failure-detection self test: launches one CTA whose bounded wait can never
+ * be satisfied (a barrier nothing arrives on).  After at most spin_limit polls
+ * (capped at 2^20) it records FW_STATUS_WAIT_TIMEOUT in the status word at the
+ * head of `workspace` and returns; the context stays usable.  No fault, trap
+ * or endless loop is involved.  (No counterpart in the reference, which has no
+ * runtime error channel.) */
+int fw_selftest_wait_timeout(void* workspace, uint32_t spin_limit, void* stream);
+
 /* Thread-local text of the last error on this thread ("" if none). */
 const char* fw_last_error(void);
 
