@@ -15,10 +15,10 @@ is one decode call over the whole batch.
   resident on the device, as it does in serving.
 * roofline: algorithmic KV bytes per launch / measured launch time, against
   the measured HBM copy bandwidth in MEASURED_PEAKS.json.
-* cpu_baseline: the NumPy restatement of the reference's test oracle on a
-  bounded sample of the same workload, on the host cores.
+* cpu_baseline: the C + OpenMP restatement of the reference's test oracle
+  (oracle/paged_decode_ref.c) on the same batch, on all host cores.
 * --impl reference: that CPU restatement as its own arm (the reference itself
-  needs JAX, which this image lacks).
+  needs JAX, which this image lacks); a step is the first 32 requests.
 
 With N > 1 (torchrun) every rank runs its own copy of the workload with its own
 seed (requests shard with no communication); value is the sum of bytes over
@@ -412,61 +412,59 @@ def make_decode_call(work, device):
     return call, out, scratch
 
 
-def cpu_baseline(work, budget_bytes=1.0e9):
-    """Times the NumPy restatement of the reference's oracle on the first few
-    requests of the workload (about `budget_bytes` of KV) on the host cores."""
-    import torch
+def cpu_baseline(work, repeats=3):
+    """Times the C/OpenMP restatement of the reference's test oracle
+    (oracle/paged_decode_ref.c) on the whole decode batch, on all host cores."""
     from flywheel_tpu.softmax_attention import _arrays
-    from oracle import paged_attention as oracle
+    from oracle import c_port
     lens, table = work["lens"], work["table"]
-    count, acc = 0, 0
-    while count < len(lens) and acc < budget_bytes:
-        acc += (int(lens[count]) + 1) * 2 * HK * D * 2
-        count += 1
-    used_pages = np.unique(np.concatenate(
-        [table[b, : -(-(int(lens[b]) + 1) // PAGE)] for b in range(count)]))
-    remap = np.zeros(work["pool_pages"], np.int32)
-    remap[used_pages] = np.arange(len(used_pages), dtype=np.int32)
-    pool = _arrays.to_host_numpy(work["pool"][torch.from_numpy(used_pages).to(work["pool"].device).long()])
+    pool = _arrays.to_host_numpy(work["pool"])
     host = work["host"]
-    q = _arrays.to_host_numpy(host["q"][:count])
-    k = _arrays.to_host_numpy(host["k"][:count])
-    v = _arrays.to_host_numpy(host["v"][:count])
-    sample_table = remap[table[:count]]
-    start = time.perf_counter()
-    out, _, _ = oracle.kvcache_paged(q, pool, k, v, lens[:count], sample_table, nheads_k=HK, causal=True)
-    seconds = time.perf_counter() - start
-    return {"value": acc / seconds / 1e9, "unit": "GB/s", "cores": os.cpu_count(), "kind": "port",
-            "sample": f"first {count} of {BATCH} requests ({acc / 1e9:.2f} GB of KV), "
-                      f"{seconds:.2f} s, NumPy (BLAS threads = host cores)"}, out, count
+    q, k, v = (_arrays.to_host_numpy(host[name]) for name in ("q", "k", "v"))
+    c_port.paged_decode(q[:2], pool, k[:2], v[:2], lens[:2], table[:2], nheads_k=HK, in_place=True)  # page in
+    times = []
+    for _ in range(repeats):
+        start = time.perf_counter()
+        out, _, _ = c_port.paged_decode(q, pool, k, v, lens, table, nheads_k=HK, causal=True, in_place=True)
+        times.append(time.perf_counter() - start)
+    seconds = float(np.median(times))
+    nbytes = work["kv_bytes"]
+    return {"value": nbytes / seconds / 1e9, "unit": "GB/s", "cores": os.cpu_count(), "kind": "port",
+            "sample": f"all {len(lens)} requests ({nbytes / 1e9:.2f} GB of KV), median of {repeats} passes of "
+                      f"{seconds:.2f} s, C + OpenMP restatement of the reference's test oracle"}, out, len(lens)
 
 
 def run_reference_arm(ns):
-    """The reference's CPU path stands in as the NumPy restatement of its own
-    test oracle (the reference needs JAX, absent from this image)."""
+    """The reference's CPU path stands in as the C + OpenMP restatement of its
+    own test oracle (the reference itself needs JAX, absent from this image),
+    on all host cores; a step is the first 32 requests of the decode batch."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
+    import ml_dtypes
     from flywheel_tpu.testing import workloads
-    from oracle import paged_attention as oracle
+    from oracle import c_port
+    bf16 = np.dtype(ml_dtypes.bfloat16)
     rng = np.random.default_rng(0)
     lens = rng.integers(LEN_LO, LEN_HI + 1, BATCH).astype(np.int32)
-    sample = 8
+    sample = min(32, BATCH)
     table, pool_pages = workloads.paged_table(rng, lens[:sample], 1, PAGE, slack=0.10)
-    draw = lambda shape: rng.standard_normal(shape, dtype=np.float32).astype(oracle.BF16)
-    pool = draw((pool_pages, PAGE, 2 * HK, D))
+    draw = lambda shape: rng.standard_normal(shape, dtype=np.float32).astype(bf16)
+    # values do not change the timing: one random block of pages, repeated
+    block = draw((256, PAGE, 2 * HK, D))
+    pool = np.ascontiguousarray(np.tile(block, (-(-pool_pages // 256), 1, 1, 1))[:pool_pages])
     q, k, v = draw((sample, 1, HQ, D)), draw((sample, 1, HK, D)), draw((sample, 1, HK, D))
     nbytes = workloads.decode_kv_bytes(lens[:sample], 1, HK, D, 2)
     times = []
     for step in range(ns.warmup + ns.steps):
         start = time.perf_counter()
-        oracle.kvcache_paged(q, pool, k, v, lens[:sample], table, nheads_k=HK, causal=True)
+        c_port.paged_decode(q, pool, k, v, lens[:sample], table, nheads_k=HK, causal=True, in_place=True)
         if step >= ns.warmup:
             times.append(time.perf_counter() - start)
     ms = 1e3 * float(np.mean(times))
     value = nbytes / (ms * 1e-3) / 1e9
-    sample_text = (f"first {sample} of {BATCH} requests per step ({nbytes / 1e9:.2f} GB of KV); "
-                   "NumPy restatement of the reference's test oracle")
+    sample_text = (f"first {sample} of {BATCH} requests per step ({nbytes / 1e9:.2f} GB of KV); C + OpenMP "
+                   "restatement of the reference's test oracle on all host cores")
     print(json.dumps({
         "impl": "reference", "metric": "paged_decode_kv_read_bandwidth", "value": value, "unit": "GB/s",
         "n_gpus": ns.gpus, "steps": ns.steps, "warmup": ns.warmup, "ms_per_step": ms,
