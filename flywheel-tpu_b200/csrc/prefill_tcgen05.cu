@@ -20,6 +20,7 @@
 // as the A operand of the PV MMA), so one stream's softmax overlaps the other
 // stream's MMAs.  One CTA per SM (192 KiB shared memory, all 512 TMEM columns).
 #include <climits>
+#include <type_traits>
 
 #include "common.cuh"
 
@@ -152,6 +153,32 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes,
 __host__ __device__ constexpr uint32_t instr_desc(int n, bool b_mn_major) {
   return (1u << 4) | (1u << 7) | (1u << 10) | (b_mn_major ? (1u << 16) : 0u) |
          (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(kBM >> 4) << 24);
+}
+
+// Packed f32x2 arithmetic (two lanes per instruction on sm_100) and packed
+// bf16x2 max: they halve the issue slots the softmax spends around each exp2.
+__device__ __forceinline__ uint64_t pack2(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack2(uint64_t v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+  return r;
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ uint32_t max_bf16x2(uint32_t a, uint32_t b) {
+  uint32_t r;
+  asm("max.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+  return r;
 }
 
 // Pass 1 of the softmax over one 64-key row: optional softcap (scores become
@@ -416,10 +443,14 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       // the tile is redone against the new base and O is rescaled.  So the
       // common tile reads S once and needs no separate max pass.
       uint32_t packed[2][32];
-      float sum0, sum1, top;
-      auto exponentiate = [&](float neg_base) {
-        sum0 = sum1 = 0.f;
+      float sum, top;   // row sum of P; row max of the exponents (true-max variant only)
+      bool over;        // some P above 2^kRescaleThreshold (cheap variant only)
+      auto exponentiate = [&](float neg_base, auto want_true_max) {
+        constexpr bool kTrueMax = decltype(want_true_max)::value;
+        uint64_t sum2 = pack2(0.f, 0.f);
+        const uint64_t mul2 = pack2(mul, mul), base2 = pack2(neg_base, neg_base);
         float top0 = -INFINITY, top1 = -INFINITY;
+        uint32_t pmax = 0u;  // P >= 0, so +0 is the identity of the bf16 max
 #pragma unroll
         for (int half = 0; half < 2; ++half) {
           uint32_t sr[2][32];
@@ -437,30 +468,46 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           for (int c = 0; c < 2; ++c)
 #pragma unroll
             for (int i = 0; i < 32; i += 2) {
-              const float y0 = fmaf(__uint_as_float(sr[c][i]), mul, neg_base);
-              const float y1 = fmaf(__uint_as_float(sr[c][i + 1]), mul, neg_base);
-              top0 = fmaxf(top0, y0);
-              top1 = fmaxf(top1, y1);
+              float y0, y1;
+              unpack2(fma2(pack2(__uint_as_float(sr[c][i]), __uint_as_float(sr[c][i + 1])), mul2, base2), y0, y1);
+              if constexpr (kTrueMax) {
+                top0 = fmaxf(top0, y0);
+                top1 = fmaxf(top1, y1);
+              }
               const float p0 = fast_exp2(y0), p1 = fast_exp2(y1);
-              sum0 += p0;
-              sum1 += p1;
-              packed[half][c * 16 + (i >> 1)] = pack_bf16(p0, p1);
+              sum2 = add2(sum2, pack2(p0, p1));
+              const uint32_t pk = pack_bf16(p0, p1);
+              if constexpr (!kTrueMax) pmax = max_bf16x2(pmax, pk);
+              packed[half][c * 16 + (i >> 1)] = pk;
             }
         }
+        float s0, s1;
+        unpack2(sum2, s0, s1);
+        sum = s0 + s1;
         top = fmaxf(top0, top1);  // row max minus the base (the row max itself when the base is 0)
+        // bf16 bit patterns of non-negative values order like integers
+        over = max(pmax & 0xffffu, pmax >> 16) > 0x4380u;  // bf16(256.0) = 2^kRescaleThreshold
       };
+      static_assert(kRescaleThreshold == 8.0f, "the bf16 constant above is 2^8");
       float alpha = 1.f;
       float neg_base = m_used == -INFINITY ? 0.f : -m_used;
-      exponentiate(neg_base);
-      const bool move_base = m_used == -INFINITY ? top > -INFINITY : top > kRescaleThreshold;
+      // Rows that have no base yet (first tile, or everything masked so far) need
+      // the true row max; otherwise the cheap variant only tells whether some
+      // exponent outran the base.
+      const bool fresh = m_used == -INFINITY;
+      const bool any_fresh = __any_sync(0xffffffffu, fresh);
+      if (any_fresh) exponentiate(neg_base, std::true_type{});
+      else exponentiate(neg_base, std::false_type{});
+      const bool move_base = fresh ? top > -INFINITY : (any_fresh ? top > kRescaleThreshold : over);
       if (__any_sync(0xffffffffu, move_base)) {
+        if (!any_fresh) exponentiate(neg_base, std::true_type{});  // rare: fetch the true max
         if (move_base) {
           const float mx = top - neg_base;
           alpha = fast_exp2(m_used - mx);  // 0 when there was no base yet
           m_used = mx;
           neg_base = -mx;
         }
-        exponentiate(neg_base);  // lanes whose base stayed put get the same P again
+        exponentiate(neg_base, std::false_type{});  // lanes whose base stayed put get the same P again
         if (j > 0) {
           // PV(j-1) of this stream precedes QK(j) in the tensor pipe, so it has
           // drained; the wait makes its writes to O visible here.
@@ -484,7 +531,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       // the PV MMA.  (All of this thread's S row has been read by now.)
       tmem_st32(s_addr, packed[0]);
       tmem_st32(s_addr + 32, packed[1]);
-      l_run = l_run * alpha + (sum0 + sum1);
+      l_run = l_run * alpha + sum;
       tmem_wait_st();
       // Last tile: keys past the valid length may hold anything (NaN included);
       // their P is 0, so their V rows must be finite: zero them.  Both streams
