@@ -1029,6 +1029,7 @@ extern "C" int fw_decode_kvcache(const FwDecodeArgs* a, void* stream_ptr) {
 namespace fw {
 
 constexpr int kMaxItems = 8192;
+constexpr int kSortBuckets = 2048;
 
 struct PrefillPlanParams {
   const int* cu;
@@ -1038,7 +1039,7 @@ struct PrefillPlanParams {
   __nv_bfloat16* out;
   float* lse;
   long long tok_stride, head_stride;
-  int batch, qb, max_items, total_q, nheads;
+  int batch, qb, max_items, total_q, nheads, causal;
 };
 
 // Block 0 writes the item table {request, first q row, valid tokens, diagonal
@@ -1046,6 +1047,7 @@ struct PrefillPlanParams {
 // clear the packed rows that belong to no active request (out 0, lse -inf).
 __global__ void __launch_bounds__(256) prefill_plan_kernel(const PrefillPlanParams pp) {
   __shared__ int off[kMaxInlineBatch + 1];
+  __shared__ int bucket[kSortBuckets];
   const int n_active = pp.num_active ? min(pp.batch, max(0, *pp.num_active)) : pp.batch;
   if (blockIdx.x == 0) {
     for (int r = threadIdx.x; r < pp.batch; r += blockDim.x) {
@@ -1059,14 +1061,40 @@ __global__ void __launch_bounds__(256) prefill_plan_kernel(const PrefillPlanPara
     }
     __syncthreads();
     const int n_items = min(off[pp.batch], pp.max_items);
+    // Items are laid out longest key range first (a counting sort on the key
+    // count in 64-token buckets): CTAs are dispatched in item order, and the
+    // long ones must not be the last to start.
+    for (int i = threadIdx.x; i < kSortBuckets; i += blockDim.x) bucket[i] = 0;
+    __syncthreads();
+    auto key_of = [&](int r, int j, int c, int used) {
+      const int anchor = used - c + (j + 1) * pp.qb;
+      const int kv_end = pp.causal ? min(anchor, used) : used;
+      return kSortBuckets - 1 - min(max(kv_end, 0) >> 6, kSortBuckets - 1);  // long ranges get small keys
+    };
+    for (int r = threadIdx.x; r < pp.batch; r += blockDim.x) {
+      const int blocks = off[r + 1] - off[r];
+      const int c = blocks ? pp.cu[r + 1] - pp.cu[r] : 0, used = blocks ? pp.seqused[r] : 0;
+      for (int j = 0; j < blocks; ++j)
+        if (off[r] + j < pp.max_items) atomicAdd(&bucket[key_of(r, j, c, used)], 1);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      int run = 0;
+      for (int i = 0; i < kSortBuckets; ++i) {
+        const int n = bucket[i];
+        bucket[i] = run;
+        run += n;
+      }
+    }
+    __syncthreads();
     for (int r = threadIdx.x; r < pp.batch; r += blockDim.x) {
       const int blocks = off[r + 1] - off[r];
       if (blocks == 0) continue;
       const int c = pp.cu[r + 1] - pp.cu[r];
       const int used = pp.seqused[r];
       for (int j = 0; j < blocks; ++j) {
-        const int idx = off[r] + j;
-        if (idx >= pp.max_items) break;
+        if (off[r] + j >= pp.max_items) break;
+        const int idx = atomicAdd(&bucket[key_of(r, j, c, used)], 1);
         int* it = pp.items + 8 * idx;
         it[0] = r;
         it[1] = pp.cu[r] + j * pp.qb;
@@ -1117,6 +1145,7 @@ int launch_prefill_plan(const FwPrefillArgs* a, int qb, int max_items, int* item
   pp.max_items = max_items;
   pp.total_q = a->total_q;
   pp.nheads = a->nheads;
+  pp.causal = a->causal != 0;
   prefill_plan_kernel<<<min(sm_count(), 64), 256, 0, stream>>>(pp);
   cudaError_t err = cudaGetLastError();
   if (err != cudaSuccess) {

@@ -219,7 +219,7 @@ __device__ __forceinline__ float transform_row(uint32_t (&sr)[2][32], float c1, 
 __device__ __forceinline__ void record_timeout(int* status, int site, int j) {
   if (status != nullptr && atomicCAS(status + 1, 0, site) == 0) {
     status[2] = j;
-    status[3] = static_cast<int>(blockIdx.x | (blockIdx.y << 20));
+    status[3] = static_cast<int>(blockIdx.y | (blockIdx.x << 20));
   }
 }
 
@@ -246,7 +246,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   Bars* bars = reinterpret_cast<Bars*>(smem + kSmemBar);
   volatile int* abort_flag = &bars->abort_flag;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int item = blockIdx.x, h = blockIdx.y;
+  const int item = blockIdx.y, h = blockIdx.x;  // heads vary fastest: items start longest first across all heads
 
   // An item is up to kStreams * tpb query tokens of one request; stream t owns
   // tokens [t * tpb, (t + 1) * tpb) x the `group` heads of KV head h.
@@ -711,7 +711,7 @@ int tcgen05_prefill(const FwPrefillArgs* a, cudaStream_t stream) {
     set_error("cudaFuncSetAttribute(%d bytes): %s", kSmemBytes, cudaGetErrorString(err));
     return FW_ERR_LAUNCH;
   }
-  dim3 grid(max_items, a->nheads_k);
+  dim3 grid(a->nheads_k, max_items);
   prefill_tcgen05_kernel<<<grid, 64 + kStreams * 128, kSmemBytes, stream>>>(map_q, map_kv, p);
   err = cudaGetLastError();
   if (err != cudaSuccess) {
