@@ -11,3 +11,5 @@ PAGE_SIZE_MULTIPLE = DECODE_TILE_TOKENS
 # (decode.py:49-53).
 MAX_FOLDED_QUERY_ROWS = 128
 SUPPORTED_HEAD_DIMS = (128,)
+# Rows one decode launch takes; the host entry slices larger batches.
+MAX_DECODE_BATCH = 2048

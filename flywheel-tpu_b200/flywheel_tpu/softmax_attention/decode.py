@@ -18,6 +18,7 @@ import torch
 
 from flywheel_tpu.softmax_attention import _arrays, _native
 from flywheel_tpu.softmax_attention.config import (
+    MAX_DECODE_BATCH,
     MAX_FOLDED_QUERY_ROWS,
     PAGE_SIZE_MULTIPLE,
     SUPPORTED_HEAD_DIMS,
@@ -296,6 +297,7 @@ def flash_attn_with_kvcache(
         if return_softmax_lse:
             lse = torch.empty((batch, nheads, seqlen_q), dtype=torch.float32,
                               device=device)
+        kernel_has_new = has_new
         args = _native.FwDecodeArgs(
             q=q_dev.data_ptr(), out=out.data_ptr(), lse=_arrays.data_ptr(lse),
             kv_cache=cache_dev[0].data_ptr(),
@@ -315,13 +317,38 @@ def flash_attn_with_kvcache(
             causal=int(is_causal),
             window_left=-1 if window[0] is None else int(window[0]),
             softmax_scale=softmax_scale, softcap=float(softcap), num_ctas=0)
-        nbytes = lib.fw_decode_workspace_bytes(ctypes.byref(args))
-        if nbytes == 0:
-            _native.check(lib.fw_decode_kvcache(ctypes.byref(args), stream))
-            raise RuntimeError(_native.last_error())
-        scratch = _native.workspace(device, nbytes)
-        args.workspace, args.workspace_bytes = scratch.data_ptr(), scratch.numel()
-        _native.check(lib.fw_decode_kvcache(ctypes.byref(args), stream))
+        # The kernel takes up to MAX_DECODE_BATCH rows per launch (its per-CTA
+        # scan of the batch lives in shared memory); larger batches go in slices.
+        # Rows are independent, so slicing changes nothing but num_active, which
+        # is rebased on the device.
+        for first in range(0, batch, MAX_DECODE_BATCH):
+            rows = min(MAX_DECODE_BATCH, batch - first)
+            part = _native.FwDecodeArgs.from_buffer_copy(args)
+            part.batch = rows
+            part.q = q_dev[first:].data_ptr()
+            part.out = out[first:].data_ptr()
+            part.lse = 0 if lse is None else lse[first:].data_ptr()
+            part.cache_seqlens = lengths[first:].data_ptr()
+            if has_new and kernel_has_new:
+                part.k_new, part.v_new = k_dev[first:].data_ptr(), v_dev[first:].data_ptr()
+            if is_paged:
+                part.block_table = table[first:].data_ptr()
+            elif cache_batch_idx is not None:
+                part.cache_batch_idx = cache_batch_idx[first:].data_ptr()
+            elif first:
+                # identity mapping of a later slice: spell the cache rows out
+                rows_idx = torch.arange(first, first + rows, dtype=torch.int32, device=device)
+                part.cache_batch_idx = rows_idx.data_ptr()
+            if active is not None and first:
+                rebased = (active - first).clamp_(0, rows)
+                part.num_active = rebased.data_ptr()
+            nbytes = lib.fw_decode_workspace_bytes(ctypes.byref(part))
+            if nbytes == 0:
+                _native.check(lib.fw_decode_kvcache(ctypes.byref(part), stream))
+                raise RuntimeError(_native.last_error())
+            scratch = _native.workspace(device, nbytes)
+            part.workspace, part.workspace_bytes = scratch.data_ptr(), scratch.numel()
+            _native.check(lib.fw_decode_kvcache(ctypes.byref(part), stream))
     else:
         from flywheel_tpu.softmax_attention.prefill import paged_prefill_device
         if is_ragged:

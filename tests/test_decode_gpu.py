@@ -260,3 +260,12 @@ def test_repeatable_bitwise():
         bits = out.view(np.uint16)
         first = bits if first is None else first
         np.testing.assert_array_equal(bits, first)
+
+
+def test_batch_larger_than_one_launch_is_sliced():
+    """2500 requests: the host entry runs the kernel in slices of 2048 rows;
+    num_active falls inside the second slice."""
+    case = host_case(16, lens=tuple(int(x) for x in np.random.default_rng(3).integers(0, 40, 2500)),
+                     hq=4, hk=1, page_size=16, extra_pages=1)
+    out = run_case(case, num_active=2300)
+    assert not out[2300:].any()
