@@ -327,6 +327,10 @@ def bench_config(ns, name, device):
         keep = (kc, vc, q, k, v, lens_t, out)
     else:
         batch, hq, hk, q_len, window = 128, 64, 8, 4, 4095
+        # experiment knobs for profiling sessions; the defaults are the configuration
+        q_len = int(os.environ.get("FW_C3_QLEN", q_len))
+        window = int(os.environ.get("FW_C3_WINDOW", window))
+        softcap_value = float(os.environ.get("FW_C3_SOFTCAP", 50.0))
         lens = rng.integers(LEN_LO, LEN_HI + 1, batch).astype(np.int32)
         table, pool_pages = workloads.paged_table(rng, lens, q_len, PAGE, slack=0.10)
         pool = torch.empty((pool_pages, PAGE, 2 * hk, D), dtype=torch.float8_e4m3fn, device=device)
@@ -347,8 +351,8 @@ def bench_config(ns, name, device):
             k_descale=descale.data_ptr(), v_descale=descale.data_ptr(), sinks=sinks.data_ptr(),
             num_pages=pool_pages, page_size=PAGE, pages_per_seq=table.shape[1], batch=batch, seqlen_q=q_len,
             nheads=hq, nheads_k=hk, head_dim=D, kv_dtype=1, causal=1, window_left=window,
-            softmax_scale=D ** -0.5, softcap=50.0)
-        kv_bytes = workloads.decode_kv_bytes(lens, q_len, hk, D, 1, window_left=window)
+            softmax_scale=D ** -0.5, softcap=softcap_value)
+        kv_bytes = workloads.decode_kv_bytes(lens, q_len, hk, D, 1, window_left=window if window >= 0 else None)
         keep = (pool, descale, q, k, v, sinks, lens_t, table_t, out)
     nbytes = lib.fw_decode_workspace_bytes(ctypes.byref(args))
     if nbytes == 0:

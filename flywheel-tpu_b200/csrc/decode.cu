@@ -609,14 +609,16 @@ constexpr int kCombineWarps = 4;
 
 // Merges the segments of (token, head) rows.  WPR warps share one row and split
 // its segments between them: 1 when there are many rows with few segments
-// each (serving batches), 4 when few rows have many segments (one long
+// each (serving batches), 16 when few rows have many segments (one long
 // request cut over every SM).  Reads the tile prefix the decode kernel left in
 // the workspace, so the two agree on which CTAs touched the request.
 template <int WPR>
-__global__ void __launch_bounds__(kCombineWarps * 32) combine_kernel(const CombineParams cp) {
+__global__ void __launch_bounds__((WPR > kCombineWarps ? WPR : kCombineWarps) * 32)
+combine_kernel(const CombineParams cp) {
+  constexpr int kWarps = WPR > kCombineWarps ? WPR : kCombineWarps;  // warps per block
   const DecodeParams& p = cp.d;
-  __shared__ float4 red_acc[kCombineWarps][32];
-  __shared__ float red_den[kCombineWarps];
+  __shared__ float4 red_acc[kWarps][32];
+  __shared__ float red_den[kWarps];
   const int b = blockIdx.x;
   const int warp_in_block = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int sub = warp_in_block % WPR, warp = warp_in_block / WPR;
@@ -625,7 +627,7 @@ __global__ void __launch_bounds__(kCombineWarps * 32) combine_kernel(const Combi
   const int total_tiles = p.tile_prefix[p.batch];
   const Span sp = request_span(p, b, n_active);
   const int rq = p.seqlen_q * p.nheads;
-  const int row = blockIdx.y * (kCombineWarps / WPR) + warp;
+  const int row = blockIdx.y * (kWarps / WPR) + warp;
   if (row >= rq) return;  // with WPR > 1 a block holds one row: all its warps leave together
   const int t = row / p.nheads, hq = row - t * p.nheads;
   if (t >= sp.q_valid) return;  // not a real query row of this item
@@ -967,12 +969,12 @@ static int launch_decode(DecodePlan& plan, void* workspace, cudaStream_t stream,
   cp.partial_lse = partial_lse;
   cp.v_descale = v_descale;
   cp.sinks = sinks;
-  // Few rows with many segments each (a long request over every SM): let four
-  // warps share a row.
+  // Few rows with many segments each (a long request cut over every SM): 16
+  // warps share a row, so its ~150 segments are read in a few rounds.
   const bool wide = static_cast<long long>(p.batch) * plan.rows_q <= 2048;
   if (wide) {
     dim3 cgrid(p.batch, plan.rows_q);
-    combine_kernel<kCombineWarps><<<cgrid, kCombineWarps * 32, 0, stream>>>(cp);
+    combine_kernel<16><<<cgrid, 16 * 32, 0, stream>>>(cp);
   } else {
     dim3 cgrid(p.batch, (plan.rows_q + kCombineWarps - 1) / kCombineWarps);
     combine_kernel<1><<<cgrid, kCombineWarps * 32, 0, stream>>>(cp);
