@@ -541,9 +541,16 @@ def main():
         return
     if ns.prefill_only:
         pf = bench_prefill(ns, device, rank, world, barrier)
+        ms = torch.tensor([pf["ms"]], dtype=torch.float64, device=device)
+        flops = torch.tensor([float(pf["flops"])], dtype=torch.float64, device=device)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+            dist.all_reduce(flops, op=dist.ReduceOp.SUM)
         if rank == 0:
-            print(json.dumps({"metric": "chunked_prefill_tflops", "value": pf["flops"] / (pf["ms"] * 1e-3) / 1e12,
-                              "unit": "TFLOP/s", "ms_per_step": pf["ms"], "n_gpus": world}))
+            print(json.dumps({"metric": "chunked_prefill_tflops", "value": float(flops) / (float(ms) * 1e-3) / 1e12,
+                              "unit": "TFLOP/s", "ms_per_step": float(ms), "n_gpus": world}), flush=True)
+        if world > 1:
+            dist.destroy_process_group()
         return
 
     from flywheel_tpu import flash_attn_with_kvcache

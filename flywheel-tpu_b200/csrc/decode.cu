@@ -848,13 +848,13 @@ static int plan_decode(const FwDecodeArgs* a, DecodePlan* plan, int max_batch = 
   // MMAs to pipeline.  (Registers allow one CTA per SM either way.)  The stage
   // must divide the page.
   p.tile = kTile;
-  const int smem_budget = 200 * 1024;
+  const int smem_for_stages = 200 * 1024;
   if (itemsize == 1) {
     while (p.tile < 64 && segs_per_stage * (p.tile * 2) * 128 <= 64 * 1024 && a->page_size % (p.tile * 2) == 0)
       p.tile *= 2;
   }
   p.stage_bytes = segs_per_stage * p.tile * 128;
-  p.stages = min(kMaxStages, smem_budget / p.stage_bytes);
+  p.stages = min(kMaxStages, smem_for_stages / p.stage_bytes);
   if (p.stages < 2) {
     set_error("stage of %d bytes leaves fewer than two pipeline stages.", p.stage_bytes);
     return FW_ERR_UNSUPPORTED;

@@ -46,7 +46,9 @@ def digest(pages_f32):
 
 
 def main():
-    reference_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: make_golden.py /path/to/reference-checkout")
+    reference_root = sys.argv[1]
     ragged_reference = load_reference_functions(reference_root)
     for name in cases.CASES:
         c = cases.build(name)
