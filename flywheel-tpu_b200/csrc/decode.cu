@@ -616,6 +616,7 @@ template <int WPR>
 __global__ void __launch_bounds__((WPR > kCombineWarps ? WPR : kCombineWarps) * 32)
 combine_kernel(const CombineParams cp) {
   constexpr int kWarps = WPR > kCombineWarps ? WPR : kCombineWarps;  // warps per block
+  constexpr int kRowsPerBlock = kWarps / WPR;
   const DecodeParams& p = cp.d;
   __shared__ float4 red_acc[kWarps][32];
   __shared__ float red_den[kWarps];
@@ -627,11 +628,8 @@ combine_kernel(const CombineParams cp) {
   const int total_tiles = p.tile_prefix[p.batch];
   const Span sp = request_span(p, b, n_active);
   const int rq = p.seqlen_q * p.nheads;
-  const int row = blockIdx.y * (kWarps / WPR) + warp;
-  if (row >= rq) return;  // with WPR > 1 a block holds one row: all its warps leave together
-  const int t = row / p.nheads, hq = row - t * p.nheads;
-  if (t >= sp.q_valid) return;  // not a real query row of this item
 
+  // CTAs [c_lo, c_hi] touched this request; the same for every row of it.
   int c_lo = 0, c_hi = -1;
   if (sp.n_tiles > 0) {
     const long long nt = total_tiles;
@@ -646,88 +644,120 @@ combine_kernel(const CombineParams cp) {
     for (cta_range(nt, p.ncta, c_lo, f0, f1); f1 <= before && c_lo < p.ncta - 1;) cta_range(nt, p.ncta, ++c_lo, f0, f1);
     for (cta_range(nt, p.ncta, c_hi, f0, f1); f0 >= end && c_hi > 0;) cta_range(nt, p.ncta, --c_hi, f0, f1);
   }
-
-  const float sink2 = cp.sinks ? cp.sinks[hq] * kLog2e : -INFINITY;
-  float m_max = -INFINITY;
-  for (int c = c_lo + lane; c <= c_hi; c += 32) {
-    int f0, f1;
-    cta_range(total_tiles, p.ncta, c, f0, f1);
-    if (f1 <= f0) continue;
-    const long long prow = (static_cast<long long>(b) + c) * rq + row;
-    m_max = fmaxf(m_max, p.part_ml[prow * 2]);
-  }
-#pragma unroll
-  for (int off = 16; off; off >>= 1) m_max = fmaxf(m_max, __shfl_xor_sync(0xffffffffu, m_max, off));
-
-  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-  float den = 0.f;
-  if (m_max != -INFINITY) {
-    // Branch-free body so the loads of several segments are in flight at once.
-#pragma unroll 4
-    for (int c = c_lo + sub; c <= c_hi; c += WPR) {
+  // With at most 32 segments (every serving batch) which of them hold tiles is
+  // worked out once per warp instead of once per row and segment.
+  const bool few = c_hi - c_lo < 32;
+  unsigned live = 0;
+  if (few) {
+    bool has_tiles = false;
+    if (c_lo + lane <= c_hi) {
       int f0, f1;
-      cta_range(total_tiles, p.ncta, c, f0, f1);
+      cta_range(total_tiles, p.ncta, c_lo + lane, f0, f1);
+      has_tiles = f1 > f0;
+    }
+    live = __ballot_sync(0xffffffffu, has_tiles);
+  }
+  const float vd = cp.v_descale ? *cp.v_descale : 1.0f;
+
+  for (int row = blockIdx.y * kRowsPerBlock + warp; row < rq; row += gridDim.y * kRowsPerBlock) {
+    const int t = row / p.nheads, hq = row - t * p.nheads;
+    if (t >= sp.q_valid) break;  // rows are token-major: the rest are not real query rows either
+
+    float m_max = -INFINITY;
+    for (int c = c_lo + lane; c <= c_hi; c += 32) {
+      bool has_tiles;
+      if (few) {
+        has_tiles = (live >> lane) & 1u;
+      } else {
+        int f0, f1;
+        cta_range(total_tiles, p.ncta, c, f0, f1);
+        has_tiles = f1 > f0;
+      }
+      if (!has_tiles) continue;
       const long long prow = (static_cast<long long>(b) + c) * rq + row;
-      const float2 ml = *reinterpret_cast<const float2*>(p.part_ml + prow * 2);
-      const float4 o = *reinterpret_cast<const float4*>(p.part_o + prow * kHeadDim + lane * 4);
-      const float w = (f1 > f0 && ml.x != -INFINITY) ? fast_exp2(ml.x - m_max) : 0.f;
-      den += w == 0.f ? 0.f : ml.y * w;
-      acc.x += w == 0.f ? 0.f : o.x * w;
-      acc.y += w == 0.f ? 0.f : o.y * w;
-      acc.z += w == 0.f ? 0.f : o.z * w;
-      acc.w += w == 0.f ? 0.f : o.w * w;
+      m_max = fmaxf(m_max, p.part_ml[prow * 2]);
     }
-  }
-  if constexpr (WPR > 1) {
-    red_acc[warp_in_block][lane] = acc;
-    if (lane == 0) red_den[warp_in_block] = den;
-    __syncthreads();
-    if (sub != 0) return;
 #pragma unroll
-    for (int w = 1; w < WPR; ++w) {
-      const float4 o = red_acc[warp * WPR + w][lane];
-      acc.x += o.x;
-      acc.y += o.y;
-      acc.z += o.z;
-      acc.w += o.w;
-      den += red_den[warp * WPR + w];
-    }
-  }
+    for (int off = 16; off; off >>= 1) m_max = fmaxf(m_max, __shfl_xor_sync(0xffffffffu, m_max, off));
 
-  if (cp.partial_out != nullptr) {
-    // Sink-free normalised state for a cross-GPU merge.
-    const long long orow = static_cast<long long>(b) * rq + row;
-    const float inv = den > 0.f ? 1.f / den : 0.f;
-    const float vd = cp.v_descale ? *cp.v_descale : 1.0f;
-    *reinterpret_cast<float4*>(cp.partial_out + orow * kHeadDim + lane * 4) =
-        make_float4(acc.x * inv * vd, acc.y * inv * vd, acc.z * inv * vd, acc.w * inv * vd);
-    if (lane == 0) cp.partial_lse[orow] = den > 0.f ? (m_max + log2f(den)) * kLn2 : -INFINITY;
-    return;
-  }
-
-  // Fold the sink: it joins the denominator only.
-  float m_all = fmaxf(m_max, sink2);
-  float out_scale = 0.f, lse = -INFINITY;
-  if (m_all != -INFINITY) {
-    const float w_keys = m_max == -INFINITY ? 0.f : fast_exp2(m_max - m_all);
-    const float den_all = den * w_keys + (sink2 == -INFINITY ? 0.f : fast_exp2(sink2 - m_all));
-    if (den_all > 0.f) {
-      const float vd = cp.v_descale ? *cp.v_descale : 1.0f;
-      out_scale = w_keys * vd / den_all;
-      lse = (m_all + log2f(den_all)) * kLn2;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    float den = 0.f;
+    if (m_max != -INFINITY) {
+      // Branch-free body so the loads of several segments are in flight at once.
+#pragma unroll 4
+      for (int c = c_lo + sub; c <= c_hi; c += WPR) {
+        bool has_tiles;
+        if (few) {
+          has_tiles = (live >> (c - c_lo)) & 1u;
+        } else {
+          int f0, f1;
+          cta_range(total_tiles, p.ncta, c, f0, f1);
+          has_tiles = f1 > f0;
+        }
+        const long long prow = (static_cast<long long>(b) + c) * rq + row;
+        const float2 ml = *reinterpret_cast<const float2*>(p.part_ml + prow * 2);
+        const float4 o = *reinterpret_cast<const float4*>(p.part_o + prow * kHeadDim + lane * 4);
+        const float w = (has_tiles && ml.x != -INFINITY) ? fast_exp2(ml.x - m_max) : 0.f;
+        den += w == 0.f ? 0.f : ml.y * w;
+        acc.x += w == 0.f ? 0.f : o.x * w;
+        acc.y += w == 0.f ? 0.f : o.y * w;
+        acc.z += w == 0.f ? 0.f : o.z * w;
+        acc.w += w == 0.f ? 0.f : o.w * w;
+      }
     }
-  }
-  const long long ooff = (static_cast<long long>(sp.q_row0) + t) * p.q_tok_stride +
-                         static_cast<long long>(hq) * p.q_head_stride;
-  uint2 packed;
-  packed.x = pack_bf16(acc.x * out_scale, acc.y * out_scale);
-  packed.y = pack_bf16(acc.z * out_scale, acc.w * out_scale);
-  *reinterpret_cast<uint2*>(cp.out + ooff + lane * 4) = packed;
-  if (cp.lse != nullptr && lane == 0) {
-    if (p.items != nullptr)
-      cp.lse[static_cast<long long>(hq) * p.total_q + sp.q_row0 + t] = lse;
-    else
-      cp.lse[(static_cast<long long>(b) * p.nheads + hq) * p.seqlen_q + t] = lse;
+    if constexpr (WPR > 1) {
+      // A block of the wide form holds one row, so its warps take every branch
+      // of this loop together.
+      __syncthreads();
+      red_acc[warp_in_block][lane] = acc;
+      if (lane == 0) red_den[warp_in_block] = den;
+      __syncthreads();
+      if (sub != 0) continue;
+#pragma unroll
+      for (int w = 1; w < WPR; ++w) {
+        const float4 o = red_acc[warp * WPR + w][lane];
+        acc.x += o.x;
+        acc.y += o.y;
+        acc.z += o.z;
+        acc.w += o.w;
+        den += red_den[warp * WPR + w];
+      }
+    }
+
+    if (cp.partial_out != nullptr) {
+      // Sink-free normalised state for a cross-GPU merge.
+      const long long orow = static_cast<long long>(b) * rq + row;
+      const float inv = den > 0.f ? 1.f / den : 0.f;
+      *reinterpret_cast<float4*>(cp.partial_out + orow * kHeadDim + lane * 4) =
+          make_float4(acc.x * inv * vd, acc.y * inv * vd, acc.z * inv * vd, acc.w * inv * vd);
+      if (lane == 0) cp.partial_lse[orow] = den > 0.f ? (m_max + log2f(den)) * kLn2 : -INFINITY;
+      continue;
+    }
+
+    // Fold the sink: it joins the denominator only.
+    const float sink2 = cp.sinks ? cp.sinks[hq] * kLog2e : -INFINITY;
+    const float m_all = fmaxf(m_max, sink2);
+    float out_scale = 0.f, lse = -INFINITY;
+    if (m_all != -INFINITY) {
+      const float w_keys = m_max == -INFINITY ? 0.f : fast_exp2(m_max - m_all);
+      const float den_all = den * w_keys + (sink2 == -INFINITY ? 0.f : fast_exp2(sink2 - m_all));
+      if (den_all > 0.f) {
+        out_scale = w_keys * vd / den_all;
+        lse = (m_all + log2f(den_all)) * kLn2;
+      }
+    }
+    const long long ooff = (static_cast<long long>(sp.q_row0) + t) * p.q_tok_stride +
+                           static_cast<long long>(hq) * p.q_head_stride;
+    uint2 packed;
+    packed.x = pack_bf16(acc.x * out_scale, acc.y * out_scale);
+    packed.y = pack_bf16(acc.z * out_scale, acc.w * out_scale);
+    *reinterpret_cast<uint2*>(cp.out + ooff + lane * 4) = packed;
+    if (cp.lse != nullptr && lane == 0) {
+      if (p.items != nullptr)
+        cp.lse[static_cast<long long>(hq) * p.total_q + sp.q_row0 + t] = lse;
+      else
+        cp.lse[(static_cast<long long>(b) * p.nheads + hq) * p.seqlen_q + t] = lse;
+    }
   }
 }
 
@@ -850,7 +880,9 @@ static int plan_decode(const FwDecodeArgs* a, DecodePlan* plan, int max_batch = 
   p.tile = kTile;
   const int smem_for_stages = 200 * 1024;
   if (itemsize == 1) {
-    while (p.tile < 64 && segs_per_stage * (p.tile * 2) * 128 <= 64 * 1024 && a->page_size % (p.tile * 2) == 0)
+    // Verify windows (two or more 16-row slices per head) measured best at 32.
+    const int max_tile = mt >= 2 ? 32 : 64;
+    while (p.tile < max_tile && segs_per_stage * (p.tile * 2) * 128 <= 64 * 1024 && a->page_size % (p.tile * 2) == 0)
       p.tile *= 2;
   }
   p.stage_bytes = segs_per_stage * p.tile * 128;
@@ -976,7 +1008,11 @@ static int launch_decode(DecodePlan& plan, void* workspace, cudaStream_t stream,
     dim3 cgrid(p.batch, plan.rows_q);
     combine_kernel<16><<<cgrid, 16 * 32, 0, stream>>>(cp);
   } else {
-    dim3 cgrid(p.batch, (plan.rows_q + kCombineWarps - 1) / kCombineWarps);
+    // Each warp walks several rows of its request, so the per-request
+    // bookkeeping is paid once per warp; enough blocks to fill the machine.
+    const int blocks_per_request = (plan.rows_q + kCombineWarps - 1) / kCombineWarps;
+    const int wanted = (8 * sm_count() + p.batch - 1) / p.batch;
+    dim3 cgrid(p.batch, max(1, min(blocks_per_request, wanted)));
     combine_kernel<1><<<cgrid, kCombineWarps * 32, 0, stream>>>(cp);
   }
   err = cudaGetLastError();
