@@ -646,9 +646,11 @@ combine_kernel(const CombineParams cp) {
   }
   // With at most 32 segments (every serving batch) which of them hold tiles is
   // worked out once per warp instead of once per row and segment.
+  // (With at least one tile per CTA, every CTA holds tiles.)
+  const bool all_live = total_tiles >= p.ncta;
   const bool few = c_hi - c_lo < 32;
   unsigned live = 0;
-  if (few) {
+  if (few && !all_live) {
     bool has_tiles = false;
     if (c_lo + lane <= c_hi) {
       int f0, f1;
@@ -665,8 +667,9 @@ combine_kernel(const CombineParams cp) {
 
     float m_max = -INFINITY;
     for (int c = c_lo + lane; c <= c_hi; c += 32) {
-      bool has_tiles;
-      if (few) {
+      bool has_tiles = true;
+      if (all_live) {
+      } else if (few) {
         has_tiles = (live >> lane) & 1u;
       } else {
         int f0, f1;
@@ -686,8 +689,9 @@ combine_kernel(const CombineParams cp) {
       // Branch-free body so the loads of several segments are in flight at once.
 #pragma unroll 4
       for (int c = c_lo + sub; c <= c_hi; c += WPR) {
-        bool has_tiles;
-        if (few) {
+        bool has_tiles = true;
+        if (all_live) {
+        } else if (few) {
           has_tiles = (live >> (c - c_lo)) & 1u;
         } else {
           int f0, f1;
