@@ -106,9 +106,11 @@ struct MergeParams {
   float* lse;
   int parts, rows, nheads, lse_head_stride, lse_token_stride;
   long long stride_out, stride_lse;
+  int head_dim;
 };
 
-// One warp per (token, head) row; head_dim 128 = 32 lanes x float4.
+// One warp per (token, head) row; a lane owns four columns of every
+// 128-column block of the head (one block at head_dim 128, two at 256).
 __global__ void __launch_bounds__(128) merge_kernel(const MergeParams p) {
   const int row = blockIdx.x * 4 + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
@@ -117,7 +119,8 @@ __global__ void __launch_bounds__(128) merge_kernel(const MergeParams p) {
   const float sink = p.sinks ? p.sinks[head] : -INFINITY;
   float top = sink;
   for (int i = 0; i < p.parts; ++i) top = fmaxf(top, p.partial_lse[i * p.stride_lse + row]);
-  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  float4 acc[2] = {make_float4(0.f, 0.f, 0.f, 0.f), make_float4(0.f, 0.f, 0.f, 0.f)};
+  const int blocks = p.head_dim / 128;
   float den = 0.f;
   if (top != -INFINITY) {
     for (int i = 0; i < p.parts; ++i) {
@@ -125,20 +128,28 @@ __global__ void __launch_bounds__(128) merge_kernel(const MergeParams p) {
       if (l == -INFINITY) continue;
       const float w = __expf(l - top);
       den += w;
-      const float4 o = *reinterpret_cast<const float4*>(
-          p.partial_out + i * p.stride_out + static_cast<long long>(row) * 128 + lane * 4);
-      acc.x += o.x * w;
-      acc.y += o.y * w;
-      acc.z += o.z * w;
-      acc.w += o.w * w;
+#pragma unroll
+      for (int nb = 0; nb < 2; ++nb) {
+        if (nb >= blocks) break;
+        const float4 o = *reinterpret_cast<const float4*>(
+            p.partial_out + i * p.stride_out + static_cast<long long>(row) * p.head_dim + nb * 128 + lane * 4);
+        acc[nb].x += o.x * w;
+        acc[nb].y += o.y * w;
+        acc[nb].z += o.z * w;
+        acc[nb].w += o.w * w;
+      }
     }
     if (sink != -INFINITY) den += __expf(sink - top);
   }
   const float inv = den > 0.f ? 1.f / den : 0.f;
-  uint2 packed;
-  packed.x = pack_bf16(acc.x * inv, acc.y * inv);
-  packed.y = pack_bf16(acc.z * inv, acc.w * inv);
-  *reinterpret_cast<uint2*>(p.out + static_cast<long long>(row) * 128 + lane * 4) = packed;
+#pragma unroll
+  for (int nb = 0; nb < 2; ++nb) {
+    if (nb >= blocks) break;
+    uint2 packed;
+    packed.x = pack_bf16(acc[nb].x * inv, acc[nb].y * inv);
+    packed.y = pack_bf16(acc[nb].z * inv, acc[nb].w * inv);
+    *reinterpret_cast<uint2*>(p.out + static_cast<long long>(row) * p.head_dim + nb * 128 + lane * 4) = packed;
+  }
   if (p.lse != nullptr && lane == 0)
     p.lse[static_cast<long long>(head) * p.lse_head_stride + static_cast<long long>(tok) * p.lse_token_stride] =
         den > 0.f ? top + logf(den) : -INFINITY;
@@ -260,8 +271,8 @@ extern "C" int fw_lse_combine(const FwCombineArgs* a, void* stream_ptr) {
     set_error("partial_out, partial_lse and out must not be NULL.");
     return FW_ERR_BAD_SHAPE;
   }
-  if (a->head_dim != 128) {
-    set_error("head_dim %d is not built; this library serves head_dim 128.", a->head_dim);
+  if (a->head_dim != 128 && a->head_dim != 256) {
+    set_error("head_dim %d is not built; this library serves head_dim 128 and 256.", a->head_dim);
     return FW_ERR_UNSUPPORTED;
   }
   if (a->parts <= 0 || a->rows < 0 || a->nheads <= 0) {
@@ -271,8 +282,8 @@ extern "C" int fw_lse_combine(const FwCombineArgs* a, void* stream_ptr) {
   if (a->rows == 0) return FW_OK;
   MergeParams p{a->partial_out, a->partial_lse, a->sinks, static_cast<__nv_bfloat16*>(a->out), a->lse,
                 a->parts, a->rows, a->nheads, a->lse_head_stride, a->lse_token_stride,
-                a->part_stride_out ? a->part_stride_out : static_cast<long long>(a->rows) * 128,
-                a->part_stride_lse ? a->part_stride_lse : static_cast<long long>(a->rows)};
+                a->part_stride_out ? a->part_stride_out : static_cast<long long>(a->rows) * a->head_dim,
+                a->part_stride_lse ? a->part_stride_lse : static_cast<long long>(a->rows), a->head_dim};
   merge_kernel<<<(a->rows + 3) / 4, 128, 0, static_cast<cudaStream_t>(stream_ptr)>>>(p);
   cudaError_t err = cudaGetLastError();
   if (err != cudaSuccess) {

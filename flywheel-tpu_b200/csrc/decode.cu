@@ -31,7 +31,7 @@ namespace fw {
 constexpr int kTile = 16;          // smallest stage: tokens per MMA k-step; page sizes are multiples of it
 constexpr int kMaxStages = 8;
 constexpr int kMaxConsumerWarps = 8;
-constexpr int kHeadDim = 128;
+constexpr int kMaxHeadDim = 256;   // head_dim 128 and 256 are built
 constexpr int kMaxInlineBatch = 2048;  // requests whose tile counts fit the CTA-local scan
 
 struct DecodeParams {
@@ -58,6 +58,7 @@ struct DecodeParams {
   int spp;          // 128-byte segments per head plane
   int stages, stage_bytes;
   int tile;         // tokens per pipeline stage (16, 32 or 64)
+  int head_dim;     // 128 or 256
   int has_new, causal, window_left;
   int zero_pad_head;  // fp8 merged pool with an odd nheads_k: append zeroes the pad head
   float scale, softcap;
@@ -161,12 +162,16 @@ __device__ __forceinline__ int v_seg(const DecodeParams& p, int hl) {
   return p.merged ? (2 * hl + 1) * p.spp : (p.hpc + hl) * p.spp;
 }
 
-template <int KVT, int TILE>
-__global__ void __launch_bounds__((kMaxConsumerWarps + 1) * 32, 1)
+// D = head_dim.  At 256 a thread carries 128 output and 64 query registers, so
+// the block is sized for four consumer warps instead of eight.
+template <int KVT, int TILE, int D = 128>
+__global__ void __launch_bounds__(((D > 128 ? kMaxConsumerWarps / 2 : kMaxConsumerWarps) + 1) * 32, 1)
 decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
               const DecodeParams p) {
   constexpr bool kFp8 = KVT != FW_DTYPE_BF16;
   constexpr int NU = TILE / 16;  // 16-key MMA sub-tiles per stage
+  constexpr int KS = D / 16;     // 16-wide k-steps over head_dim
+  constexpr int ND = D / 8;      // 8-wide output column tiles
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
@@ -300,14 +305,14 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
     const bool row0_ok = row0_in && t0 < sp.q_valid, row1_ok = row1_in && t1 < sp.q_valid;
 
     // ---- Q fragments of this warp's 16 rows (zero for rows past the window)
-    uint32_t qa[8][4];
+    uint32_t qa[KS][4];
     {
       const __nv_bfloat16* q0 = p.q + (static_cast<long long>(sp.q_row0) + t0) * p.q_tok_stride +
                                 static_cast<long long>(h * p.group + g0) * p.q_head_stride;
       const __nv_bfloat16* q1 = p.q + (static_cast<long long>(sp.q_row0) + t1) * p.q_tok_stride +
                                 static_cast<long long>(h * p.group + g1) * p.q_head_stride;
 #pragma unroll
-      for (int ks = 0; ks < 8; ++ks) {
+      for (int ks = 0; ks < KS; ++ks) {
         if constexpr (!kFp8) {
           const int d = ks * 16 + 2 * tq;
           qa[ks][0] = row0_ok ? *reinterpret_cast<const uint32_t*>(q0 + d) : 0u;
@@ -331,9 +336,9 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
         }
       }
     }
-    float o[16][4];
+    float o[ND][4];
 #pragma unroll
-    for (int i = 0; i < 16; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    for (int i = 0; i < ND; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
     float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
     // Bottom-right diagonals of the two rows this thread owns.
     const int diag0 = sp.diag_base + t0, diag1 = sp.diag_base + t1;
@@ -413,7 +418,7 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
         const int mi = lane >> 3;
         const int key = u * 16 + ((mi >> 1) << 3) + (lane & 7);
 #pragma unroll
-        for (int ks = 0; ks < 8; ++ks) {
+        for (int ks = 0; ks < KS; ++ks) {
           const int chunk = ks * 2 + (mi & 1);
           const uint32_t addr = st + (kseg + (chunk >> 3)) * seg_bytes + key * 128 +
                                 (((chunk & 7) ^ (key & 7)) << 4);
@@ -426,9 +431,10 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
         const int mi = lane >> 3;
         const int key = u * 16 + ((mi & 1) << 3) + (lane & 7);
 #pragma unroll
-        for (int kp = 0; kp < 4; ++kp) {
+        for (int kp = 0; kp < KS / 2; ++kp) {
           const int chunk = kp * 2 + (mi >> 1);
-          const uint32_t addr = st + kseg * seg_bytes + key * 128 + (((chunk & 7) ^ (key & 7)) << 4);
+          const uint32_t addr = st + (kseg + (chunk >> 3)) * seg_bytes + key * 128 +
+                                (((chunk & 7) ^ (key & 7)) << 4);
           uint32_t r0, r1, r2, r3;  // (keys 0-7, c), (keys 8-15, c), (keys 0-7, c+1), (keys 8-15, c+1)
           ldmatrix_x4(addr, r0, r1, r2, r3);
           mma_f16(s[u][0], qa[2 * kp], fp8x2_to_f16x2<KVT>(r0 & 0xffff), fp8x2_to_f16x2<KVT>(r0 >> 16));
@@ -494,7 +500,7 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
       }
       if (__any_sync(0xffffffffu, alpha[0] != 1.f || alpha[1] != 1.f)) {
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
+        for (int i = 0; i < ND; ++i) {
           o[i][0] *= alpha[0];
           o[i][1] *= alpha[0];
           o[i][2] *= alpha[1];
@@ -514,7 +520,7 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
         const int mi = lane >> 3;
         const int key = u * 16 + ((mi & 1) << 3) + (lane & 7);
 #pragma unroll
-        for (int cp = 0; cp < 8; ++cp) {
+        for (int cp = 0; cp < ND / 2; ++cp) {
           const int chunk = cp * 2 + (mi >> 1);
           const uint32_t addr = st + (vseg + (chunk >> 3)) * seg_bytes + key * 128 +
                                 (((chunk & 7) ^ (key & 7)) << 4);
@@ -531,9 +537,10 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
         const int mi = lane >> 3;
         const int key = u * 16 + ((mi & 1) << 3) + (lane & 7);
 #pragma unroll
-        for (int cp = 0; cp < 4; ++cp) {
+        for (int cp = 0; cp < ND / 4; ++cp) {
           const int chunk = cp * 2 + (mi >> 1);
-          const uint32_t addr = st + vseg * seg_bytes + key * 128 + (((chunk & 7) ^ (key & 7)) << 4);
+          const uint32_t addr = st + (vseg + (chunk >> 3)) * seg_bytes + key * 128 +
+                                (((chunk & 7) ^ (key & 7)) << 4);
           uint32_t r0, r1, r2, r3;  // (keys 0-7, c), (keys 8-15, c), (keys 0-7, c+1), (keys 8-15, c+1)
           ldmatrix_x4_trans(addr, r0, r1, r2, r3);
           // Each register holds keys (2tq, 2tq+1) x head_dim (2u, 2u+1); regroup
@@ -575,14 +582,14 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
         p.part_ml[prow * 2] = m_run[r];
         p.part_ml[prow * 2 + 1] = l_run[r];
       }
-      float* po = p.part_o + prow * kHeadDim;
+      float* po = p.part_o + prow * D;
       if constexpr (!kFp8) {
 #pragma unroll
-        for (int nd = 0; nd < 16; ++nd)
+        for (int nd = 0; nd < ND; ++nd)
           *reinterpret_cast<float2*>(po + nd * 8 + 2 * tq) = make_float2(o[nd][2 * r], o[nd][2 * r + 1]);
       } else {
 #pragma unroll
-        for (int c = 0; c < 8; ++c)
+        for (int c = 0; c < ND / 2; ++c)
           *reinterpret_cast<float4*>(po + c * 16 + 4 * tq) =
               make_float4(o[2 * c][2 * r], o[2 * c + 1][2 * r], o[2 * c][2 * r + 1], o[2 * c + 1][2 * r + 1]);
       }
@@ -612,13 +619,14 @@ constexpr int kCombineWarps = 4;
 // each (serving batches), 16 when few rows have many segments (one long
 // request cut over every SM).  Reads the tile prefix the decode kernel left in
 // the workspace, so the two agree on which CTAs touched the request.
-template <int WPR>
+template <int WPR, int D>
 __global__ void __launch_bounds__((WPR > kCombineWarps ? WPR : kCombineWarps) * 32)
 combine_kernel(const CombineParams cp) {
   constexpr int kWarps = WPR > kCombineWarps ? WPR : kCombineWarps;  // warps per block
   constexpr int kRowsPerBlock = kWarps / WPR;
+  constexpr int NB = D / 128;  // a lane owns four columns of every 128-column block
   const DecodeParams& p = cp.d;
-  __shared__ float4 red_acc[kWarps][32];
+  __shared__ float4 red_acc[kWarps][NB][32];
   __shared__ float red_den[kWarps];
   const int b = blockIdx.x;
   const int warp_in_block = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -683,7 +691,9 @@ combine_kernel(const CombineParams cp) {
 #pragma unroll
     for (int off = 16; off; off >>= 1) m_max = fmaxf(m_max, __shfl_xor_sync(0xffffffffu, m_max, off));
 
-    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    float4 acc[NB];
+#pragma unroll
+    for (int nb = 0; nb < NB; ++nb) acc[nb] = make_float4(0.f, 0.f, 0.f, 0.f);
     float den = 0.f;
     if (m_max != -INFINITY) {
       // Branch-free body so the loads of several segments are in flight at once.
@@ -700,30 +710,40 @@ combine_kernel(const CombineParams cp) {
         }
         const long long prow = (static_cast<long long>(b) + c) * rq + row;
         const float2 ml = *reinterpret_cast<const float2*>(p.part_ml + prow * 2);
-        const float4 o = *reinterpret_cast<const float4*>(p.part_o + prow * kHeadDim + lane * 4);
+        float4 o[NB];
+#pragma unroll
+        for (int nb = 0; nb < NB; ++nb)
+          o[nb] = *reinterpret_cast<const float4*>(p.part_o + prow * D + nb * 128 + lane * 4);
         const float w = (has_tiles && ml.x != -INFINITY) ? fast_exp2(ml.x - m_max) : 0.f;
         den += w == 0.f ? 0.f : ml.y * w;
-        acc.x += w == 0.f ? 0.f : o.x * w;
-        acc.y += w == 0.f ? 0.f : o.y * w;
-        acc.z += w == 0.f ? 0.f : o.z * w;
-        acc.w += w == 0.f ? 0.f : o.w * w;
+#pragma unroll
+        for (int nb = 0; nb < NB; ++nb) {
+          acc[nb].x += w == 0.f ? 0.f : o[nb].x * w;
+          acc[nb].y += w == 0.f ? 0.f : o[nb].y * w;
+          acc[nb].z += w == 0.f ? 0.f : o[nb].z * w;
+          acc[nb].w += w == 0.f ? 0.f : o[nb].w * w;
+        }
       }
     }
     if constexpr (WPR > 1) {
       // A block of the wide form holds one row, so its warps take every branch
       // of this loop together.
       __syncthreads();
-      red_acc[warp_in_block][lane] = acc;
+#pragma unroll
+      for (int nb = 0; nb < NB; ++nb) red_acc[warp_in_block][nb][lane] = acc[nb];
       if (lane == 0) red_den[warp_in_block] = den;
       __syncthreads();
       if (sub != 0) continue;
 #pragma unroll
       for (int w = 1; w < WPR; ++w) {
-        const float4 o = red_acc[warp * WPR + w][lane];
-        acc.x += o.x;
-        acc.y += o.y;
-        acc.z += o.z;
-        acc.w += o.w;
+#pragma unroll
+        for (int nb = 0; nb < NB; ++nb) {
+          const float4 o = red_acc[warp * WPR + w][nb][lane];
+          acc[nb].x += o.x;
+          acc[nb].y += o.y;
+          acc[nb].z += o.z;
+          acc[nb].w += o.w;
+        }
         den += red_den[warp * WPR + w];
       }
     }
@@ -732,8 +752,10 @@ combine_kernel(const CombineParams cp) {
       // Sink-free normalised state for a cross-GPU merge.
       const long long orow = static_cast<long long>(b) * rq + row;
       const float inv = den > 0.f ? 1.f / den : 0.f;
-      *reinterpret_cast<float4*>(cp.partial_out + orow * kHeadDim + lane * 4) =
-          make_float4(acc.x * inv * vd, acc.y * inv * vd, acc.z * inv * vd, acc.w * inv * vd);
+#pragma unroll
+      for (int nb = 0; nb < NB; ++nb)
+        *reinterpret_cast<float4*>(cp.partial_out + orow * D + nb * 128 + lane * 4) = make_float4(
+            acc[nb].x * inv * vd, acc[nb].y * inv * vd, acc[nb].z * inv * vd, acc[nb].w * inv * vd);
       if (lane == 0) cp.partial_lse[orow] = den > 0.f ? (m_max + log2f(den)) * kLn2 : -INFINITY;
       continue;
     }
@@ -752,10 +774,13 @@ combine_kernel(const CombineParams cp) {
     }
     const long long ooff = (static_cast<long long>(sp.q_row0) + t) * p.q_tok_stride +
                            static_cast<long long>(hq) * p.q_head_stride;
-    uint2 packed;
-    packed.x = pack_bf16(acc.x * out_scale, acc.y * out_scale);
-    packed.y = pack_bf16(acc.z * out_scale, acc.w * out_scale);
-    *reinterpret_cast<uint2*>(cp.out + ooff + lane * 4) = packed;
+#pragma unroll
+    for (int nb = 0; nb < NB; ++nb) {
+      uint2 packed;
+      packed.x = pack_bf16(acc[nb].x * out_scale, acc[nb].y * out_scale);
+      packed.y = pack_bf16(acc[nb].z * out_scale, acc[nb].w * out_scale);
+      *reinterpret_cast<uint2*>(cp.out + ooff + nb * 128 + lane * 4) = packed;
+    }
     if (cp.lse != nullptr && lane == 0) {
       if (p.items != nullptr)
         cp.lse[static_cast<long long>(hq) * p.total_q + sp.q_row0 + t] = lse;
@@ -793,8 +818,8 @@ static int plan_decode(const FwDecodeArgs* a, DecodePlan* plan, int max_batch = 
     set_error("nheads=%d must be a multiple of nheads_k=%d.", a->nheads, a->nheads_k);
     return FW_ERR_BAD_SHAPE;
   }
-  if (a->head_dim != kHeadDim) {
-    set_error("head_dim %d is not built; this library serves head_dim 128.", a->head_dim);
+  if (a->head_dim != 128 && a->head_dim != kMaxHeadDim) {
+    set_error("head_dim %d is not built; this library serves head_dim 128 and 256.", a->head_dim);
     return FW_ERR_UNSUPPORTED;
   }
   if (paged) {
@@ -855,9 +880,11 @@ static int plan_decode(const FwDecodeArgs* a, DecodePlan* plan, int max_batch = 
   const int group = a->nheads / a->nheads_k;
   const int rows_per_head = a->seqlen_q * group;
   const int mt = (rows_per_head + 15) / 16;
-  if (mt > kMaxConsumerWarps) {
-    set_error("seqlen_q * (nheads / nheads_k) = %d exceeds %d query rows per KV head.", rows_per_head,
-              16 * kMaxConsumerWarps);
+  // head_dim 256 doubles the registers a warp needs; its block has four consumer warps.
+  const int max_warps = a->head_dim > 128 ? kMaxConsumerWarps / 2 : kMaxConsumerWarps;
+  if (mt > max_warps) {
+    set_error("seqlen_q * (nheads / nheads_k) = %d exceeds %d query rows per KV head at head_dim %d.",
+              rows_per_head, 16 * max_warps, a->head_dim);
     return FW_ERR_UNSUPPORTED;
   }
   const int itemsize = a->kv_dtype == FW_DTYPE_BF16 ? 2 : 1;
@@ -867,7 +894,11 @@ static int plan_decode(const FwDecodeArgs* a, DecodePlan* plan, int max_batch = 
   p.spp = p.plane_bytes / 128;
   p.merged = paged ? 1 : 0;
   p.mt = mt;
-  p.hpc = max(1, min(a->nheads_k, kMaxConsumerWarps / mt));
+  p.head_dim = a->head_dim;
+  // Heads per CTA: as many as there are warps for, and no more than keep a
+  // 16-token stage within 64 KiB.
+  p.hpc = max(1, min(a->nheads_k, max_warps / mt));
+  p.hpc = max(1, min(p.hpc, 64 * 1024 / (2 * p.spp * kTile * 128)));
   p.nhg = (a->nheads_k + p.hpc - 1) / p.hpc;
   const int heads_per_word = itemsize == 1 ? 2 : 1;
   const int cache_heads = paged ? 2 * ((a->nheads_k + heads_per_word - 1) / heads_per_word * heads_per_word)
@@ -885,7 +916,7 @@ static int plan_decode(const FwDecodeArgs* a, DecodePlan* plan, int max_batch = 
   const int smem_for_stages = 200 * 1024;
   if (itemsize == 1) {
     // Verify windows (two or more 16-row slices per head) measured best at 32.
-    const int max_tile = mt >= 2 ? 32 : 64;
+    const int max_tile = a->head_dim > 128 ? kTile : mt >= 2 ? 32 : 64;
     while (p.tile < max_tile && segs_per_stage * (p.tile * 2) * 128 <= 64 * 1024 && a->page_size % (p.tile * 2) == 0)
       p.tile *= 2;
   }
@@ -926,8 +957,8 @@ static int plan_decode(const FwDecodeArgs* a, DecodePlan* plan, int max_batch = 
   p.scale = a->softmax_scale;
   p.softcap = a->softcap;
   p.items = nullptr;
-  p.q_tok_stride = static_cast<long long>(a->nheads) * kHeadDim;
-  p.q_head_stride = kHeadDim;
+  p.q_tok_stride = static_cast<long long>(a->nheads) * a->head_dim;
+  p.q_head_stride = a->head_dim;
   p.total_q = a->batch * a->seqlen_q;
   plan->itemsize = itemsize;
   plan->rows_q = a->seqlen_q * a->nheads;
@@ -936,7 +967,7 @@ static int plan_decode(const FwDecodeArgs* a, DecodePlan* plan, int max_batch = 
   plan->off_ml = (plan->off_prefix + (static_cast<uint64_t>(a->batch) + 1) * sizeof(int) + 255) & ~255ull;
   const uint64_t ml_bytes = static_cast<uint64_t>(plan->slots) * plan->rows_q * 2 * sizeof(float);
   plan->off_o = (plan->off_ml + ml_bytes + 255) & ~255ull;
-  plan->bytes = plan->off_o + static_cast<uint64_t>(plan->slots) * plan->rows_q * kHeadDim * sizeof(float);
+  plan->bytes = plan->off_o + static_cast<uint64_t>(plan->slots) * plan->rows_q * a->head_dim * sizeof(float);
   return FW_OK;
 }
 
@@ -972,7 +1003,15 @@ static int launch_decode(DecodePlan& plan, void* workspace, cudaStream_t stream,
 
   using Kernel = void (*)(const CUtensorMap, const CUtensorMap, const DecodeParams);
   Kernel kernel = nullptr;
-  if (kv_dtype == FW_DTYPE_BF16) {
+  if (p.head_dim == kMaxHeadDim) {
+    if (kv_dtype == FW_DTYPE_BF16) {
+      kernel = decode_kernel<FW_DTYPE_BF16, 16, 256>;
+    } else if (kv_dtype == FW_DTYPE_E4M3) {
+      kernel = decode_kernel<FW_DTYPE_E4M3, 16, 256>;
+    } else {
+      kernel = decode_kernel<FW_DTYPE_E5M2, 16, 256>;
+    }
+  } else if (kv_dtype == FW_DTYPE_BF16) {
     kernel = decode_kernel<FW_DTYPE_BF16, 16>;
   } else if (kv_dtype == FW_DTYPE_E4M3) {
     kernel = p.tile == 64   ? decode_kernel<FW_DTYPE_E4M3, 64>
@@ -1008,16 +1047,23 @@ static int launch_decode(DecodePlan& plan, void* workspace, cudaStream_t stream,
   // Few rows with many segments each (a long request cut over every SM): 16
   // warps share a row, so its ~150 segments are read in a few rounds.
   const bool wide = static_cast<long long>(p.batch) * plan.rows_q <= 2048;
+  const bool d256 = p.head_dim == kMaxHeadDim;
   if (wide) {
     dim3 cgrid(p.batch, plan.rows_q);
-    combine_kernel<16><<<cgrid, 16 * 32, 0, stream>>>(cp);
+    if (d256)
+      combine_kernel<16, 256><<<cgrid, 16 * 32, 0, stream>>>(cp);
+    else
+      combine_kernel<16, 128><<<cgrid, 16 * 32, 0, stream>>>(cp);
   } else {
     // Each warp walks several rows of its request, so the per-request
     // bookkeeping is paid once per warp; enough blocks to fill the machine.
     const int blocks_per_request = (plan.rows_q + kCombineWarps - 1) / kCombineWarps;
     const int wanted = (8 * sm_count() + p.batch - 1) / p.batch;
     dim3 cgrid(p.batch, max(1, min(blocks_per_request, wanted)));
-    combine_kernel<1><<<cgrid, kCombineWarps * 32, 0, stream>>>(cp);
+    if (d256)
+      combine_kernel<1, 256><<<cgrid, kCombineWarps * 32, 0, stream>>>(cp);
+    else
+      combine_kernel<1, 128><<<cgrid, kCombineWarps * 32, 0, stream>>>(cp);
   }
   err = cudaGetLastError();
   if (err != cudaSuccess) {
@@ -1081,7 +1127,7 @@ struct PrefillPlanParams {
   __nv_bfloat16* out;
   float* lse;
   long long tok_stride, head_stride;
-  int batch, qb, max_items, total_q, nheads, causal;
+  int batch, qb, max_items, total_q, nheads, causal, head_dim;
 };
 
 // Block 0 writes the item table {request, first q row, valid tokens, diagonal
@@ -1154,11 +1200,11 @@ __global__ void __launch_bounds__(256) prefill_plan_kernel(const PrefillPlanPara
   }
   const int pad_start = min(max(pp.cu[n_active], 0), pp.total_q);
   const long long pad_rows = pp.total_q - pad_start;
-  const long long chunks = pad_rows * pp.nheads * (kHeadDim / 8);
+  const long long chunks = pad_rows * pp.nheads * (pp.head_dim / 8);
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < chunks;
        i += static_cast<long long>(gridDim.x) * blockDim.x) {
-    const int c = static_cast<int>(i % (kHeadDim / 8));
-    const long long rh = i / (kHeadDim / 8);
+    const int c = static_cast<int>(i % (pp.head_dim / 8));
+    const long long rh = i / (pp.head_dim / 8);
     const int hq = static_cast<int>(rh % pp.nheads);
     const long long row = pad_start + rh / pp.nheads;
     *reinterpret_cast<uint4*>(pp.out + row * pp.tok_stride + hq * pp.head_stride + c * 8) =
@@ -1184,6 +1230,7 @@ int launch_prefill_plan(const FwPrefillArgs* a, int qb, int max_items, int* item
   pp.head_stride = head_stride;
   pp.batch = a->batch;
   pp.qb = qb;
+  pp.head_dim = a->head_dim;
   pp.max_items = max_items;
   pp.total_q = a->total_q;
   pp.nheads = a->nheads;
@@ -1222,7 +1269,11 @@ static int plan_splitkv_prefill(const FwPrefillArgs* a, SplitKvPrefillPlan* sp) 
     set_error("nheads / nheads_k = %d exceeds 128 query heads per KV head.", group);
     return FW_ERR_UNSUPPORTED;
   }
-  sp->qb = 128 / group;
+  sp->qb = (a->head_dim > 128 ? 64 : 128) / group;  // query rows per KV head a decode block takes
+  if (sp->qb < 1) {
+    set_error("nheads / nheads_k = %d exceeds 64 query heads per KV head at head_dim %d.", group, a->head_dim);
+    return FW_ERR_UNSUPPORTED;
+  }
   sp->max_items = (a->total_q + sp->qb - 1) / sp->qb + a->batch;
   if (sp->max_items > kMaxItems) {
     set_error("total_q %d makes %d query blocks; the split-KV prefill takes at most %d per call.", a->total_q,
@@ -1252,11 +1303,11 @@ static int plan_splitkv_prefill(const FwPrefillArgs* a, SplitKvPrefillPlan* sp) 
   p.k_descale = a->k_descale;
   p.total_q = a->total_q;
   if (a->token_major) {
-    p.q_tok_stride = static_cast<long long>(a->nheads) * kHeadDim;
-    p.q_head_stride = kHeadDim;
+    p.q_tok_stride = static_cast<long long>(a->nheads) * a->head_dim;
+    p.q_head_stride = a->head_dim;
   } else {
-    p.q_tok_stride = kHeadDim;
-    p.q_head_stride = static_cast<long long>(a->total_q) * kHeadDim;
+    p.q_tok_stride = a->head_dim;
+    p.q_head_stride = static_cast<long long>(a->total_q) * a->head_dim;
   }
   sp->off_items = (sp->decode.bytes + 255) & ~255ull;
   sp->bytes = sp->off_items + static_cast<uint64_t>(sp->max_items) * 8 * sizeof(int);

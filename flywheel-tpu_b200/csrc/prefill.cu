@@ -17,8 +17,8 @@ static int check_prefill_args(const FwPrefillArgs* a) {
     set_error("kv_dtype must be bf16, e4m3 or e5m2; got %d", a->kv_dtype);
     return FW_ERR_BAD_DTYPE;
   }
-  if (a->head_dim != 128) {
-    set_error("head_dim %d is not built; this library serves head_dim 128.", a->head_dim);
+  if (a->head_dim != 128 && a->head_dim != 256) {
+    set_error("head_dim %d is not built; this library serves head_dim 128 and 256.", a->head_dim);
     return FW_ERR_UNSUPPORTED;
   }
   if (a->total_q < 0 || a->batch <= 0) {
@@ -49,7 +49,7 @@ struct RopeParams {
   const int* cu;
   const int* seqused;
   long long tok_stride, head_stride;
-  int batch, total_q, nheads, rotary_len, interleaved, table_bf16;
+  int batch, total_q, nheads, rotary_len, interleaved, table_bf16, head_dim;
 };
 
 __device__ __forceinline__ float table_value(const void* table, long long index, int is_bf16) {
@@ -57,13 +57,14 @@ __device__ __forceinline__ float table_value(const void* table, long long index,
                  : static_cast<const float*>(table)[index];
 }
 
-// One thread per (token, head, pair of 8 elements): 128 / 16 = 8 threads per row.
+// One thread per (token, head, 8 rotation pairs): head_dim / 16 threads per row.
 __global__ void __launch_bounds__(256) rope_q_kernel(const RopeParams p) {
-  const long long total = static_cast<long long>(p.total_q) * p.nheads * 8;
+  const int parts = p.head_dim / 16, half = p.head_dim / 2;
+  const long long total = static_cast<long long>(p.total_q) * p.nheads * parts;
   for (long long idx = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; idx < total;
        idx += static_cast<long long>(gridDim.x) * blockDim.x) {
-    const int part = static_cast<int>(idx & 7);
-    const long long th = idx >> 3;
+    const int part = static_cast<int>(idx % parts);
+    const long long th = idx / parts;
     const int hq = static_cast<int>(th % p.nheads);
     const int tok = static_cast<int>(th / p.nheads);
     const long long base = static_cast<long long>(tok) * p.tok_stride + static_cast<long long>(hq) * p.head_stride;
@@ -76,26 +77,26 @@ __global__ void __launch_bounds__(256) rope_q_kernel(const RopeParams p) {
     int pos = -1;
     if (tok >= p.cu[lo] && tok < p.cu[lo + 1]) pos = p.seqused[lo] - (p.cu[lo + 1] - p.cu[lo]) + (tok - p.cu[lo]);
     const bool rotate = pos >= 0 && pos < p.rotary_len;
-    // This thread's 8 pairs: split halves pair element i with i + 64;
+    // This thread's 8 pairs: split halves pair element i with i + head_dim / 2;
     // interleaved pairs (2i, 2i + 1).
     if (!p.interleaved) {
       const int i0 = part * 8;
       uint4 a = *reinterpret_cast<const uint4*>(p.q + base + i0);
-      uint4 b = *reinterpret_cast<const uint4*>(p.q + base + 64 + i0);
+      uint4 b = *reinterpret_cast<const uint4*>(p.q + base + half + i0);
       if (rotate) {
         __nv_bfloat16* x1 = reinterpret_cast<__nv_bfloat16*>(&a);
         __nv_bfloat16* x2 = reinterpret_cast<__nv_bfloat16*>(&b);
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
-          const float c = table_value(p.cos, static_cast<long long>(pos) * 64 + i0 + i, p.table_bf16);
-          const float s = table_value(p.sin, static_cast<long long>(pos) * 64 + i0 + i, p.table_bf16);
+          const float c = table_value(p.cos, static_cast<long long>(pos) * half + i0 + i, p.table_bf16);
+          const float s = table_value(p.sin, static_cast<long long>(pos) * half + i0 + i, p.table_bf16);
           const float u = __bfloat162float(x1[i]), w = __bfloat162float(x2[i]);
           x1[i] = __float2bfloat16_rn(u * c - w * s);
           x2[i] = __float2bfloat16_rn(u * s + w * c);
         }
       }
       *reinterpret_cast<uint4*>(p.q_out + base + i0) = a;
-      *reinterpret_cast<uint4*>(p.q_out + base + 64 + i0) = b;
+      *reinterpret_cast<uint4*>(p.q_out + base + half + i0) = b;
     } else {
       const int e0 = part * 16;
       uint4 a = *reinterpret_cast<const uint4*>(p.q + base + e0);
@@ -106,8 +107,8 @@ __global__ void __launch_bounds__(256) rope_q_kernel(const RopeParams p) {
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
           __nv_bfloat16* pair = i < 4 ? x + 2 * i : y + 2 * (i - 4);
-          const float c = table_value(p.cos, static_cast<long long>(pos) * 64 + part * 8 + i, p.table_bf16);
-          const float s = table_value(p.sin, static_cast<long long>(pos) * 64 + part * 8 + i, p.table_bf16);
+          const float c = table_value(p.cos, static_cast<long long>(pos) * half + part * 8 + i, p.table_bf16);
+          const float s = table_value(p.sin, static_cast<long long>(pos) * half + part * 8 + i, p.table_bf16);
           const float u = __bfloat162float(pair[0]), w = __bfloat162float(pair[1]);
           pair[0] = __float2bfloat16_rn(u * c - w * s);
           pair[1] = __float2bfloat16_rn(u * s + w * c);
@@ -121,7 +122,7 @@ __global__ void __launch_bounds__(256) rope_q_kernel(const RopeParams p) {
 
 static uint64_t rope_bytes(const FwPrefillArgs* a) {
   if (a->rotary_cos == nullptr) return 0;
-  return (static_cast<uint64_t>(a->total_q) * a->nheads * 128 * 2 + 255) & ~255ull;
+  return (static_cast<uint64_t>(a->total_q) * a->nheads * a->head_dim * 2 + 255) & ~255ull;
 }
 
 // Chunks of at least this many tokens go to the tensor-core kernel; shorter
@@ -178,15 +179,16 @@ extern "C" int fw_prefill_paged(const FwPrefillArgs* a, void* stream_ptr) {
     rp.sin = a->rotary_sin;
     rp.cu = a->cu_seqlens_q;
     rp.seqused = a->seqused_k;
-    rp.tok_stride = a->token_major ? static_cast<long long>(a->nheads) * 128 : 128;
-    rp.head_stride = a->token_major ? 128 : static_cast<long long>(a->total_q) * 128;
+    rp.tok_stride = a->token_major ? static_cast<long long>(a->nheads) * a->head_dim : a->head_dim;
+    rp.head_stride = a->token_major ? a->head_dim : static_cast<long long>(a->total_q) * a->head_dim;
+    rp.head_dim = a->head_dim;
     rp.batch = a->batch;
     rp.total_q = a->total_q;
     rp.nheads = a->nheads;
     rp.rotary_len = a->rotary_len;
     rp.interleaved = a->rotary_interleaved;
     rp.table_bf16 = a->rotary_bf16;
-    const long long threads = static_cast<long long>(a->total_q) * a->nheads * 8;
+    const long long threads = static_cast<long long>(a->total_q) * a->nheads * (a->head_dim / 16);
     const long long want = (threads + 255) / 256, cap = static_cast<long long>(sm_count()) * 32;
     rope_q_kernel<<<static_cast<int>(want < cap ? want : cap), 256, 0, stream>>>(rp);
     cudaError_t err = cudaGetLastError();

@@ -10,6 +10,12 @@ PAGE_SIZE_MULTIPLE = DECODE_TILE_TOKENS
 # in one launch; the reference folds a verify window up to the same bound
 # (decode.py:49-53).
 MAX_FOLDED_QUERY_ROWS = 128
-SUPPORTED_HEAD_DIMS = (128,)
+
+
+def max_folded_query_rows(head_dim: int) -> int:
+    """The bound above at head_dim 128; half of it at 256, where a warp's
+    registers hold twice the output columns."""
+    return MAX_FOLDED_QUERY_ROWS if head_dim <= 128 else MAX_FOLDED_QUERY_ROWS // 2
+SUPPORTED_HEAD_DIMS = (128, 256)
 # Rows one decode launch takes; the host entry slices larger batches.
 MAX_DECODE_BATCH = 2048

@@ -19,7 +19,7 @@ import torch
 from flywheel_tpu.softmax_attention import _arrays, _native
 from flywheel_tpu.softmax_attention.config import (
     MAX_DECODE_BATCH,
-    MAX_FOLDED_QUERY_ROWS,
+    max_folded_query_rows,
     PAGE_SIZE_MULTIPLE,
     SUPPORTED_HEAD_DIMS,
 )
@@ -288,7 +288,7 @@ def flash_attn_with_kvcache(
 
     group = nheads // nheads_k
     is_folded = (is_extend and not is_ragged
-                 and seqlen_q * group <= MAX_FOLDED_QUERY_ROWS)
+                 and seqlen_q * group <= max_folded_query_rows(head_dim))
     lib = _native.library()
     stream = _native.current_stream(device)
     lse = None
