@@ -298,6 +298,17 @@ def bench_long_context(ns, device, rank, world, barrier):
             "per_step": "decode kernel + combine + all-gather + merge, replayed as one CUDA graph"}
 
 
+# The reference's own serving and perf-gate decode shapes (page 128), beside
+# which its TPU tables sit: docs/v7x.md:129-150 and scripts/perf_gate.py:80-107
+# of the reference.  Paged bf16, single-token decode unless q_len says otherwise.
+SECONDARY_SHAPES = {
+    "serve-d256-gqa": dict(batch=128, hq=32, hk=4, d=256, page=128, q_len=1, lens=(15360, 15360)),
+    "serve-d256-mha": dict(batch=32, hq=32, hk=32, d=256, page=128, q_len=1, lens=(15360, 15360)),
+    "gate-decode": dict(batch=64, hq=32, hk=8, d=128, page=128, q_len=1, lens=(6144, 10239)),
+    "gate-verify": dict(batch=32, hq=32, hk=8, d=128, page=128, q_len=4, lens=(6144, 10239)),
+}
+
+
 def bench_config(ns, name, device):
     """Secondary decode configurations (one JSON line each, device-resident):
     c1 = contiguous bf16 GQA decode (batch 8, 32:8 heads, capacity 2048, lengths
@@ -325,6 +336,29 @@ def bench_config(ns, name, device):
             kv_dtype=0, causal=1, window_left=-1, softmax_scale=D ** -0.5, softcap=0.0)
         kv_bytes = workloads.decode_kv_bytes(lens, 1, hk, D, 2)
         keep = (kc, vc, q, k, v, lens_t, out)
+    elif name in SECONDARY_SHAPES:
+        spec = SECONDARY_SHAPES[name]
+        batch, hq, hk, d, page, q_len = (spec[key] for key in ("batch", "hq", "hk", "d", "page", "q_len"))
+        lo, hi = spec["lens"]
+        lens = rng.integers(lo, hi + 1, batch).astype(np.int32)
+        table, pool_pages = workloads.paged_table(rng, lens, q_len, page, slack=0.10)
+        pool = torch.empty((pool_pages, page, 2 * hk, d), dtype=torch.bfloat16, device=device)
+        rows = max(1, (256 << 20) // (page * 2 * hk * d * 2))
+        for first in range(0, pool_pages, rows):
+            pool[first:first + rows].normal_()
+        q = torch.randn((batch, q_len, hq, d), device=device).to(torch.bfloat16)
+        k = torch.randn((batch, q_len, hk, d), device=device).to(torch.bfloat16)
+        v = torch.randn((batch, q_len, hk, d), device=device).to(torch.bfloat16)
+        lens_t, table_t = torch.from_numpy(lens).to(device), torch.from_numpy(table).to(device)
+        out = torch.empty_like(q)
+        args = _native.FwDecodeArgs(
+            q=q.data_ptr(), out=out.data_ptr(), kv_cache=pool.data_ptr(), k_new=k.data_ptr(),
+            v_new=v.data_ptr(), cache_seqlens=lens_t.data_ptr(), block_table=table_t.data_ptr(),
+            num_pages=pool_pages, page_size=page, pages_per_seq=table.shape[1], batch=batch, seqlen_q=q_len,
+            nheads=hq, nheads_k=hk, head_dim=d, kv_dtype=0, causal=1, window_left=-1,
+            softmax_scale=d ** -0.5, softcap=0.0)
+        kv_bytes = workloads.decode_kv_bytes(lens, q_len, hk, d, 2)
+        keep = (pool, q, k, v, lens_t, table_t, out)
     else:
         batch, hq, hk, q_len, window = 128, 64, 8, 4, 4095
         # experiment knobs for profiling sessions; the defaults are the configuration
@@ -497,7 +531,7 @@ def main():
     parser.add_argument("--skip-cpu-baseline", action="store_true")
     parser.add_argument("--skip-e2e", action="store_true")
     parser.add_argument("--skip-prefill", action="store_true")
-    parser.add_argument("--config", choices=["c1", "c3"], default=None,
+    parser.add_argument("--config", choices=["c1", "c3", *SECONDARY_SHAPES], default=None,
                         help="run one secondary decode configuration instead of the headline")
     parser.add_argument("--long-context", action="store_true",
                         help="run the single-request 128K-token decode split over the GPUs")

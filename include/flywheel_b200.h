@@ -59,6 +59,9 @@ extern "C" {
  * Attention of q against a KV cache with the new tokens' K/V appended in the
  * same launch (flash_attn_with_kvcache, decode.py:189-625).
  *
+ * head_dim is 128 or 256 (at 256: at most 64 query rows, seqlen_q * nheads /
+ * nheads_k, per KV head).
+ *
  * Layouts
  *   paged merged (block_table != NULL): kv_cache is one pool
  *     (num_pages, page_size, cache_heads, head_dim) whose token rows hold
