@@ -1121,7 +1121,8 @@ constexpr int kSortBuckets = 2048;
 
 struct PrefillPlanParams {
   const int* cu;
-  const int* seqused;
+  const int* cu_k;     // packed K/V: request r's keys are rows [cu_k[r], cu_k[r + 1]); else NULL
+  const int* seqused;  // paged: request r's key count
   const int* num_active;
   int* items;
   __nv_bfloat16* out;
@@ -1137,6 +1138,7 @@ __global__ void __launch_bounds__(256) prefill_plan_kernel(const PrefillPlanPara
   __shared__ int off[kMaxInlineBatch + 1];
   __shared__ int bucket[kSortBuckets];
   const int n_active = pp.num_active ? min(pp.batch, max(0, *pp.num_active)) : pp.batch;
+  auto used_of = [&](int r) { return pp.cu_k ? max(0, pp.cu_k[r + 1] - pp.cu_k[r]) : pp.seqused[r]; };
   if (blockIdx.x == 0) {
     for (int r = threadIdx.x; r < pp.batch; r += blockDim.x) {
       const int c = r < n_active ? max(0, pp.cu[r + 1] - pp.cu[r]) : 0;
@@ -1161,7 +1163,7 @@ __global__ void __launch_bounds__(256) prefill_plan_kernel(const PrefillPlanPara
     };
     for (int r = threadIdx.x; r < pp.batch; r += blockDim.x) {
       const int blocks = off[r + 1] - off[r];
-      const int c = blocks ? pp.cu[r + 1] - pp.cu[r] : 0, used = blocks ? pp.seqused[r] : 0;
+      const int c = blocks ? pp.cu[r + 1] - pp.cu[r] : 0, used = blocks ? used_of(r) : 0;
       for (int j = 0; j < blocks; ++j)
         if (off[r] + j < pp.max_items) atomicAdd(&bucket[key_of(r, j, c, used)], 1);
     }
@@ -1179,7 +1181,7 @@ __global__ void __launch_bounds__(256) prefill_plan_kernel(const PrefillPlanPara
       const int blocks = off[r + 1] - off[r];
       if (blocks == 0) continue;
       const int c = pp.cu[r + 1] - pp.cu[r];
-      const int used = pp.seqused[r];
+      const int used = used_of(r);
       for (int j = 0; j < blocks; ++j) {
         if (off[r] + j >= pp.max_items) break;
         const int idx = atomicAdd(&bucket[key_of(r, j, c, used)], 1);
@@ -1189,7 +1191,8 @@ __global__ void __launch_bounds__(256) prefill_plan_kernel(const PrefillPlanPara
         it[2] = min(pp.qb, c - j * pp.qb);
         it[3] = used - c + (j + 1) * pp.qb;  // token t of the block sits on diagonal it[3] - qb + t
         it[4] = used;
-        it[5] = it[6] = it[7] = 0;
+        it[5] = pp.cu_k ? pp.cu_k[r] : 0;  // first key row of a packed request
+        it[6] = it[7] = 0;
       }
     }
     for (int idx = n_items + threadIdx.x; idx < pp.max_items; idx += blockDim.x) {
@@ -1221,6 +1224,7 @@ int launch_prefill_plan(const FwPrefillArgs* a, int qb, int max_items, int* item
   }
   PrefillPlanParams pp;
   pp.cu = a->cu_seqlens_q;
+  pp.cu_k = a->block_table == nullptr ? a->cu_seqlens_k : nullptr;
   pp.seqused = a->seqused_k;
   pp.num_active = a->num_active;
   pp.items = items;

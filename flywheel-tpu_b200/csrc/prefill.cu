@@ -46,8 +46,9 @@ struct RopeParams {
   __nv_bfloat16* q_out;
   const void* cos;
   const void* sin;
-  const int* cu;
-  const int* seqused;
+  const int* cu;       // token ownership: request r holds rows [cu[r], cu[r + 1])
+  const int* seqused;  // request r's key count, or NULL: then it is cu_k[r + 1] - cu_k[r]
+  const int* cu_k;
   long long tok_stride, head_stride;
   int batch, total_q, nheads, rotary_len, interleaved, table_bf16, head_dim;
 };
@@ -75,7 +76,10 @@ __global__ void __launch_bounds__(256) rope_q_kernel(const RopeParams p) {
       if (p.cu[mid] <= tok) lo = mid; else hi = mid;
     }
     int pos = -1;
-    if (tok >= p.cu[lo] && tok < p.cu[lo + 1]) pos = p.seqused[lo] - (p.cu[lo + 1] - p.cu[lo]) + (tok - p.cu[lo]);
+    if (tok >= p.cu[lo] && tok < p.cu[lo + 1]) {
+      const int used = p.seqused ? p.seqused[lo] : p.cu_k[lo + 1] - p.cu_k[lo];
+      pos = used - (p.cu[lo + 1] - p.cu[lo]) + (tok - p.cu[lo]);
+    }
     const bool rotate = pos >= 0 && pos < p.rotary_len;
     // This thread's 8 pairs: split halves pair element i with i + head_dim / 2;
     // interleaved pairs (2i, 2i + 1).
@@ -179,6 +183,7 @@ extern "C" int fw_prefill_paged(const FwPrefillArgs* a, void* stream_ptr) {
     rp.sin = a->rotary_sin;
     rp.cu = a->cu_seqlens_q;
     rp.seqused = a->seqused_k;
+    rp.cu_k = nullptr;
     rp.tok_stride = a->token_major ? static_cast<long long>(a->nheads) * a->head_dim : a->head_dim;
     rp.head_stride = a->token_major ? a->head_dim : static_cast<long long>(a->total_q) * a->head_dim;
     rp.head_dim = a->head_dim;
@@ -201,4 +206,114 @@ extern "C" int fw_prefill_paged(const FwPrefillArgs* a, void* stream_ptr) {
   }
   if (use_tensor_core_kernel(&local)) return tcgen05_prefill(&local, stream);
   return splitkv_prefill(&local, stream);
+}
+
+// ---------------------------------------------------------------- packed K/V
+// flash_attn_varlen_func without a block table and flash_attn_func of the
+// reference project (flywheel_tpu/softmax_attention/prefill.py:818-963 and
+// 62-341): the tensor-core kernel with K and V addressed by token row.
+static int check_packed_args(const FwPrefillArgs* a) {
+  int rc = check_prefill_args(a);
+  if (rc != FW_OK) return rc;
+  if (a->block_table != nullptr || a->seqused_k != nullptr || a->num_active != nullptr ||
+      a->k_descale != nullptr || a->v_descale != nullptr) {
+    set_error("block_table, seqused_k, num_active and the descales describe a paged cache; packed K/V takes"
+              " cu_seqlens_k.");
+    return FW_ERR_BAD_SHAPE;
+  }
+  if (a->kv_dtype != FW_DTYPE_BF16) {
+    set_error("packed K/V is bfloat16.");
+    return FW_ERR_BAD_DTYPE;
+  }
+  if (a->v_packed == nullptr || a->cu_seqlens_k == nullptr || a->total_k <= 0) {
+    set_error("v, cu_seqlens_k and a positive total_k are required.");
+    return FW_ERR_BAD_SHAPE;
+  }
+  if (!tcgen05_prefill_supported(a)) {
+    set_error("packed K/V attention is built for head_dim 128 and nheads / nheads_k a power of two up to 16;"
+              " got head_dim %d, nheads %d, nheads_k %d.", a->head_dim, a->nheads, a->nheads_k);
+    return FW_ERR_UNSUPPORTED;
+  }
+  return FW_OK;
+}
+
+static uint64_t packed_rope_k_bytes(const FwPrefillArgs* a) {
+  if (a->rotary_cos == nullptr || !a->rotary_k) return 0;
+  return (static_cast<uint64_t>(a->total_k) * a->nheads_k * a->head_dim * 2 + 255) & ~255ull;
+}
+
+extern "C" uint64_t fw_attention_packed_workspace_bytes(const FwPrefillArgs* a) {
+  if (check_packed_args(a) != FW_OK) return 0;
+  return ((tcgen05_prefill_workspace_bytes(a) + 255) & ~255ull) + rope_bytes(a) + packed_rope_k_bytes(a);
+}
+
+static int launch_rope(const RopeParams& rp, long long rows, cudaStream_t stream) {
+  const long long threads = rows * rp.nheads * (rp.head_dim / 16);
+  const long long want = (threads + 255) / 256, cap = static_cast<long long>(sm_count()) * 32;
+  rope_q_kernel<<<static_cast<int>(want < cap ? want : cap), 256, 0, stream>>>(rp);
+  cudaError_t err = cudaGetLastError();
+  if (err != cudaSuccess) {
+    set_error("rope kernel launch: %s", cudaGetErrorString(err));
+    return FW_ERR_LAUNCH;
+  }
+  return FW_OK;
+}
+
+extern "C" int fw_attention_packed(const FwPrefillArgs* a, void* stream_ptr) {
+  int rc = check_packed_args(a);
+  if (rc != FW_OK) return rc;
+  if (a->total_q == 0) return FW_OK;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
+  FwPrefillArgs local = *a;
+  const uint64_t head = (tcgen05_prefill_workspace_bytes(a) + 255) & ~255ull;
+  if (a->rotary_cos != nullptr) {
+    const uint64_t need = head + rope_bytes(a) + packed_rope_k_bytes(a);
+    if (a->workspace == nullptr || a->workspace_bytes < need || (reinterpret_cast<uintptr_t>(a->workspace) & 255)) {
+      set_error("workspace must be 256-byte aligned and hold %llu bytes; got %llu.",
+                static_cast<unsigned long long>(need), static_cast<unsigned long long>(a->workspace_bytes));
+      return FW_ERR_WORKSPACE;
+    }
+    if (a->q == nullptr || a->kv_cache == nullptr || a->cu_seqlens_q == nullptr) {
+      set_error("q, k and cu_seqlens_q must not be NULL.");
+      return FW_ERR_BAD_SHAPE;
+    }
+    uint8_t* ws = static_cast<uint8_t*>(a->workspace);
+    RopeParams rp;
+    rp.q = static_cast<const __nv_bfloat16*>(a->q);
+    rp.q_out = reinterpret_cast<__nv_bfloat16*>(ws + head);
+    rp.cos = a->rotary_cos;
+    rp.sin = a->rotary_sin;
+    rp.cu = a->cu_seqlens_q;
+    rp.seqused = nullptr;
+    rp.cu_k = a->cu_seqlens_k;
+    rp.tok_stride = a->token_major ? static_cast<long long>(a->nheads) * a->head_dim : a->head_dim;
+    rp.head_stride = a->token_major ? a->head_dim : static_cast<long long>(a->total_q) * a->head_dim;
+    rp.batch = a->batch;
+    rp.total_q = a->total_q;
+    rp.nheads = a->nheads;
+    rp.rotary_len = a->rotary_len;
+    rp.interleaved = a->rotary_interleaved;
+    rp.table_bf16 = a->rotary_bf16;
+    rp.head_dim = a->head_dim;
+    rc = launch_rope(rp, a->total_q, stream);
+    if (rc != FW_OK) return rc;
+    local.q = rp.q_out;
+    if (a->rotary_k) {
+      // K's token t of a request sits at position t: rotate it as a tensor whose
+      // rows are its own keys (length = key count).
+      RopeParams rk = rp;
+      rk.q = static_cast<const __nv_bfloat16*>(a->kv_cache);
+      rk.q_out = reinterpret_cast<__nv_bfloat16*>(ws + head + rope_bytes(a));
+      rk.cu = a->cu_seqlens_k;
+      rk.tok_stride = a->kv_token_major ? static_cast<long long>(a->nheads_k) * a->head_dim : a->head_dim;
+      rk.head_stride = a->kv_token_major ? a->head_dim : static_cast<long long>(a->total_k) * a->head_dim;
+      rk.total_q = a->total_k;
+      rk.nheads = a->nheads_k;
+      rc = launch_rope(rk, a->total_k, stream);
+      if (rc != FW_OK) return rc;
+      local.kv_cache = rk.q_out;
+    }
+    local.workspace_bytes = head;
+  }
+  return tcgen05_prefill(&local, stream);
 }

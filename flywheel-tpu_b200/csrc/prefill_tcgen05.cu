@@ -53,6 +53,8 @@ struct Tc05Params {
   int total_q, nheads, group, tpb, page_size, pages_per_seq;
   int causal, window_left;
   float scale, softcap;
+  int packed;       // K and V are packed tensors addressed by token (no block table)
+  int sink_period;  // head h uses sinks[h % sink_period]; 0 = one sink per head
 };
 
 // ---------------------------------------------------------------- tcgen05 wrappers
@@ -241,7 +243,7 @@ __device__ __forceinline__ uint32_t tmem_s(uint32_t base, int t) { return base +
 
 __global__ void __launch_bounds__(64 + kStreams * 128, 1)
 prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv,
-                       const Tc05Params p) {
+                       const __grid_constant__ CUtensorMap map_v, const Tc05Params p) {
   extern __shared__ __align__(1024) uint8_t smem[];
   Bars* bars = reinterpret_cast<Bars*>(smem + kSmemBar);
   volatile int* abort_flag = &bars->abort_flag;
@@ -253,6 +255,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   const int4 it = *reinterpret_cast<const int4*>(p.items + 8 * item);
   const int req = it.x, q_row0 = it.y, q_valid = it.z, anchor = it.w;
   const int kv_limit = p.items[8 * item + 4];
+  const int kv_start = p.items[8 * item + 5];  // packed K/V: first key row of the request
   const int kv_end = p.causal ? min(anchor, kv_limit) : kv_limit;
   if (q_valid <= 0) return;  // uniform across the CTA: nothing allocated yet
   // Once any CTA has reported a failed wait the launch is void: later CTAs
@@ -295,6 +298,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     if (lane == 0) {
       tma_prefetch_desc(&map_q);
       tma_prefetch_desc(&map_kv);
+      if (p.packed) tma_prefetch_desc(&map_v);
       mbar_arrive_expect_tx(&bars->q_full, n_streams * kBM * 256);
       for (int t = 0; t < n_streams; ++t)
         for (int g = 0; g < p.group; ++g)
@@ -320,6 +324,13 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         int page[2], tok[2];
         for (int sub = 0; sub < subs; ++sub) {
           const int pos = pos0 + sub * 64;
+          if (p.packed) {
+            // rows past the tensor read as zeros; rows of the next request are
+            // masked (K) or zeroed (V) like stale page slots
+            tok[sub] = kv_start + pos;
+            page[sub] = 0;
+            continue;
+          }
           const int page_idx = pos / p.page_size;
           page[sub] = p.block_table[static_cast<long long>(req) * p.pages_per_seq + page_idx];
           if (page[sub] < 0 || page[sub] >= p.num_pages) {
@@ -330,18 +341,22 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         }
         mbar_arrive_expect_tx(&bars->k_full[s], subs * 64 * 256);
         for (int sub = 0; sub < subs; ++sub)
-          for (int half = 0; half < 2; ++half)
-            tma_load_4d(smem + kSmemK + s * 32768 + half * 16384 + sub * 8192, &map_kv, &bars->k_full[s],
-                        half * 64, 2 * h, tok[sub], page[sub]);
+          for (int half = 0; half < 2; ++half) {
+            uint8_t* dst = smem + kSmemK + s * 32768 + half * 16384 + sub * 8192;
+            if (p.packed) tma_load_3d(dst, &map_kv, &bars->k_full[s], half * 64, tok[sub], h);
+            else tma_load_4d(dst, &map_kv, &bars->k_full[s], half * 64, 2 * h, tok[sub], page[sub]);
+          }
         if (!FW_WAIT(18, j, &bars->v_empty[s], (round & 1) ^ 1)) {
           ok = false;
           break;
         }
         mbar_arrive_expect_tx(&bars->v_full[s], subs * 64 * 256);
         for (int sub = 0; sub < subs; ++sub)
-          for (int half = 0; half < 2; ++half)
-            tma_load_4d(smem + kSmemV + s * 32768 + half * 16384 + sub * 8192, &map_kv, &bars->v_full[s],
-                        half * 64, 2 * h + 1, tok[sub], page[sub]);
+          for (int half = 0; half < 2; ++half) {
+            uint8_t* dst = smem + kSmemV + s * 32768 + half * 16384 + sub * 8192;
+            if (p.packed) tma_load_3d(dst, &map_v, &bars->v_full[s], half * 64, tok[sub], h);
+            else tma_load_4d(dst, &map_kv, &bars->v_full[s], half * 64, 2 * h + 1, tok[sub], page[sub]);
+          }
       }
       if (!ok) {
         *abort_flag = 1;
@@ -560,7 +575,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     if (ok) {
       tc_fence_after();
       const int hq = h * p.group + min(g, p.group - 1);
-      const float sink2 = p.sinks ? p.sinks[hq] * kLog2e : -INFINITY;
+      const float sink2 = p.sinks ? p.sinks[p.sink_period > 0 ? hq % p.sink_period : hq] * kLog2e : -INFINITY;
       const float m_all = fmaxf(m_used, sink2);
       float out_scale = 0.f, lse = -INFINITY;
       if (m_all != -INFINITY) {
@@ -619,7 +634,8 @@ bool tcgen05_prefill_supported(const FwPrefillArgs* a) {
   if (a->nheads_k <= 0 || a->nheads % a->nheads_k) return false;
   const int group = a->nheads / a->nheads_k;
   if (!power_of_two(group) || group > 16) return false;  // 128 rows = (128 / group) tokens x group heads
-  if (a->page_size <= 0 || a->page_size % 64) return false;  // a tile is two 64-token boxes
+  const bool packed = a->block_table == nullptr && a->v_packed != nullptr;
+  if (!packed && (a->page_size <= 0 || a->page_size % 64)) return false;  // a tile is two 64-token boxes
   if (a->batch > 2048) return false;
   if (!(a->softmax_scale > 0.f)) return false;  // the row max is taken before scaling
   return true;
@@ -635,8 +651,19 @@ uint64_t tcgen05_prefill_workspace_bytes(const FwPrefillArgs* a) {
 }
 
 int tcgen05_prefill(const FwPrefillArgs* a, cudaStream_t stream) {
-  if (a->q == nullptr || a->out == nullptr || a->kv_cache == nullptr || a->cu_seqlens_q == nullptr ||
-      a->seqused_k == nullptr || a->block_table == nullptr) {
+  const bool packed = a->block_table == nullptr && a->v_packed != nullptr;
+  if (packed) {
+    if (a->q == nullptr || a->out == nullptr || a->kv_cache == nullptr || a->cu_seqlens_q == nullptr ||
+        a->cu_seqlens_k == nullptr || a->total_k <= 0) {
+      set_error("q, out, k, v, cu_seqlens_q and cu_seqlens_k must not be NULL and total_k positive.");
+      return FW_ERR_BAD_SHAPE;
+    }
+    if (reinterpret_cast<uintptr_t>(a->v_packed) & 15) {
+      set_error("v must be 16-byte aligned.");
+      return FW_ERR_BAD_SHAPE;
+    }
+  } else if (a->q == nullptr || a->out == nullptr || a->kv_cache == nullptr || a->cu_seqlens_q == nullptr ||
+             a->seqused_k == nullptr || a->block_table == nullptr) {
     set_error("q, out, kv_cache, cu_seqlens_q, seqused_k and block_table must not be NULL.");
     return FW_ERR_BAD_SHAPE;
   }
@@ -681,13 +708,15 @@ int tcgen05_prefill(const FwPrefillArgs* a, cudaStream_t stream) {
   p.window_left = a->window_left;
   p.scale = a->softmax_scale;
   p.softcap = a->softcap;
+  p.packed = packed;
+  p.sink_period = a->sink_period;
 
   int rc = launch_prefill_plan(a, kStreams * tpb, max_items, const_cast<int*>(p.items), p.tok_stride,
                                p.head_stride, stream);
   if (rc != FW_OK) return rc;
 
   // q viewed as (head_dim, tokens, heads); a box is 64 elements x tpb tokens of one head.
-  CUtensorMap map_q, map_kv;
+  CUtensorMap map_q, map_kv, map_v;
   {
     const uint64_t dims[3] = {128, static_cast<uint64_t>(a->total_q), static_cast<uint64_t>(a->nheads)};
     const uint64_t strides[2] = {static_cast<uint64_t>(p.tok_stride) * 2, static_cast<uint64_t>(p.head_stride) * 2};
@@ -695,7 +724,18 @@ int tcgen05_prefill(const FwPrefillArgs* a, cudaStream_t stream) {
     rc = encode_tensor_map_bf16(&map_q, 3, a->q, dims, strides, box);
     if (rc != FW_OK) return rc;
   }
-  {
+  if (packed) {
+    // K and V viewed as (head_dim, tokens, heads); a box is 64 elements x 64 tokens of one head.
+    const uint64_t dims[3] = {128, static_cast<uint64_t>(a->total_k), static_cast<uint64_t>(a->nheads_k)};
+    const uint64_t tok = a->kv_token_major ? static_cast<uint64_t>(a->nheads_k) * 256 : 256;
+    const uint64_t head = a->kv_token_major ? 256 : static_cast<uint64_t>(a->total_k) * 256;
+    const uint64_t strides[2] = {tok, head};
+    const uint32_t box[3] = {64, 64, 1};
+    rc = encode_tensor_map_bf16(&map_kv, 3, a->kv_cache, dims, strides, box);
+    if (rc != FW_OK) return rc;
+    rc = encode_tensor_map_bf16(&map_v, 3, a->v_packed, dims, strides, box);
+    if (rc != FW_OK) return rc;
+  } else {
     // pool viewed as (head_dim, head planes [k0,v0,k1,v1,...], tokens in page, pages)
     const uint64_t planes = 2ull * a->nheads_k;
     const uint64_t row_bytes = planes * 256;
@@ -704,6 +744,7 @@ int tcgen05_prefill(const FwPrefillArgs* a, cudaStream_t stream) {
     const uint32_t box[4] = {64, 1, 64, 1};
     rc = encode_tensor_map_bf16(&map_kv, 4, a->kv_cache, dims, strides, box);
     if (rc != FW_OK) return rc;
+    map_v = map_kv;
   }
   cudaError_t err = cudaFuncSetAttribute(prefill_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          kSmemBytes);
@@ -712,7 +753,7 @@ int tcgen05_prefill(const FwPrefillArgs* a, cudaStream_t stream) {
     return FW_ERR_LAUNCH;
   }
   dim3 grid(a->nheads_k, max_items);
-  prefill_tcgen05_kernel<<<grid, 64 + kStreams * 128, kSmemBytes, stream>>>(map_q, map_kv, p);
+  prefill_tcgen05_kernel<<<grid, 64 + kStreams * 128, kSmemBytes, stream>>>(map_q, map_kv, map_v, p);
   err = cudaGetLastError();
   if (err != cudaSuccess) {
     set_error("tcgen05 prefill kernel launch: %s", cudaGetErrorString(err));

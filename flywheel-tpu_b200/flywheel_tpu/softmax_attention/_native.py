@@ -79,6 +79,8 @@ class FwPrefillArgs(ctypes.Structure):
         ("softmax_scale", f32), ("softcap", f32), ("token_major", i32),
         ("rotary_cos", c_ptr), ("rotary_sin", c_ptr), ("rotary_len", i32),
         ("rotary_interleaved", i32), ("rotary_bf16", i32),
+        ("v_packed", c_ptr), ("cu_seqlens_k", c_ptr), ("total_k", i32),
+        ("kv_token_major", i32), ("rotary_k", i32), ("sink_period", i32),
     ]
 
 
@@ -100,6 +102,8 @@ EXPORTS = {
     "fw_write_kv_pages": (ctypes.c_int, [ctypes.POINTER(FwWritePagesArgs), c_ptr]),
     "fw_prefill_workspace_bytes": (u64, [ctypes.POINTER(FwPrefillArgs)]),
     "fw_prefill_paged": (ctypes.c_int, [ctypes.POINTER(FwPrefillArgs), c_ptr]),
+    "fw_attention_packed_workspace_bytes": (u64, [ctypes.POINTER(FwPrefillArgs)]),
+    "fw_attention_packed": (ctypes.c_int, [ctypes.POINTER(FwPrefillArgs), c_ptr]),
     "fw_lse_combine": (ctypes.c_int, [ctypes.POINTER(FwCombineArgs), c_ptr]),
     "fw_selftest_wait_timeout": (ctypes.c_int, [c_ptr, ctypes.c_uint32, c_ptr]),
     "fw_read_status": (ctypes.c_int, [c_ptr, c_ptr, ctypes.POINTER(i32)]),

@@ -1,9 +1,9 @@
-"""flash_attn_varlen_func on B200: chunked prefill over the paged merged cache.
+"""flash_attn_varlen_func on B200: chunked prefill over the paged merged cache,
+and packed K/V through the same tensor-core kernel.
 
-Mirrors the block_table branch of flywheel_tpu/softmax_attention/prefill.py
-(flash_attn_varlen_func :664-963, paged_varlen_attn :437-661 of the reference
-project).  The packed-K/V branch and flash_attn_func (dense attention, not the
-paged serving path) are not built: they raise NotImplementedError.
+Mirrors flywheel_tpu/softmax_attention/prefill.py of the reference project
+(flash_attn_varlen_func :664-963, paged_varlen_attn :437-661).  The packed-K/V
+branch and flash_attn_func live in packed.py.
 """
 
 from __future__ import annotations
@@ -26,14 +26,9 @@ from flywheel_tpu.softmax_attention.inputs import (
     sinks_operand,
 )
 from flywheel_tpu.softmax_attention.kv_layout import resolve_merged_kv_heads
+from flywheel_tpu.softmax_attention.packed import flash_attn_func, packed_varlen_attn
 
-
-def flash_attn_func(*args, **kwargs):
-    """Dense attention is outside the paged-KV serving path this build covers."""
-    raise NotImplementedError(
-        "flash_attn_func (dense attention) is not part of the B200 paged-KV"
-        " build; use flash_attn_varlen_func(block_table=...) or"
-        " flash_attn_with_kvcache.")
+__all__ = ["flash_attn_func", "flash_attn_varlen_func", "paged_prefill_device"]
 
 
 def paged_prefill_device(q, kv_cache, cu_seqlens_q, seqused_k, block_table,
@@ -122,7 +117,14 @@ def flash_attn_varlen_func(
     learnable_sink=None,
     guard_replay_unroll=1,
 ):
-    """Packed-sequence attention; here the paged KV cache branch only.
+    """Packed-sequence attention, forward only.
+
+    Packed K/V (no block_table): q (nheads, total_q, 128), k / v (nheads_k,
+    total_k, 128) bf16, or token-major (total, nheads * head_dim) with
+    head_dim=128; cu_seqlens_q / cu_seqlens_k are (num_seqs + 1,) cumulative
+    offsets; causal / window masks are bottom-right aligned per sequence (right
+    bound -1 or 0); rows past cu_seqlens_q[-1] return out = 0, lse = -inf; RoPE
+    rotates K at its own positions and Q from len_k - len_q on.
 
     Paged KV cache (block_table given; read-only): q is head-major (nheads,
     total_q, headdim) bf16, k is one merged (num_pages, page_size, cache_heads,
@@ -152,9 +154,17 @@ def flash_attn_varlen_func(
             raise ValueError(
                 "seqused_k and num_active describe a paged KV cache and need"
                 " block_table; packed K/V takes cu_seqlens_k.")
-        raise NotImplementedError(
-            "packed K/V flash_attn_varlen_func is not part of the B200"
-            " paged-KV build; pass block_table.")
+        if any(arg is not None for arg in (k_descale, v_descale, nheads_k)):
+            raise ValueError(
+                "k_descale, v_descale and nheads_k describe an fp8 paged pool and"
+                " need block_table; packed K/V is bf16.")
+        return packed_varlen_attn(
+            q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k,
+            softmax_scale=softmax_scale, causal=causal, window_size=window_size,
+            softcap=softcap, return_softmax_lse=bool(return_softmax_lse),
+            head_dim=head_dim, token_major=bool(token_major), rotary_cos=rotary_cos,
+            rotary_sin=rotary_sin, rotary_interleaved=rotary_interleaved,
+            rotary_k=rotary_k, learnable_sink=learnable_sink)
     if guard_replay_unroll != 1:
         raise ValueError(
             "guard_replay_unroll applies to packed K/V; a paged KV cache"

@@ -251,10 +251,35 @@ typedef struct FwPrefillArgs {
   int32_t rotary_len;
   int32_t rotary_interleaved;
   int32_t rotary_bf16;
+  /* Packed K/V (fw_attention_packed only; leave zero for fw_prefill_paged):
+   * kv_cache is K and v_packed is V, bf16, (nheads_k, total_k, head_dim) or,
+   * with kv_token_major = 1, (total_k, nheads_k, head_dim).  Request r's keys
+   * are rows [cu_seqlens_k[r], cu_seqlens_k[r + 1]). */
+  const void* v_packed;
+  const int32_t* cu_seqlens_k;   /* (batch + 1,) */
+  int32_t total_k;
+  int32_t kv_token_major;
+  int32_t rotary_k;      /* 1: K is rotated too, token t of a request at position t */
+  int32_t sink_period;   /* 0: sinks has nheads entries; n > 0: head h uses sinks[h % n] */
 } FwPrefillArgs;
 
 uint64_t fw_prefill_workspace_bytes(const FwPrefillArgs* args);
 int fw_prefill_paged(const FwPrefillArgs* args, void* stream);
+
+/*
+ * Forward attention of packed q over packed K/V without a block table: the
+ * non-paged branch of flash_attn_varlen_func (prefill.py:818-963) and, with one
+ * sequence per batch row, flash_attn_func (prefill.py:62-341; its head-major
+ * (batch, nheads, seqlen, head_dim) layout is this call with batch * nheads
+ * heads over a single sequence, sink_period = nheads).  Causal and left-window
+ * masks are bottom-right aligned per sequence; a right window bound other than
+ * "none" or 0 is not built.  bf16, head_dim 128, nheads / nheads_k a power of
+ * two up to 16.  block_table, seqused_k, num_active, descales must be NULL.
+ * Rows past cu_seqlens_q[batch] return out 0, lse -inf.  With rotary tables q
+ * (and K when rotary_k = 1) are rotated into scratch copies first.
+ */
+uint64_t fw_attention_packed_workspace_bytes(const FwPrefillArgs* args);
+int fw_attention_packed(const FwPrefillArgs* args, void* stream);
 
 /*
  * Merge `parts` sink-free partial states over disjoint key sets

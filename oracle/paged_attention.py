@@ -351,6 +351,53 @@ def rotate_packed_q(q, cos, sin, cu_seqlens_q, seqused_k, interleaved=False):
 
 
 # ----------------------------------------------------------------------------
+# Packed (non-paged) K/V: flash_attn_varlen_func with cu_seqlens_k and
+# flash_attn_func.  Semantics of tests/softmax_attention/util.py:181-273 of the
+# reference (attention_ref: f32, bottom-right aligned causal / window masks on
+# each sequence's own lengths, sink as one more logit, rows with no visible key
+# out 0 / lse -inf or the sink), restricted to a right bound of none or 0.
+# That function is jax.numpy code and cannot run here, so these two restate it
+# through attend_rows, which the golden vectors pin.
+# ----------------------------------------------------------------------------
+def packed_varlen_attention(q, k, v, cu_seqlens_q, cu_seqlens_k, *, causal=False,
+                            window_left=None, softcap=0.0, softmax_scale=None,
+                            sinks=None):
+    """q (total_q, heads, d), k / v (total_k, kv_heads, d) token-major.  Returns
+    out (total_q, heads, d) f32 and lse (heads, total_q); rows outside every
+    sequence give out 0, lse -inf."""
+    q32 = np.asarray(q).astype(np.float32)
+    k32, v32 = np.asarray(k).astype(np.float32), np.asarray(v).astype(np.float32)
+    total_q, heads, d = q32.shape
+    cu_q = np.asarray(cu_seqlens_q).astype(np.int64)
+    cu_k = np.asarray(cu_seqlens_k).astype(np.int64)
+    scale = 1.0 / math.sqrt(d) if softmax_scale is None else softmax_scale
+    out = np.zeros((total_q, heads, d), np.float32)
+    lse = np.full((heads, total_q), -np.inf, np.float32)
+    for seq in range(len(cu_q) - 1):
+        qs, qe, ks, ke = int(cu_q[seq]), int(cu_q[seq + 1]), int(cu_k[seq]), int(cu_k[seq + 1])
+        if qe <= qs:
+            continue
+        o, l = attend_rows(q32[qs:qe], k32[ks:ke], v32[ks:ke], total=ke - ks, causal=causal,
+                           window_left=window_left, softcap=softcap, scale=scale, sinks=sinks)
+        out[qs:qe] = o
+        lse[:, qs:qe] = l
+    return out, lse
+
+
+def dense_attention(q, k, v, **kwargs):
+    """q (batch, seqlen_q, heads, d), k / v (batch, seqlen_k, kv_heads, d).
+    Returns out like q (f32) and lse (batch, heads, seqlen_q)."""
+    q, k, v = np.asarray(q), np.asarray(k), np.asarray(v)
+    batch, seqlen_q, heads, d = q.shape
+    seqlen_k = k.shape[1]
+    out, lse = packed_varlen_attention(
+        q.reshape(batch * seqlen_q, heads, d), k.reshape(batch * seqlen_k, -1, d),
+        v.reshape(batch * seqlen_k, -1, d), np.arange(batch + 1) * seqlen_q,
+        np.arange(batch + 1) * seqlen_k, **kwargs)
+    return out.reshape(q.shape), lse.reshape(heads, batch, seqlen_q).transpose(1, 0, 2)
+
+
+# ----------------------------------------------------------------------------
 # LSE merge (patches/tpu-inference.patch:7174-7186)
 # ----------------------------------------------------------------------------
 def merge_states(outs, lses, sinks=None):
