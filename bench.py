@@ -309,6 +309,46 @@ SECONDARY_SHAPES = {
 }
 
 
+# Dense causal prefill shapes for flash_attn_func (the reference's dense-prefill
+# table uses 32:8 heads, head_dim 128; docs/v7x.md:54 of the reference).
+DENSE_SHAPES = {
+    "dense-causal-8k": dict(batch=4, hq=32, hk=8, seqlen=8192),
+    "dense-causal-32k": dict(batch=1, hq=32, hk=8, seqlen=32768),
+}
+
+
+def bench_dense(ns, name, device):
+    """flash_attn_func (head-major, causal) through the public API on device
+    tensors: TFLOP/s = 4 * visible pairs * heads * head_dim / time."""
+    import torch
+    from flywheel_tpu import flash_attn_func
+    spec = DENSE_SHAPES[name]
+    batch, hq, hk, seqlen = (spec[key] for key in ("batch", "hq", "hk", "seqlen"))
+    q = torch.randn((batch, hq, seqlen, D), device=device).to(torch.bfloat16)
+    k = torch.randn((batch, hk, seqlen, D), device=device).to(torch.bfloat16)
+    v = torch.randn((batch, hk, seqlen, D), device=device).to(torch.bfloat16)
+    flops = 4.0 * batch * (seqlen * (seqlen + 1) / 2) * hq * D
+    steps = max(ns.steps, 10)
+    times = []
+    for i in range(ns.warmup + steps):
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        flash_attn_func(q, k, v, causal=True)
+        end.record()
+        torch.cuda.synchronize()
+        if i >= ns.warmup:
+            times.append(start.elapsed_time(end))
+    ms = float(np.median(times))
+    _, tensor_peak, kind = measured_peaks()
+    tflops = flops / (ms * 1e-3) / 1e12
+    return {"metric": "dense_causal_prefill_tflops", "config": {"workload": name, **spec, "head_dim": D,
+            "l2": "inputs exceed L2" if 3 * q.numel() * 2 > (126 << 20) else "inputs fit L2 (compute-bound)"},
+            "value": tflops, "unit": "TFLOP/s", "ms_per_step": ms, "steps": steps,
+            "algorithmic_flops_per_launch": flops,
+            "roofline": {"bound": "tensor", "achieved": tflops, "peak": tensor_peak,
+                         "frac": tflops / tensor_peak if tensor_peak else None, "peak_kind": f"of {kind}"}}
+
+
 def bench_config(ns, name, device):
     """Secondary decode configurations (one JSON line each, device-resident):
     c1 = contiguous bf16 GQA decode (batch 8, 32:8 heads, capacity 2048, lengths
@@ -531,7 +571,7 @@ def main():
     parser.add_argument("--skip-cpu-baseline", action="store_true")
     parser.add_argument("--skip-e2e", action="store_true")
     parser.add_argument("--skip-prefill", action="store_true")
-    parser.add_argument("--config", choices=["c1", "c3", *SECONDARY_SHAPES], default=None,
+    parser.add_argument("--config", choices=["c1", "c3", *SECONDARY_SHAPES, *DENSE_SHAPES], default=None,
                         help="run one secondary decode configuration instead of the headline")
     parser.add_argument("--long-context", action="store_true",
                         help="run the single-request 128K-token decode split over the GPUs")
@@ -563,6 +603,9 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
+    if ns.config in DENSE_SHAPES:
+        print(json.dumps(bench_dense(ns, ns.config, device)))
+        return
     if ns.config:
         print(json.dumps(bench_config(ns, ns.config, device)))
         return
