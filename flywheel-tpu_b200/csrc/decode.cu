@@ -1129,6 +1129,7 @@ struct PrefillPlanParams {
   float* lse;
   long long tok_stride, head_stride;
   int batch, qb, max_items, total_q, nheads, causal, head_dim;
+  int right;  // right reach of the mask for the sort key: 0 causal, > 0 a window, -1 none
 };
 
 // Block 0 writes the item table {request, first q row, valid tokens, diagonal
@@ -1158,7 +1159,7 @@ __global__ void __launch_bounds__(256) prefill_plan_kernel(const PrefillPlanPara
     __syncthreads();
     auto key_of = [&](int r, int j, int c, int used) {
       const int anchor = used - c + (j + 1) * pp.qb;
-      const int kv_end = pp.causal ? min(anchor, used) : used;
+      const int kv_end = pp.right >= 0 ? min(anchor + pp.right, used) : used;
       return kSortBuckets - 1 - min(max(kv_end, 0) >> 6, kSortBuckets - 1);  // long ranges get small keys
     };
     for (int r = threadIdx.x; r < pp.batch; r += blockDim.x) {
@@ -1239,6 +1240,7 @@ int launch_prefill_plan(const FwPrefillArgs* a, int qb, int max_items, int* item
   pp.total_q = a->total_q;
   pp.nheads = a->nheads;
   pp.causal = a->causal != 0;
+  pp.right = a->causal ? 0 : (a->block_table == nullptr && a->window_right > 0 ? a->window_right : -1);
   prefill_plan_kernel<<<min(sm_count(), 64), 256, 0, stream>>>(pp);
   cudaError_t err = cudaGetLastError();
   if (err != cudaSuccess) {

@@ -51,7 +51,7 @@ struct Tc05Params {
   long long tok_stride, head_stride;  // elements, shared by q and out
   long long num_pages;
   int total_q, nheads, group, tpb, page_size, pages_per_seq;
-  int causal, window_left;
+  int right, window_left;  // keys up to `right` past a row's diagonal are visible (0 = causal); -1 = no bound
   float scale, softcap;
   int packed;       // K and V are packed tensors addressed by token (no block table)
   int sink_period;  // head h uses sinks[h % sink_period]; 0 = one sink per head
@@ -188,9 +188,9 @@ __device__ __forceinline__ uint32_t max_bf16x2(uint32_t a, uint32_t b) {
 // max of what is left in `sr` (raw scores without a softcap).
 template <bool kSoftcap, bool kMask>
 __device__ __forceinline__ float transform_row(uint32_t (&sr)[2][32], float c1, float c2, int pos0, int kv_end,
-                                               int diag, int causal, int window_left) {
+                                               int diag, int right, int window_left) {
   float mx0 = -INFINITY, mx1 = -INFINITY;
-  const int hi = causal ? min(kv_end - 1, diag) : kv_end - 1;        // last visible key
+  const int hi = right >= 0 ? min(kv_end - 1, diag + right) : kv_end - 1;  // last visible key
   const int lo = window_left >= 0 ? diag - window_left : INT_MIN;    // first visible key
 #pragma unroll
   for (int c = 0; c < 2; ++c)
@@ -256,7 +256,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   const int req = it.x, q_row0 = it.y, q_valid = it.z, anchor = it.w;
   const int kv_limit = p.items[8 * item + 4];
   const int kv_start = p.items[8 * item + 5];  // packed K/V: first key row of the request
-  const int kv_end = p.causal ? min(anchor, kv_limit) : kv_limit;
+  const int kv_end = p.right >= 0 ? min(anchor + p.right, kv_limit) : kv_limit;  // the item's last row sits on diagonal anchor - 1
   if (q_valid <= 0) return;  // uniform across the CTA: nothing allocated yet
   // Once any CTA has reported a failed wait the launch is void: later CTAs
   // leave at once instead of each running into its own time limit.
@@ -449,7 +449,9 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         break;
       }
       tc_fence_after();
-      const bool need_mask = pos0 + kBN > min(diag_lo, kv_end) ||
+      // keys every row of the stream sees without a right-side mask
+      const int clear_end = p.right >= 0 ? min(diag_lo + p.right + 1, kv_end) : kv_end;
+      const bool need_mask = pos0 + kBN > clear_end ||
                              (p.window_left >= 0 && pos0 < diag_hi - p.window_left);
       // One pass per 64-key half: load S, softcap / mask (warp-uniform code
       // variants), P = 2^(s * mul - base) against the CURRENT exponent base, and
@@ -474,10 +476,10 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           tmem_wait_ld();
           const int hpos = pos0 + half * 64;
           if (p.softcap > 0.f) {
-            if (need_mask) transform_row<true, true>(sr, c1, c2, hpos, kv_end, diag, p.causal, p.window_left);
-            else transform_row<true, false>(sr, c1, c2, hpos, kv_end, diag, p.causal, p.window_left);
+            if (need_mask) transform_row<true, true>(sr, c1, c2, hpos, kv_end, diag, p.right, p.window_left);
+            else transform_row<true, false>(sr, c1, c2, hpos, kv_end, diag, p.right, p.window_left);
           } else if (need_mask) {
-            transform_row<false, true>(sr, c1, c2, hpos, kv_end, diag, p.causal, p.window_left);
+            transform_row<false, true>(sr, c1, c2, hpos, kv_end, diag, p.right, p.window_left);
           }
 #pragma unroll
           for (int c = 0; c < 2; ++c)
@@ -704,7 +706,7 @@ int tcgen05_prefill(const FwPrefillArgs* a, cudaStream_t stream) {
   p.tpb = tpb;
   p.page_size = a->page_size;
   p.pages_per_seq = a->pages_per_seq;
-  p.causal = a->causal != 0;
+  p.right = a->causal ? 0 : (packed && a->window_right > 0 ? a->window_right : -1);
   p.window_left = a->window_left;
   p.scale = a->softmax_scale;
   p.softcap = a->softcap;

@@ -5,10 +5,9 @@ Mirrors flywheel_tpu/softmax_attention/prefill.py:62-341 (flash_attn_func) and
 :818-963 (packed flash_attn_varlen_func) of the reference project, forward
 only.  Both run the tcgen05 prefill kernel with K and V addressed by token row
 (fw_attention_packed).  Built: bfloat16, head_dim 128, nheads / nheads_k a
-power of two up to 16, causal / full / left-window masks (right bound -1 or
-0), softcap, sinks, lse, fused RoPE on Q and K.  Not built (raise
-NotImplementedError): other head dims, head_dim_v != head_dim, a positive
-right window bound, heads_outer_fold, attention_chunk.
+power of two up to 16, causal / full / (left, right) window masks, softcap,
+sinks, lse, fused RoPE on Q and K.  Not built (raise NotImplementedError):
+other head dims, head_dim_v != head_dim, heads_outer_fold, attention_chunk.
 """
 
 from __future__ import annotations
@@ -131,7 +130,7 @@ def rotary_operand(rotary_cos, rotary_sin, rotary_interleaved, rotary_k, head_di
 
 def packed_attention_device(q, k, v, cu_seqlens_q, cu_seqlens_k, *, nheads, nheads_k, total_q,
                             total_k, token_major, max_seqlen_q, softmax_scale, causal, window_left,
-                            softcap, return_lse, sinks, sink_period=0, rotary=None):
+                            softcap, return_lse, sinks, sink_period=0, rotary=None, window_right=0):
     """Launches fw_attention_packed on contiguous CUDA tensors.  q is (nheads,
     total_q, 128) or, token-major, (total_q, nheads, 128); k / v likewise with
     nheads_k and total_k.  Returns (out shaped like q, lse (nheads, total_q) or
@@ -155,7 +154,7 @@ def packed_attention_device(q, k, v, cu_seqlens_q, cu_seqlens_k, *, nheads, nhea
         head_dim=PACKED_HEAD_DIM, kv_dtype=_native.DTYPE_CODE["bfloat16"], causal=int(bool(causal)),
         window_left=-1 if window_left is None else int(window_left), softmax_scale=float(softmax_scale),
         softcap=float(softcap), token_major=int(bool(token_major)), kv_token_major=int(bool(token_major)),
-        sink_period=int(sink_period))
+        sink_period=int(sink_period), window_right=int(window_right))
     if rotary is not None:
         cos, sin, interleaved, rotate_k = rotary
         args.rotary_cos, args.rotary_sin = cos.data_ptr(), sin.data_ptr()
@@ -176,14 +175,9 @@ def packed_attention_device(q, k, v, cu_seqlens_q, cu_seqlens_k, *, nheads, nhea
 
 
 def packed_window(window_size, causal):
-    """(left or None, causal flag) for the kernel; a positive right bound is not
-    built."""
+    """(left or None, causal flag, positive right reach or 0) for the kernel."""
     left, right = resolve_window(window_size, bool(causal))
-    if right not in (None, 0):
-        raise NotImplementedError(
-            "a window right bound other than -1 (unbounded) or 0 (causal) is not built;"
-            f" got window_size={tuple(window_size)}.")
-    return left, right == 0
+    return left, right == 0, (right if right else 0)
 
 
 def flash_attn_func(
@@ -218,7 +212,8 @@ def flash_attn_func(
     heads fused into the last axis, (batch, seqlen, nheads * head_dim), with
     head_dim=128.  All bfloat16; nheads / nheads_k a power of two up to 16.
     causal is bottom-right aligned: query i attends key j iff j <= i + seqlen_k -
-    seqlen_q; window_size=(left, -1 or 0) adds a left reach.  Rows with no
+    seqlen_q; window_size=(left, right) bounds the reach either side of that
+    diagonal.  Rows with no
     reachable key return out = 0 and lse = -inf (or the sink).
     return_softmax_lse adds lse (batch, nheads, seqlen_q) float32, natural log.
     softcap > 0 applies tanh(scale * q k^T / softcap) * softcap.  rotary_cos /
@@ -243,7 +238,7 @@ def flash_attn_func(
     batch = q.shape[0]
     seq_axis = 1 if token_major else 2
     seqlen_q, seqlen_k = q.shape[seq_axis], k.shape[seq_axis]
-    left, is_causal = packed_window(window_size, causal)
+    left, is_causal, right = packed_window(window_size, causal)
     device = _arrays.pick_device(q, k)
     rotary = rotary_operand(rotary_cos, rotary_sin, rotary_interleaved, rotary_k, head_dim_qk,
                             seqlen_k, device)
@@ -262,7 +257,7 @@ def flash_attn_func(
             v_dev.view(batch * seqlen_k, nheads_k, head_dim_qk), cu_q, cu_k, nheads=nheads, nheads_k=nheads_k,
             total_q=batch * seqlen_q, total_k=batch * seqlen_k, token_major=True, max_seqlen_q=max(seqlen_q, 1),
             softmax_scale=scale, causal=is_causal, window_left=left, softcap=softcap,
-            return_lse=return_softmax_lse, sinks=sinks, rotary=rotary)
+            return_lse=return_softmax_lse, sinks=sinks, rotary=rotary, window_right=right)
         out = out.view(q_dev.shape)
         if lse is not None:
             lse = lse.view(nheads, batch, seqlen_q).transpose(0, 1).contiguous()
@@ -275,7 +270,8 @@ def flash_attn_func(
             v_dev.view(batch * nheads_k, seqlen_k, head_dim_qk), cu_q, cu_k, nheads=batch * nheads,
             nheads_k=batch * nheads_k, total_q=seqlen_q, total_k=seqlen_k, token_major=False,
             max_seqlen_q=max(seqlen_q, 1), softmax_scale=scale, causal=is_causal, window_left=left,
-            softcap=softcap, return_lse=return_softmax_lse, sinks=sinks, sink_period=nheads, rotary=rotary)
+            softcap=softcap, return_lse=return_softmax_lse, sinks=sinks, sink_period=nheads, rotary=rotary,
+            window_right=right)
         out = out.view(q_dev.shape)
         if lse is not None:
             lse = lse.view(batch, nheads, seqlen_q)
@@ -309,7 +305,7 @@ def packed_varlen_attn(q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_se
                 " static bucket bound, not a traced value.")
         if bound <= 0:
             raise ValueError(f"{arg_name} must be positive; got {bound}.")
-    left, is_causal = packed_window(window_size, causal)
+    left, is_causal, right = packed_window(window_size, causal)
     device = _arrays.pick_device(q, k)
     rotary = rotary_operand(rotary_cos, rotary_sin, rotary_interleaved, rotary_k, head_dim_qk,
                             max_seqlen_k, device)
@@ -324,7 +320,7 @@ def packed_varlen_attn(q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_se
         _arrays.to_device(cu_seqlens_k, device, dtype="int32").contiguous(), nheads=nheads,
         nheads_k=nheads_k, total_q=total_q, total_k=total_k, token_major=token_major,
         max_seqlen_q=max_seqlen_q, softmax_scale=scale, causal=is_causal, window_left=left,
-        softcap=softcap, return_lse=return_softmax_lse, sinks=sinks, rotary=rotary)
+        softcap=softcap, return_lse=return_softmax_lse, sinks=sinks, rotary=rotary, window_right=right)
     if token_major:
         out = out.view(total_q, nheads * head_dim_qk)
     if return_softmax_lse:

@@ -261,6 +261,7 @@ typedef struct FwPrefillArgs {
   int32_t kv_token_major;
   int32_t rotary_k;      /* 1: K is rotated too, token t of a request at position t */
   int32_t sink_period;   /* 0: sinks has nheads entries; n > 0: head h uses sinks[h % n] */
+  int32_t window_right;  /* > 0 with causal = 0: keys up to this far past a row's diagonal are visible */
 } FwPrefillArgs;
 
 uint64_t fw_prefill_workspace_bytes(const FwPrefillArgs* args);
@@ -272,8 +273,8 @@ int fw_prefill_paged(const FwPrefillArgs* args, void* stream);
  * sequence per batch row, flash_attn_func (prefill.py:62-341; its head-major
  * (batch, nheads, seqlen, head_dim) layout is this call with batch * nheads
  * heads over a single sequence, sink_period = nheads).  Causal and left-window
- * masks are bottom-right aligned per sequence; a right window bound other than
- * "none" or 0 is not built.  bf16, head_dim 128, nheads / nheads_k a power of
+ * masks are bottom-right aligned per sequence (causal = 1 is a right bound of
+ * 0, window_right a positive one).  bf16, head_dim 128, nheads / nheads_k a power of
  * two up to 16.  block_table, seqused_k, num_active, descales must be NULL.
  * Rows past cu_seqlens_q[batch] return out 0, lse -inf.  With rotary tables q
  * (and K when rotary_k = 1) are rotated into scratch copies first.

@@ -141,7 +141,7 @@ def append_contiguous(k_cache, v_cache, k, v, cache_seqlens, cache_batch_idx,
 # Attention core (test_paged.py:98-206)
 # ----------------------------------------------------------------------------
 def attend_rows(q, keys, values, *, total, causal, window_left, softcap,
-                scale, sinks, row_chunk=256):
+                scale, sinks, row_chunk=256, window_right=None):
     """f32 softmax attention of (q_len, heads, d) query rows against one
     request's (total, kv_heads, d) keys/values.  Row r sits on the bottom-right
     diagonal ``total - q_len + r``; causal hides keys past it, window_left
@@ -174,6 +174,8 @@ def attend_rows(q, keys, values, *, total, causal, window_left, softcap,
             visible = np.ones((len(rows), total), bool)
         if window_left is not None:
             visible = visible & (positions[None] >= diagonal - window_left)
+        if window_right is not None and not causal:
+            visible = visible & (positions[None] <= diagonal + window_right)
         seen = visible.any(axis=-1)                                # (rows,)
         scores = np.where(visible[None, :, None, :], scores, -np.inf)
         anchor = np.where(
@@ -355,13 +357,13 @@ def rotate_packed_q(q, cos, sin, cu_seqlens_q, seqused_k, interleaved=False):
 # flash_attn_func.  Semantics of tests/softmax_attention/util.py:181-273 of the
 # reference (attention_ref: f32, bottom-right aligned causal / window masks on
 # each sequence's own lengths, sink as one more logit, rows with no visible key
-# out 0 / lse -inf or the sink), restricted to a right bound of none or 0.
+# out 0 / lse -inf or the sink).
 # That function is jax.numpy code and cannot run here, so these two restate it
 # through attend_rows, which the golden vectors pin.
 # ----------------------------------------------------------------------------
 def packed_varlen_attention(q, k, v, cu_seqlens_q, cu_seqlens_k, *, causal=False,
                             window_left=None, softcap=0.0, softmax_scale=None,
-                            sinks=None):
+                            sinks=None, window_right=None):
     """q (total_q, heads, d), k / v (total_k, kv_heads, d) token-major.  Returns
     out (total_q, heads, d) f32 and lse (heads, total_q); rows outside every
     sequence give out 0, lse -inf."""
@@ -378,7 +380,8 @@ def packed_varlen_attention(q, k, v, cu_seqlens_q, cu_seqlens_k, *, causal=False
         if qe <= qs:
             continue
         o, l = attend_rows(q32[qs:qe], k32[ks:ke], v32[ks:ke], total=ke - ks, causal=causal,
-                           window_left=window_left, softcap=softcap, scale=scale, sinks=sinks)
+                           window_left=window_left, softcap=softcap, scale=scale, sinks=sinks,
+                           window_right=window_right)
         out[qs:qe] = o
         lse[:, qs:qe] = l
     return out, lse

@@ -145,12 +145,23 @@ def test_dense_rotary_matches_varlen_rule():
     np.testing.assert_allclose(out.astype(np.float32).transpose(0, 2, 1, 3).reshape(-1, hq, D), want, **OUT_TOL)
 
 
+@pytest.mark.parametrize("window", [(-1, 3), (50, 20), (0, 0), (7, 300), (200, 1)])
+@pytest.mark.parametrize("sq,sk", [(160, 160), (90, 400), (300, 130)])
+def test_two_sided_window(window, sq, sk):
+    from flywheel_tpu import flash_attn_func
+    rng = np.random.default_rng(sq + window[1])
+    q, k, v = draw(rng, (2, 8, sq, D)), draw(rng, (2, 2, sk, D)), draw(rng, (2, 2, sk, D))
+    out, lse = flash_attn_func(q, k, v, window_size=window, return_softmax_lse=True)
+    want, want_lse = oracle.dense_attention(
+        q.transpose(0, 2, 1, 3), k.transpose(0, 2, 1, 3), v.transpose(0, 2, 1, 3),
+        window_left=None if window[0] < 0 else window[0], window_right=window[1])
+    check(out.transpose(0, 2, 1, 3), lse, want, want_lse)
+
+
 def test_rejections():
     from flywheel_tpu import flash_attn_func, flash_attn_varlen_func
     rng = np.random.default_rng(0)
     q, k = draw(rng, (1, 4, 8, D)), draw(rng, (1, 4, 8, D))
-    with pytest.raises(NotImplementedError, match="right bound"):
-        flash_attn_func(q, k, k, window_size=(-1, 3))
     with pytest.raises(NotImplementedError, match="head_dim"):
         flash_attn_func(q[..., :64], k[..., :64], k[..., :64])
     with pytest.raises(NotImplementedError, match="power of two"):
