@@ -230,7 +230,7 @@ static int check_packed_args(const FwPrefillArgs* a) {
     return FW_ERR_BAD_SHAPE;
   }
   if (!tcgen05_prefill_supported(a)) {
-    set_error("packed K/V attention is built for head_dim 128 and nheads / nheads_k a power of two up to 16;"
+    set_error("packed K/V attention is built for head_dim 128 and nheads / nheads_k up to 128;"
               " got head_dim %d, nheads %d, nheads_k %d.", a->head_dim, a->nheads, a->nheads_k);
     return FW_ERR_UNSUPPORTED;
   }

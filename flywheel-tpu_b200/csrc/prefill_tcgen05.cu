@@ -299,7 +299,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       tma_prefetch_desc(&map_q);
       tma_prefetch_desc(&map_kv);
       if (p.packed) tma_prefetch_desc(&map_v);
-      mbar_arrive_expect_tx(&bars->q_full, n_streams * kBM * 256);
+      mbar_arrive_expect_tx(&bars->q_full, n_streams * p.group * p.tpb * 256);
       for (int t = 0; t < n_streams; ++t)
         for (int g = 0; g < p.group; ++g)
           for (int half = 0; half < 2; ++half)
@@ -629,13 +629,13 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 }
 
 // ---------------------------------------------------------------- host
-static bool power_of_two(int x) { return x > 0 && (x & (x - 1)) == 0; }
-
 bool tcgen05_prefill_supported(const FwPrefillArgs* a) {
   if (a->kv_dtype != FW_DTYPE_BF16 || a->head_dim != 128) return false;
   if (a->nheads_k <= 0 || a->nheads % a->nheads_k) return false;
   const int group = a->nheads / a->nheads_k;
-  if (!power_of_two(group) || group > 16) return false;  // 128 rows = (128 / group) tokens x group heads
+  // 128 rows hold (128 / group) tokens x group heads; a group that does not
+  // divide 128 leaves the last rows idle.
+  if (group > kBM) return false;
   const bool packed = a->block_table == nullptr && a->v_packed != nullptr;
   if (!packed && (a->page_size <= 0 || a->page_size % 64)) return false;  // a tile is two 64-token boxes
   if (a->batch > 2048) return false;

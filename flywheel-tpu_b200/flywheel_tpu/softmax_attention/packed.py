@@ -4,8 +4,7 @@ cu_seqlens_k branch of flash_attn_varlen_func.
 Mirrors flywheel_tpu/softmax_attention/prefill.py:62-341 (flash_attn_func) and
 :818-963 (packed flash_attn_varlen_func) of the reference project, forward
 only.  Both run the tcgen05 prefill kernel with K and V addressed by token row
-(fw_attention_packed).  Built: bfloat16, head_dim 128, nheads / nheads_k a
-power of two up to 16, causal / full / (left, right) window masks, softcap,
+(fw_attention_packed).  Built: bfloat16, head_dim 128, nheads / nheads_k up to 128, causal / full / (left, right) window masks, softcap,
 sinks, lse, fused RoPE on Q and K.  Not built (raise NotImplementedError):
 other head dims, head_dim_v != head_dim, heads_outer_fold, attention_chunk.
 """
@@ -25,7 +24,7 @@ from flywheel_tpu.softmax_attention.inputs import (
 )
 
 PACKED_HEAD_DIM = 128
-MAX_PACKED_GROUP = 16
+MAX_PACKED_GROUP = 128
 
 
 def parse_qkv(q, k, v, head_dim, token_major, expected_rank, layout):
@@ -92,10 +91,10 @@ def parse_qkv(q, k, v, head_dim, token_major, expected_rank, layout):
         raise NotImplementedError(
             f"packed K/V attention is built for head_dim {PACKED_HEAD_DIM}; got {head_dim_qk}.")
     group = nheads // nheads_k
-    if group > MAX_PACKED_GROUP or group & (group - 1):
+    if group > MAX_PACKED_GROUP:
         raise NotImplementedError(
-            "packed K/V attention is built for nheads / nheads_k a power of two up to"
-            f" {MAX_PACKED_GROUP}; got {nheads} / {nheads_k}.")
+            f"packed K/V attention is built for nheads / nheads_k up to {MAX_PACKED_GROUP};"
+            f" got {nheads} / {nheads_k}.")
     return nheads, nheads_k, head_dim_qk
 
 
@@ -210,7 +209,7 @@ def flash_attn_func(
     Head-major (default): q (batch, nheads, seqlen_q, 128), k / v (batch,
     nheads_k, seqlen_k, 128), out like q.  Token-major (token_major=True): the
     heads fused into the last axis, (batch, seqlen, nheads * head_dim), with
-    head_dim=128.  All bfloat16; nheads / nheads_k a power of two up to 16.
+    head_dim=128.  All bfloat16; nheads / nheads_k up to 128.
     causal is bottom-right aligned: query i attends key j iff j <= i + seqlen_k -
     seqlen_q; window_size=(left, right) bounds the reach either side of that
     diagonal.  Rows with no

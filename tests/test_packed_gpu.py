@@ -28,7 +28,7 @@ def check(out, lse, want, want_lse):
     np.testing.assert_allclose(lse[finite], want_lse[finite], **LSE_TOL)
 
 
-@pytest.mark.parametrize("hq,hk", [(4, 4), (8, 2), (8, 1), (16, 1)])
+@pytest.mark.parametrize("hq,hk", [(4, 4), (8, 2), (8, 1), (16, 1), (6, 2), (6, 1), (10, 2), (14, 2), (12, 1), (32, 1), (64, 1), (128, 1)])
 @pytest.mark.parametrize("sq,sk", [(1, 239), (113, 203), (128, 128), (256, 512), (300, 77), (1, 1)])
 @pytest.mark.parametrize("causal,left", [(False, None), (True, None), (True, 64), (False, 100)])
 def test_flash_attn_func_head_major(hq, hk, sq, sk, causal, left):
@@ -164,8 +164,8 @@ def test_rejections():
     q, k = draw(rng, (1, 4, 8, D)), draw(rng, (1, 4, 8, D))
     with pytest.raises(NotImplementedError, match="head_dim"):
         flash_attn_func(q[..., :64], k[..., :64], k[..., :64])
-    with pytest.raises(NotImplementedError, match="power of two"):
-        flash_attn_func(draw(rng, (1, 6, 8, D)), k[:, :2], k[:, :2])
+    with pytest.raises(NotImplementedError, match="up to 128"):
+        flash_attn_func(draw(rng, (1, 130, 8, D)), k[:, :1], k[:, :1])
     with pytest.raises(ValueError, match="head_dim="):
         flash_attn_func(q.reshape(1, 8, 4 * D), k.reshape(1, 8, 4 * D), k.reshape(1, 8, 4 * D), token_major=True)
     with pytest.raises(ValueError, match="need block_table"):
