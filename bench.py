@@ -254,7 +254,9 @@ def bench_long_context(ns, device, rank, world, barrier):
     """Single-request long-context decode: one 128K-token paged bf16 cache (page
     64, random block table), 64 q heads, 8 kv heads, 256 decode steps with the
     fused append, the pages split evenly over the ranks; per step every rank
-    decodes its pages, the (o, lse) states are all-gathered (NCCL) and merged."""
+    decodes its pages, then the (o, lse) states are exchanged and merged:
+    FLYWHEEL_EXCHANGE=p2p (default; peer stores over NVLink + flags, fused with
+    the merge) or nccl (all-gather + merge)."""
     import torch
     import torch.distributed as dist
     from flywheel_tpu.softmax_attention import distributed as d
@@ -272,7 +274,9 @@ def bench_long_context(ns, device, rank, world, barrier):
     if world == 1 and not dist.is_initialized():
         dist.init_process_group("nccl", init_method="tcp://127.0.0.1:29555", rank=0, world_size=1,
                                 device_id=device)
-    decoder = d.ShardedDecoder(pool=pool, table=table, total_pages=total_pages, nheads=HQ, nheads_k=HK)
+    exchange = os.environ.get("FLYWHEEL_EXCHANGE", "p2p")
+    decoder = d.ShardedDecoder(pool=pool, table=table, total_pages=total_pages, nheads=HQ, nheads_k=HK,
+                               exchange=exchange)
     q = torch.randn((1, 1, HQ, D), device=device).to(torch.bfloat16)
     k = torch.randn((1, 1, HK, D), device=device).to(torch.bfloat16)
     v = torch.randn((1, 1, HK, D), device=device).to(torch.bfloat16)
@@ -290,12 +294,22 @@ def bench_long_context(ns, device, rank, world, barrier):
     if world > 1:
         dist.all_reduce(ms, op=dist.ReduceOp.MAX)
     kv_bytes = sum((context + step + 1) * 2 * HK * D * 2 for step in range(steps)) / steps
+    if _native_status(decoder, device) != 0:
+        raise RuntimeError("a kernel of the long-context step reported a device status")
+    decoder.close()
+    how = ("peer stores of (o, lse) over NVLink + flags, fused with the merge" if exchange == "p2p"
+           else "NCCL all-gather of (o, lse) + merge")
     return {"metric": "long_context_decode_kv_read_bandwidth", "value": kv_bytes / (float(ms) * 1e-3) / 1e9,
             "unit": "GB/s", "ms_per_step": float(ms), "n_gpus": world, "steps": steps, "scaling": "strong",
             "config": {"workload": "1 request, 128K-token paged bf16 cache, page 64, 64 q heads, 8 kv heads, "
                                    "256 decode steps with fused append, pages split evenly over the GPUs, "
-                                   "NCCL all-gather of (o, lse) + merge per step"},
-            "per_step": "decode kernel + combine + all-gather + merge, replayed as one CUDA graph"}
+                                   + how + " per step", "exchange": exchange},
+            "per_step": "decode kernel + combine + exchange + merge, replayed as one CUDA graph"}
+
+
+def _native_status(decoder, device):
+    from flywheel_tpu.softmax_attention import _native
+    return _native.read_status(decoder.scratch, device)
 
 
 # The reference's own serving and perf-gate decode shapes (page 128), beside

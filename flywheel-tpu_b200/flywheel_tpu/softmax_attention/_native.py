@@ -95,6 +95,15 @@ class FwCombineArgs(ctypes.Structure):
     ]
 
 
+class FwExchangeArgs(ctypes.Structure):
+    _fields_ = [
+        ("peer_buffers", c_ptr), ("state_out", c_ptr), ("state_lse", c_ptr),
+        ("sinks", c_ptr), ("out", c_ptr), ("lse", c_ptr), ("status", c_ptr),
+        ("world", i32), ("rank", i32), ("rows", i32), ("nheads", i32),
+        ("head_dim", i32), ("lse_head_stride", i32), ("lse_token_stride", i32),
+    ]
+
+
 EXPORTS = {
     "fw_decode_workspace_bytes": (u64, [ctypes.POINTER(FwDecodeArgs)]),
     "fw_decode_kvcache": (ctypes.c_int, [ctypes.POINTER(FwDecodeArgs), c_ptr]),
@@ -106,6 +115,12 @@ EXPORTS = {
     "fw_attention_packed_workspace_bytes": (u64, [ctypes.POINTER(FwPrefillArgs)]),
     "fw_attention_packed": (ctypes.c_int, [ctypes.POINTER(FwPrefillArgs), c_ptr]),
     "fw_lse_combine": (ctypes.c_int, [ctypes.POINTER(FwCombineArgs), c_ptr]),
+    "fw_exchange_buffer_bytes": (u64, [i32, i32, i32]),
+    "fw_peer_alloc": (ctypes.c_int, [u64, ctypes.POINTER(c_ptr), c_ptr]),
+    "fw_peer_open": (ctypes.c_int, [c_ptr, ctypes.POINTER(c_ptr)]),
+    "fw_peer_close": (ctypes.c_int, [c_ptr]),
+    "fw_peer_free": (ctypes.c_int, [c_ptr]),
+    "fw_state_exchange_merge": (ctypes.c_int, [ctypes.POINTER(FwExchangeArgs), c_ptr]),
     "fw_selftest_wait_timeout": (ctypes.c_int, [c_ptr, ctypes.c_uint32, c_ptr]),
     "fw_read_status": (ctypes.c_int, [c_ptr, c_ptr, ctypes.POINTER(i32)]),
     "fw_last_error": (ctypes.c_char_p, []),

@@ -4,10 +4,14 @@ The reference library is single-device; its serving patch merges per-device
 attention states with `_merge_states` (patches/tpu-inference.patch:7174-7186 of
 the reference project).  Here one process per GPU holds a contiguous range of
 the request's logical pages in its own pool; every decode step each rank runs
-the split-KV decode kernel over its own pages in partial-state mode, the
-sink-free `(o, lse)` states are all-gathered with NCCL (33 KB per rank for 64
-heads), and every rank merges them with `fw_lse_combine`.  The rank that owns
-the page holding position `cache_len` appends the new token.
+the split-KV decode kernel over its own pages in partial-state mode; then the
+sink-free `(o, lse)` states (33 KB per rank for 64 heads) are exchanged and
+merged.  Two exchanges are built: "p2p" (default) - every rank stores its
+state into each peer's exchange buffer over NVLink and raises a flag there,
+and the merge kernel waits for all flags (fw_state_exchange_merge: two
+launches, no collective library on the data path); "nccl" - an NCCL
+all-gather followed by `fw_lse_combine`.  The rank that owns the page holding
+position `cache_len` appends the new token.
 
 Requests and KV heads need none of this: they shard with no communication.
 """
@@ -76,6 +80,7 @@ class ShardedDecoder:
     group: dist.ProcessGroup | None = None
     softmax_scale: float | None = None
     sinks: torch.Tensor | None = None
+    exchange: str = "p2p"
 
     def __post_init__(self):
         self.device = self.pool.device
@@ -95,6 +100,50 @@ class ShardedDecoder:
         self.scale = self.softmax_scale or self.head_dim ** -0.5
         self.lib = _native.library()
         self.scratch = None
+        self.peers = None
+        if self.exchange not in ("p2p", "nccl"):
+            raise ValueError(f"exchange must be 'p2p' or 'nccl'; got {self.exchange!r}.")
+        if self.exchange == "p2p":
+            self._open_exchange_buffers()
+
+    def _open_exchange_buffers(self):
+        """Allocates this rank's exchange buffer, passes its IPC handle to the
+        peers and maps theirs.  Collective over `group`; set-up, not the step."""
+        rows, d = self.nheads, self.head_dim
+        nbytes = self.lib.fw_exchange_buffer_bytes(self.world, rows, d)
+        if nbytes == 0:
+            raise RuntimeError(_native.last_error())
+        own = ctypes.c_void_p()
+        handle = ctypes.create_string_buffer(64)
+        with torch.cuda.device(self.device):
+            _native.check(self.lib.fw_peer_alloc(nbytes, ctypes.byref(own), handle))
+            handles = [None] * self.world
+            dist.all_gather_object(handles, handle.raw, group=self.group)
+            pointers = []
+            for rank, raw in enumerate(handles):
+                if rank == self.rank:
+                    pointers.append(own.value)
+                    continue
+                mapped = ctypes.c_void_p()
+                _native.check(self.lib.fw_peer_open(raw, ctypes.byref(mapped)))
+                pointers.append(mapped.value)
+        self.peers = (ctypes.c_void_p * self.world)(*pointers)
+        dist.barrier(group=self.group)   # every rank has mapped every buffer
+
+    def close(self):
+        """Unmaps the peers' buffers and frees this rank's.  Collective: no rank
+        may still be stepping."""
+        if self.peers is None:
+            return
+        torch.cuda.synchronize(self.device)
+        dist.barrier(group=self.group)
+        with torch.cuda.device(self.device):
+            for rank in range(self.world):
+                if rank != self.rank:
+                    _native.check(self.lib.fw_peer_close(self.peers[rank]))
+            dist.barrier(group=self.group)  # nobody maps this buffer any more
+            _native.check(self.lib.fw_peer_free(self.peers[self.rank]))
+        self.peers = None
 
     def step(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, global_len: int):
         """One decode step: q (1, 1, nheads, d), new k / v (1, 1, nheads_k, d),
@@ -127,7 +176,8 @@ class ShardedDecoder:
         torch.cuda.synchronize(self.device)
         self.local_len.fill_(local_length(global_len, self.page_size, self.first_page, self.last_page))
         graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph):
+        # thread_local: the process group's watchdog thread may query events meanwhile
+        with torch.cuda.graph(graph, capture_error_mode="thread_local"):
             self._enqueue(q, k, v, appends)
             if appends:
                 self.local_len.add_(1)
@@ -156,6 +206,17 @@ class ShardedDecoder:
             self.scratch = torch.zeros(nbytes, dtype=torch.uint8, device=self.device)
         args.workspace, args.workspace_bytes = self.scratch.data_ptr(), self.scratch.numel()
         _native.check(self.lib.fw_decode_kvcache(ctypes.byref(args), stream))
+        if self.exchange == "p2p":
+            if self.peers is None:
+                raise RuntimeError("the exchange buffers were closed.")
+            swap = _native.FwExchangeArgs(
+                peer_buffers=ctypes.cast(self.peers, ctypes.c_void_p), state_out=partial_out.data_ptr(),
+                state_lse=partial_lse.data_ptr(), sinks=_arrays.data_ptr(self.sinks),
+                out=self.out.data_ptr(), lse=self.lse.data_ptr(), status=self.scratch.data_ptr(),
+                world=self.world, rank=self.rank, rows=rows, nheads=self.nheads, head_dim=d,
+                lse_head_stride=1, lse_token_stride=self.nheads)
+            _native.check(self.lib.fw_state_exchange_merge(ctypes.byref(swap), stream))
+            return self.out, self.lse
         dist.all_gather_into_tensor(self.gathered, self.state, group=self.group)
         outs, lses = unpack_states(self.gathered, self.world, rows, d)
         merge = _native.FwCombineArgs(

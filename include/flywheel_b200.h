@@ -313,6 +313,49 @@ typedef struct FwCombineArgs {
 
 int fw_lse_combine(const FwCombineArgs* args, void* stream);
 
+/*
+ * Exchange + merge of per-rank attention states without a collective library:
+ * for one long request whose pages are split over the GPUs of a node, every
+ * rank runs fw_decode_kvcache in partial-state mode and then this call, which
+ * stores the rank's (o, lse) state into every peer's exchange buffer over
+ * NVLink, raises a per-rank epoch flag there, waits (with an iteration limit;
+ * FW_STATUS_WAIT_TIMEOUT in *status when a peer does not deliver) for the
+ * flags of all ranks and merges the gathered states like fw_lse_combine.  Two
+ * launches, capturable in a CUDA graph; every rank must make the same sequence
+ * of calls.  (No counterpart in the reference, whose library is single-device;
+ * the merge is _merge_states, patches/tpu-inference.patch:7174-7186.)
+ *
+ * Exchange buffers: fw_peer_alloc allocates and zeroes one of
+ * fw_exchange_buffer_bytes on the current device and returns a 64-byte handle;
+ * the host program passes the handles between the ranks' processes, each rank
+ * maps its peers' buffers with fw_peer_open (which also enables peer access)
+ * and lists all of them, its own included, in peer_buffers[0 .. world).  These
+ * four routines allocate / map memory and belong to set-up, not to the step.
+ */
+typedef struct FwExchangeArgs {
+  void* const* peer_buffers;  /* host array of `world` device pointers */
+  const float* state_out;     /* (rows, head_dim) f32: partial_out of the decode call */
+  const float* state_lse;     /* (rows,) f32 */
+  const float* sinks;         /* NULL or (nheads,) */
+  void* out;                  /* (rows, head_dim) bf16 */
+  float* lse;                 /* NULL or strided like FwCombineArgs.lse */
+  int32_t* status;            /* NULL or a device status word */
+  int32_t world;
+  int32_t rank;
+  int32_t rows;
+  int32_t nheads;
+  int32_t head_dim;
+  int32_t lse_head_stride;
+  int32_t lse_token_stride;
+} FwExchangeArgs;
+
+uint64_t fw_exchange_buffer_bytes(int32_t world, int32_t rows, int32_t head_dim);
+int fw_peer_alloc(uint64_t bytes, void** ptr, void* handle64);
+int fw_peer_open(const void* handle64, void** ptr);
+int fw_peer_close(void* ptr);
+int fw_peer_free(void* ptr);
+int fw_state_exchange_merge(const FwExchangeArgs* args, void* stream);
+
 /* Copies the device status word at the head of `workspace` to *status (host).
  * Synchronises `stream`; meant for tests and debugging, not the hot path. */
 int fw_read_status(const void* workspace, void* stream, int32_t* status);

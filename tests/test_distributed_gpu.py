@@ -1,5 +1,6 @@
-"""Long-context decode with the KV pages split over 2 GPUs (NCCL all-gather of
-the per-rank (o, lse) states + merge) against the CPU oracle.  Needs 2 GPUs."""
+"""Long-context decode with the KV pages split over 2 GPUs against the CPU
+oracle, with both exchanges of the per-rank (o, lse) states: peer stores over
+NVLink fused with the merge, and an NCCL all-gather + merge.  Needs 2 GPUs."""
 
 import os
 import socket
@@ -18,7 +19,7 @@ def free_port():
         return sock.getsockname()[1]
 
 
-def _rank_main(rank, world, port, results):
+def _rank_main(rank, world, port, results, exchange):
     import sys
     import pathlib
     import ml_dtypes
@@ -52,7 +53,8 @@ def _rank_main(rank, world, port, results):
         pool_t = torch.from_numpy(pool.view(np.int16)).to(device).view(torch.bfloat16)
         table = torch.from_numpy(perm.astype(np.int32)[None]).to(device)
         decoder = d.ShardedDecoder(pool=pool_t, table=table, total_pages=total_pages, nheads=heads,
-                                   nheads_k=kv_heads, sinks=torch.from_numpy(sinks).to(device))
+                                   nheads_k=kv_heads, sinks=torch.from_numpy(sinks).to(device),
+                                   exchange=exchange)
         to_t = lambda a: torch.from_numpy(a.view(np.int16)).to(device).view(torch.bfloat16)
         worst = 0.0
         for step in range(steps):
@@ -73,15 +75,35 @@ def _rank_main(rank, world, port, results):
         got_pool = pool_t.cpu().view(torch.int16).numpy()
         want_rows = oracle.merge_kv_heads(keys, values).reshape(total_pages, page, 2 * kv_heads, dim)
         np.testing.assert_array_equal(got_pool[perm], want_rows[first:last].view(np.int16))
+        # the same step replayed as a CUDA graph: the cached length lives on the device
+        # (peer-store exchange only: a capture right after eager NCCL work trips over
+        # the process group's watchdog thread, which is not this library's concern)
+        q, k, v = draw((1, 1, heads, dim)), draw((1, 1, kv_heads, dim)), draw((1, 1, kv_heads, dim))
+        q_t, k_t, v_t = to_t(q), to_t(k), to_t(v)
+        graph = decoder.capture(q_t, k_t, v_t, length, 3) if exchange == "p2p" else None
+        for _ in range(3 if graph is not None else 0):
+            graph.replay()
+            torch.cuda.synchronize()
+            keys[length], values[length] = k[0, 0], v[0, 0]
+            length += 1
+            want, _ = oracle.attend_rows(
+                q[0].astype(np.float32), keys[:length].astype(np.float32),
+                values[:length].astype(np.float32), total=length, causal=True, window_left=None,
+                softcap=0.0, scale=dim ** -0.5, sinks=sinks)
+            np.testing.assert_allclose(decoder.out.float().cpu().numpy()[0], want, rtol=1e-2, atol=2e-2)
+        from flywheel_tpu.softmax_attention import _native
+        assert _native.read_status(decoder.scratch, device) == 0
+        decoder.close()
         results[rank] = worst
     finally:
         dist.destroy_process_group()
 
 
-def test_long_context_decode_split_over_two_gpus():
+@pytest.mark.parametrize("exchange", ["p2p", "nccl"])
+def test_long_context_decode_split_over_two_gpus(exchange):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
     world, port = 2, free_port()
     results = mp.Manager().dict()
-    mp.spawn(_rank_main, args=(world, port, results), nprocs=world, join=True)
+    mp.spawn(_rank_main, args=(world, port, results, exchange), nprocs=world, join=True)
     assert len(results) == 2 and max(results.values()) < 2e-2
