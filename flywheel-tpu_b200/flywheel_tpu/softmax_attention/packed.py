@@ -98,9 +98,9 @@ def parse_qkv(q, k, v, head_dim, token_major, expected_rank, layout):
     return nheads, nheads_k, head_dim_qk
 
 
-def rotary_operand(rotary_cos, rotary_sin, rotary_interleaved, rotary_k, head_dim, min_len, device):
-    """None, or (cos, sin, interleaved, rotate_k) on the device (rotary.py:27-215
-    of the reference: full-head tables (seqlen_ro, head_dim / 2) in bf16 or f32)."""
+def check_rotary(rotary_cos, rotary_sin, rotary_interleaved, rotary_k, head_dim, min_len):
+    """Validates the RoPE arguments (rotary.py:27-215 of the reference: full-head
+    tables (seqlen_ro, head_dim / 2) in bf16 or f32); True when tables are given."""
     if type(rotary_interleaved) is not bool:
         raise ValueError("rotary_interleaved must be a static bool.")
     if type(rotary_k) is not bool:
@@ -110,7 +110,7 @@ def rotary_operand(rotary_cos, rotary_sin, rotary_interleaved, rotary_k, head_di
     if rotary_cos is None:
         if not rotary_k:
             raise ValueError("rotary_k=False needs rotary_cos and rotary_sin.")
-        return None
+        return False
     cos_shape, sin_shape = _arrays.shape(rotary_cos), _arrays.shape(rotary_sin)
     if len(cos_shape) != 2 or tuple(sin_shape) != tuple(cos_shape):
         raise ValueError("rotary_cos and rotary_sin must have the same 2-D shape.")
@@ -123,6 +123,11 @@ def rotary_operand(rotary_cos, rotary_sin, rotary_interleaved, rotary_k, head_di
         raise ValueError("rotary_cos and rotary_sin must share Q's dtype or be float32.")
     if cos_shape[0] < min_len:
         raise ValueError("rotary table is shorter than the KV sequence bound.")
+    return True
+
+
+def rotary_operand(rotary_cos, rotary_sin, rotary_interleaved, rotary_k, device):
+    """(cos, sin, interleaved, rotate_k) with the tables on the device."""
     return (_arrays.to_device(rotary_cos, device).contiguous(),
             _arrays.to_device(rotary_sin, device).contiguous(), rotary_interleaved, rotary_k)
 
@@ -238,11 +243,12 @@ def flash_attn_func(
     seq_axis = 1 if token_major else 2
     seqlen_q, seqlen_k = q.shape[seq_axis], k.shape[seq_axis]
     left, is_causal, right = packed_window(window_size, causal)
-    device = _arrays.pick_device(q, k)
-    rotary = rotary_operand(rotary_cos, rotary_sin, rotary_interleaved, rotary_k, head_dim_qk,
-                            seqlen_k, device)
-    if rotary is not None and seqlen_q > seqlen_k:
+    has_rotary = check_rotary(rotary_cos, rotary_sin, rotary_interleaved, rotary_k, head_dim_qk, seqlen_k)
+    if has_rotary and seqlen_q > seqlen_k:
         raise ValueError("fused RoPE rotates Q from seqlen_k - seqlen_q on, so seqlen_q <= seqlen_k.")
+    device = _arrays.pick_device(q, k)
+    rotary = (rotary_operand(rotary_cos, rotary_sin, rotary_interleaved, rotary_k, device)
+              if has_rotary else None)
     sinks = sinks_operand(learnable_sink, nheads, device)
     scale = 1.0 / math.sqrt(head_dim_qk) if softmax_scale is None else float(softmax_scale)
     q_dev, k_dev, v_dev = (_arrays.to_device(x, device).contiguous() for x in (q, k, v))
@@ -305,9 +311,10 @@ def packed_varlen_attn(q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_se
         if bound <= 0:
             raise ValueError(f"{arg_name} must be positive; got {bound}.")
     left, is_causal, right = packed_window(window_size, causal)
+    has_rotary = check_rotary(rotary_cos, rotary_sin, rotary_interleaved, rotary_k, head_dim_qk, max_seqlen_k)
     device = _arrays.pick_device(q, k)
-    rotary = rotary_operand(rotary_cos, rotary_sin, rotary_interleaved, rotary_k, head_dim_qk,
-                            max_seqlen_k, device)
+    rotary = (rotary_operand(rotary_cos, rotary_sin, rotary_interleaved, rotary_k, device)
+              if has_rotary else None)
     sinks = sinks_operand(learnable_sink, nheads, device)
     scale = 1.0 / math.sqrt(head_dim_qk) if softmax_scale is None else float(softmax_scale)
     q_dev, k_dev, v_dev = (_arrays.to_device(x, device).contiguous() for x in (q, k, v))
