@@ -152,10 +152,16 @@ def build_prefill_workload(seed, device):
     gen.manual_seed(1000 + seed)
     pool = torch.randn((pool_pages, PAGE, 2 * PF_HK, D), generator=gen, device=device,
                        dtype=torch.float32).to(torch.bfloat16)
+    # FW_PREFILL_POOL=e4m3 re-types the pool for the fp8 variant of the workload
+    # (same shapes; per-tensor descale 5.5 / 448).
+    descale = None
+    if os.environ.get("FW_PREFILL_POOL", "bf16") == "e4m3":
+        pool = (pool.float() * (448.0 / 5.5)).clamp(-448, 448).to(torch.float8_e4m3fn)
+        descale = torch.tensor([5.5 / 448.0], dtype=torch.float32, device=device)
     cu = np.concatenate(([0], np.cumsum(chunk))).astype(np.int32)
     total_q = int(cu[-1])
     q_host = torch.randn((PF_HQ, total_q, D), dtype=torch.float32).to(torch.bfloat16).pin_memory()
-    return {"pool": pool, "q_host": q_host, "q": q_host.to(device), "cu": cu, "seqused": seqused,
+    return {"pool": pool, "descale": descale, "q_host": q_host, "q": q_host.to(device), "cu": cu, "seqused": seqused,
             "table": table, "prefix": prefix, "chunk": chunk, "total_q": total_q,
             "flops": workloads.prefill_flops(prefix, chunk, PF_HQ, D),
             "cu_dev": torch.from_numpy(cu).to(device), "seqused_dev": torch.from_numpy(seqused).to(device),
@@ -171,8 +177,11 @@ def make_prefill_call(work, device):
         cu_seqlens_q=work["cu_dev"].data_ptr(), seqused_k=work["seqused_dev"].data_ptr(),
         block_table=work["table_dev"].data_ptr(), num_pages=work["pool"].shape[0], page_size=PAGE,
         pages_per_seq=work["table_dev"].shape[1], batch=PF_BATCH, total_q=work["total_q"],
-        max_seqlen_q=int(work["chunk"].max()), nheads=PF_HQ, nheads_k=PF_HK, head_dim=D, kv_dtype=0,
+        max_seqlen_q=int(work["chunk"].max()), nheads=PF_HQ, nheads_k=PF_HK, head_dim=D,
+        kv_dtype=0 if work["descale"] is None else 1,
         causal=1, window_left=-1, softmax_scale=D ** -0.5, softcap=0.0, token_major=0)
+    if work["descale"] is not None:
+        args.k_descale = args.v_descale = work["descale"].data_ptr()
     lib = _native.library()
     nbytes = lib.fw_prefill_workspace_bytes(ctypes.byref(args))
     if nbytes == 0:

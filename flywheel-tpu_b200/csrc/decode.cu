@@ -1122,6 +1122,7 @@ constexpr int kSortBuckets = 2048;
 struct PrefillPlanParams {
   const int* cu;
   const int* cu_k;     // packed K/V: request r's keys are rows [cu_k[r], cu_k[r + 1]); else NULL
+  int kv_stride;       // packed K/V in fixed slots: request r's keys start at row r * kv_stride
   const int* seqused;  // paged: request r's key count
   const int* num_active;
   int* items;
@@ -1192,7 +1193,7 @@ __global__ void __launch_bounds__(256) prefill_plan_kernel(const PrefillPlanPara
         it[2] = min(pp.qb, c - j * pp.qb);
         it[3] = used - c + (j + 1) * pp.qb;  // token t of the block sits on diagonal it[3] - qb + t
         it[4] = used;
-        it[5] = pp.cu_k ? pp.cu_k[r] : 0;  // first key row of a packed request
+        it[5] = pp.cu_k ? pp.cu_k[r] : r * pp.kv_stride;  // first key row of a packed request
         it[6] = it[7] = 0;
       }
     }
@@ -1226,6 +1227,7 @@ int launch_prefill_plan(const FwPrefillArgs* a, int qb, int max_items, int* item
   PrefillPlanParams pp;
   pp.cu = a->cu_seqlens_q;
   pp.cu_k = a->block_table == nullptr ? a->cu_seqlens_k : nullptr;
+  pp.kv_stride = a->block_table == nullptr && a->cu_seqlens_k == nullptr ? a->kv_request_stride : 0;
   pp.seqused = a->seqused_k;
   pp.num_active = a->num_active;
   pp.items = items;

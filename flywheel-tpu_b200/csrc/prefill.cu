@@ -129,30 +129,128 @@ static uint64_t rope_bytes(const FwPrefillArgs* a) {
   return (static_cast<uint64_t>(a->total_q) * a->nheads * a->head_dim * 2 + 255) & ~255ull;
 }
 
-// Chunks of at least this many tokens go to the tensor-core kernel; shorter
-// ones are KV-streaming work and go to the split-KV kernel.  The environment
-// variable FLYWHEEL_PREFILL_KERNEL=tcgen05|splitkv pins the choice (tests and
-// profiling).
-static constexpr int kTensorCoreMinChunk = 64;
+// ---------------------------------------------------------------- gather for the tensor-core kernel
+// The tensor-core kernel reads bf16 K/V through 64-token TMA boxes.  Pools it
+// cannot read in place (fp8, or pages that are not a multiple of 64 tokens) are
+// first copied, request by request, into bf16 K and V scratch tensors of
+// (batch * capacity, nheads_k, head_dim), capacity = pages_per_seq * page_size:
+// request r's key t lands in row r * capacity + t.  fp8 widens exactly to bf16;
+// the descales stay where they were (score scale and output scale).  One block
+// per (page, request); pages past the request's length are skipped.
+struct GatherParams {
+  const uint8_t* pool;
+  const int* block_table;
+  const int* seqused;
+  const int* num_active;
+  __nv_bfloat16* k_out;
+  __nv_bfloat16* v_out;
+  int* status;
+  long long num_pages;
+  int batch, page_size, pages_per_seq, nheads_k, cache_heads, head_dim, kv_dtype;
+};
 
-static bool use_tensor_core_kernel(const FwPrefillArgs* a) {
-  if (!tcgen05_prefill_supported(a)) return false;
+template <int KVT>
+__device__ __forceinline__ uint4 widen8(uint2 raw) {
+  // eight fp8 values -> eight bf16 (exact: fp8 -> f16 -> f32 -> bf16 loses nothing)
+  uint32_t h[4] = {fp8x2_to_f16x2<KVT>(raw.x & 0xffff), fp8x2_to_f16x2<KVT>(raw.x >> 16),
+                   fp8x2_to_f16x2<KVT>(raw.y & 0xffff), fp8x2_to_f16x2<KVT>(raw.y >> 16)};
+  uint32_t o[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&h[i]));
+    o[i] = pack_bf16(f.x, f.y);
+  }
+  return make_uint4(o[0], o[1], o[2], o[3]);
+}
+
+__global__ void __launch_bounds__(256) gather_kv_kernel(const GatherParams p) {
+  const int page_idx = blockIdx.x, r = blockIdx.y;
+  const int n_active = p.num_active ? min(p.batch, max(0, *p.num_active)) : p.batch;
+  if (r >= n_active) return;
+  const int used = p.seqused[r];
+  const int tok0 = page_idx * p.page_size;
+  if (tok0 >= used) return;
+  int page = p.block_table[static_cast<long long>(r) * p.pages_per_seq + page_idx];
+  if (page < 0 || page >= p.num_pages) {
+    if (threadIdx.x == 0) report_status(p.status, FW_STATUS_BAD_PAGE);
+    page = 0;
+  }
+  const int itemsize = p.kv_dtype == FW_DTYPE_BF16 ? 2 : 1;
+  const int tokens = min(p.page_size, used - tok0);
+  const int chunks_per_plane = p.head_dim / 8;                 // 16-byte output chunks per head plane
+  const long long row_bytes = static_cast<long long>(p.cache_heads) * p.head_dim * itemsize;
+  const uint8_t* src_page = p.pool + static_cast<long long>(page) * p.page_size * row_bytes;
+  const long long capacity = static_cast<long long>(p.pages_per_seq) * p.page_size;
+  const int per_token = 2 * p.nheads_k * chunks_per_plane;
+  for (int i = threadIdx.x; i < tokens * per_token; i += blockDim.x) {
+    const int t = i / per_token, rem = i - t * per_token;
+    const int plane = rem / chunks_per_plane, c = rem - plane * chunks_per_plane;  // plane = 2 * head + is_v
+    const uint8_t* src = src_page + t * row_bytes + (static_cast<long long>(plane) * p.head_dim + c * 8) * itemsize;
+    uint4 value;
+    if (p.kv_dtype == FW_DTYPE_BF16) value = *reinterpret_cast<const uint4*>(src);
+    else if (p.kv_dtype == FW_DTYPE_E4M3) value = widen8<FW_DTYPE_E4M3>(*reinterpret_cast<const uint2*>(src));
+    else value = widen8<FW_DTYPE_E5M2>(*reinterpret_cast<const uint2*>(src));
+    __nv_bfloat16* dst = ((plane & 1) ? p.v_out : p.k_out) +
+                         ((r * capacity + tok0 + t) * p.nheads_k + (plane >> 1)) * p.head_dim + c * 8;
+    *reinterpret_cast<uint4*>(dst) = value;
+  }
+}
+
+// Chunks of at least this many tokens go to the tensor-core kernel; shorter
+// ones are KV-streaming work and go to the split-KV kernel.  Pools the
+// tensor-core kernel cannot read in place take the gather above first, which
+// pays off once a chunk is a few hundred tokens (the copy is linear in the key
+// count, the attention is chunk times that).  The environment variable
+// FLYWHEEL_PREFILL_KERNEL=tcgen05|splitkv pins the choice (tests and profiling).
+static constexpr int kTensorCoreMinChunk = 64;
+static constexpr int kGatherMinChunk = 256;
+
+enum class PrefillRoute { kTensorCore, kGatherTensorCore, kSplitKv };
+
+static bool gather_route_possible(const FwPrefillArgs* a) {
+  if (a->head_dim != 128 || a->block_table == nullptr || a->page_size <= 0 || a->pages_per_seq <= 0) return false;
+  if (a->page_size % 16) return false;  // the split-KV kernel reports the shape error
+  FwPrefillArgs as_packed = *a;
+  as_packed.kv_dtype = FW_DTYPE_BF16;
+  as_packed.page_size = 64;
+  if (!tcgen05_prefill_supported(&as_packed)) return false;
+  const long long rows = static_cast<long long>(a->batch) * a->pages_per_seq * a->page_size;
+  return rows < (1ll << 31);
+}
+
+static PrefillRoute pick_route(const FwPrefillArgs* a) {
   const char* pin = std::getenv("FLYWHEEL_PREFILL_KERNEL");
-  if (pin != nullptr && std::strcmp(pin, "splitkv") == 0) return false;
-  if (pin != nullptr && std::strcmp(pin, "tcgen05") == 0) return true;
-  return a->max_seqlen_q >= kTensorCoreMinChunk;
+  const bool pin_split = pin != nullptr && std::strcmp(pin, "splitkv") == 0;
+  const bool pin_tensor = pin != nullptr && std::strcmp(pin, "tcgen05") == 0;
+  if (pin_split) return PrefillRoute::kSplitKv;
+  if (tcgen05_prefill_supported(a))
+    return pin_tensor || a->max_seqlen_q >= kTensorCoreMinChunk ? PrefillRoute::kTensorCore : PrefillRoute::kSplitKv;
+  if (gather_route_possible(a) && (pin_tensor || a->max_seqlen_q >= kGatherMinChunk))
+    return PrefillRoute::kGatherTensorCore;
+  return PrefillRoute::kSplitKv;
+}
+
+static uint64_t gather_scratch_bytes(const FwPrefillArgs* a) {
+  const uint64_t rows = static_cast<uint64_t>(a->batch) * a->pages_per_seq * a->page_size;
+  return (rows * a->nheads_k * a->head_dim * 2 + 255) & ~255ull;  // one of K / V
 }
 
 static uint64_t attention_workspace_bytes(const FwPrefillArgs* a) {
-  const uint64_t n = use_tensor_core_kernel(a) ? tcgen05_prefill_workspace_bytes(a)
-                                               : splitkv_prefill_workspace_bytes(a);
+  uint64_t n = 0;
+  switch (pick_route(a)) {
+    case PrefillRoute::kTensorCore: n = tcgen05_prefill_workspace_bytes(a); break;
+    case PrefillRoute::kGatherTensorCore: n = tcgen05_prefill_workspace_bytes(a); break;
+    case PrefillRoute::kSplitKv: n = splitkv_prefill_workspace_bytes(a); break;
+  }
   return n == 0 ? 0 : (n + 255) & ~255ull;
 }
 
 extern "C" uint64_t fw_prefill_workspace_bytes(const FwPrefillArgs* a) {
   if (check_prefill_args(a) != FW_OK) return 0;
   const uint64_t n = attention_workspace_bytes(a);
-  return n == 0 ? 0 : n + rope_bytes(a);
+  if (n == 0) return 0;
+  const uint64_t gather = pick_route(a) == PrefillRoute::kGatherTensorCore ? 2 * gather_scratch_bytes(a) : 0;
+  return n + rope_bytes(a) + gather;
 }
 
 extern "C" int fw_prefill_paged(const FwPrefillArgs* a, void* stream_ptr) {
@@ -204,8 +302,60 @@ extern "C" int fw_prefill_paged(const FwPrefillArgs* a, void* stream_ptr) {
     local.q = rp.q_out;
     local.workspace_bytes = head;
   }
-  if (use_tensor_core_kernel(&local)) return tcgen05_prefill(&local, stream);
-  return splitkv_prefill(&local, stream);
+  switch (pick_route(a)) {
+    case PrefillRoute::kTensorCore: return tcgen05_prefill(&local, stream);
+    case PrefillRoute::kSplitKv: return splitkv_prefill(&local, stream);
+    case PrefillRoute::kGatherTensorCore: break;
+  }
+  // Gather route: [attention scratch | rotated q | K scratch | V scratch].
+  const uint64_t head = attention_workspace_bytes(a), rope = rope_bytes(a), plane = gather_scratch_bytes(a);
+  if (a->workspace == nullptr || a->workspace_bytes < head + rope + 2 * plane ||
+      (reinterpret_cast<uintptr_t>(a->workspace) & 255)) {
+    set_error("workspace must be 256-byte aligned and hold %llu bytes; got %llu.",
+              static_cast<unsigned long long>(head + rope + 2 * plane),
+              static_cast<unsigned long long>(a->workspace_bytes));
+    return FW_ERR_WORKSPACE;
+  }
+  if (a->kv_cache == nullptr || a->seqused_k == nullptr || a->block_table == nullptr) {
+    set_error("kv_cache, seqused_k and block_table must not be NULL.");
+    return FW_ERR_BAD_SHAPE;
+  }
+  uint8_t* ws = static_cast<uint8_t*>(a->workspace);
+  const int itemsize = a->kv_dtype == FW_DTYPE_BF16 ? 2 : 1;
+  const int heads_per_word = itemsize == 1 ? 2 : 1;
+  GatherParams gp;
+  gp.pool = static_cast<const uint8_t*>(a->kv_cache);
+  gp.block_table = a->block_table;
+  gp.seqused = a->seqused_k;
+  gp.num_active = a->num_active;
+  gp.k_out = reinterpret_cast<__nv_bfloat16*>(ws + head + rope);
+  gp.v_out = reinterpret_cast<__nv_bfloat16*>(ws + head + rope + plane);
+  gp.status = reinterpret_cast<int*>(ws);
+  gp.num_pages = a->num_pages;
+  gp.batch = a->batch;
+  gp.page_size = a->page_size;
+  gp.pages_per_seq = a->pages_per_seq;
+  gp.nheads_k = a->nheads_k;
+  gp.cache_heads = 2 * ((a->nheads_k + heads_per_word - 1) / heads_per_word * heads_per_word);
+  gp.head_dim = a->head_dim;
+  gp.kv_dtype = a->kv_dtype;
+  gather_kv_kernel<<<dim3(a->pages_per_seq, a->batch), 256, 0, stream>>>(gp);
+  cudaError_t err = cudaGetLastError();
+  if (err != cudaSuccess) {
+    set_error("gather kernel launch: %s", cudaGetErrorString(err));
+    return FW_ERR_LAUNCH;
+  }
+  // The same request table, now over packed bf16 K / V: request r's keys start
+  // at row r * capacity, seqused_k still counts them.
+  local.kv_cache = gp.k_out;
+  local.v_packed = gp.v_out;
+  local.block_table = nullptr;
+  local.kv_dtype = FW_DTYPE_BF16;
+  local.kv_token_major = 1;
+  local.kv_request_stride = a->pages_per_seq * a->page_size;
+  local.total_k = a->batch * local.kv_request_stride;
+  local.workspace_bytes = head;
+  return tcgen05_prefill(&local, stream);
 }
 
 // ---------------------------------------------------------------- packed K/V

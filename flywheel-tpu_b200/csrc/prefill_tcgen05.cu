@@ -655,8 +655,9 @@ uint64_t tcgen05_prefill_workspace_bytes(const FwPrefillArgs* a) {
 int tcgen05_prefill(const FwPrefillArgs* a, cudaStream_t stream) {
   const bool packed = a->block_table == nullptr && a->v_packed != nullptr;
   if (packed) {
+    const bool slots = a->kv_request_stride > 0 && a->seqused_k != nullptr;  // fixed-size request slots
     if (a->q == nullptr || a->out == nullptr || a->kv_cache == nullptr || a->cu_seqlens_q == nullptr ||
-        a->cu_seqlens_k == nullptr || a->total_k <= 0) {
+        (a->cu_seqlens_k == nullptr && !slots) || a->total_k <= 0) {
       set_error("q, out, k, v, cu_seqlens_q and cu_seqlens_k must not be NULL and total_k positive.");
       return FW_ERR_BAD_SHAPE;
     }

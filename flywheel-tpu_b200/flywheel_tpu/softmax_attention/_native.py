@@ -81,7 +81,7 @@ class FwPrefillArgs(ctypes.Structure):
         ("rotary_interleaved", i32), ("rotary_bf16", i32),
         ("v_packed", c_ptr), ("cu_seqlens_k", c_ptr), ("total_k", i32),
         ("kv_token_major", i32), ("rotary_k", i32), ("sink_period", i32),
-        ("window_right", i32),
+        ("window_right", i32), ("kv_request_stride", i32),
     ]
 
 

@@ -262,6 +262,9 @@ typedef struct FwPrefillArgs {
   int32_t rotary_k;      /* 1: K is rotated too, token t of a request at position t */
   int32_t sink_period;   /* 0: sinks has nheads entries; n > 0: head h uses sinks[h % n] */
   int32_t window_right;  /* > 0 with causal = 0: keys up to this far past a row's diagonal are visible */
+  /* Packed K/V in fixed-size request slots instead of cu_seqlens_k: n > 0 puts
+   * request r's keys at rows [r * n, r * n + seqused_k[r]) (cu_seqlens_k NULL). */
+  int32_t kv_request_stride;
 } FwPrefillArgs;
 
 uint64_t fw_prefill_workspace_bytes(const FwPrefillArgs* args);
