@@ -241,6 +241,10 @@ __device__ __forceinline__ uint32_t tmem_s(uint32_t base, int t) { return base +
 #define FW_WAIT(site, j, bar, parity) \
   (mbar_wait_bounded(bar, parity, abort_flag) || (record_timeout(p.status, site, j), false))
 
+// D = head_dim, 128 or 64 (64 for packed K/V only).  Shared memory keeps the
+// 128-wide layout either way: operands are stored as 64-element (128-byte) halves,
+// and at 64 the second half of every tile simply stays unused.
+template <int D>
 __global__ void __launch_bounds__(64 + kStreams * 128, 1)
 prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv,
                        const __grid_constant__ CUtensorMap map_v, const Tc05Params p) {
@@ -299,10 +303,10 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       tma_prefetch_desc(&map_q);
       tma_prefetch_desc(&map_kv);
       if (p.packed) tma_prefetch_desc(&map_v);
-      mbar_arrive_expect_tx(&bars->q_full, n_streams * p.group * p.tpb * 256);
+      mbar_arrive_expect_tx(&bars->q_full, n_streams * p.group * p.tpb * D * 2);
       for (int t = 0; t < n_streams; ++t)
         for (int g = 0; g < p.group; ++g)
-          for (int half = 0; half < 2; ++half)
+          for (int half = 0; half < D / 64; ++half)
             tma_load_3d(smem + kSmemQ + t * 32768 + half * 16384 + g * p.tpb * 128, &map_q, &bars->q_full,
                         half * 64, q_row0 + t * p.tpb, h * p.group + g);
       bool ok = true;
@@ -339,9 +343,9 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           }
           tok[sub] = pos - page_idx * p.page_size;
         }
-        mbar_arrive_expect_tx(&bars->k_full[s], subs * 64 * 256);
+        mbar_arrive_expect_tx(&bars->k_full[s], subs * 64 * D * 2);
         for (int sub = 0; sub < subs; ++sub)
-          for (int half = 0; half < 2; ++half) {
+          for (int half = 0; half < D / 64; ++half) {
             uint8_t* dst = smem + kSmemK + s * 32768 + half * 16384 + sub * 8192;
             if (p.packed) tma_load_3d(dst, &map_kv, &bars->k_full[s], half * 64, tok[sub], h);
             else tma_load_4d(dst, &map_kv, &bars->k_full[s], half * 64, 2 * h, tok[sub], page[sub]);
@@ -350,9 +354,9 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           ok = false;
           break;
         }
-        mbar_arrive_expect_tx(&bars->v_full[s], subs * 64 * 256);
+        mbar_arrive_expect_tx(&bars->v_full[s], subs * 64 * D * 2);
         for (int sub = 0; sub < subs; ++sub)
-          for (int half = 0; half < 2; ++half) {
+          for (int half = 0; half < D / 64; ++half) {
             uint8_t* dst = smem + kSmemV + s * 32768 + half * 16384 + sub * 8192;
             if (p.packed) tma_load_3d(dst, &map_v, &bars->v_full[s], half * 64, tok[sub], h);
             else tma_load_4d(dst, &map_kv, &bars->v_full[s], half * 64, 2 * h + 1, tok[sub], page[sub]);
@@ -371,7 +375,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     // one stream's MMAs while the other stream's softmax group works.
     if (lane == 0) {
       constexpr uint32_t idesc_qk = instr_desc(kBN, false);
-      constexpr uint32_t idesc_pv = instr_desc(128, true);
+      constexpr uint32_t idesc_pv = instr_desc(D, true);
       const uint64_t q_desc0 = smem_desc(smem_u32(smem + kSmemQ), 16, 1024);
       const uint64_t k_desc0 = smem_desc(smem_u32(smem + kSmemK), 16, 1024);
       const uint64_t v_desc0 = smem_desc(smem_u32(smem + kSmemV), 16384, 1024);
@@ -380,7 +384,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         const uint64_t k_desc = k_desc0 + static_cast<uint32_t>((j % kKvStages) * (32768 >> 4));
         const uint32_t d_addr = tmem_s(tmem, t);
 #pragma unroll
-        for (int k = 0; k < 8; ++k) {
+        for (int k = 0; k < D / 16; ++k) {
           const uint32_t off = (k >> 2) * 16384 + (k & 3) * 32;  // head_dim half, 16-element step
           tc_mma(d_addr, desc_advance(q_desc, off), desc_advance(k_desc, off), idesc_qk, k > 0 ? 1u : 0u);
         }
@@ -534,7 +538,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           }
           tc_fence_after();
 #pragma unroll
-          for (int c = 0; c < 4; ++c) {
+          for (int c = 0; c < D / 32; ++c) {
             uint32_t o[32];
             tmem_ld32(o_addr + c * 32, o);
             tmem_wait_ld();
@@ -560,8 +564,8 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         }
         const int first_bad = kv_end - pos0;  // in [1, kBN - 1]
         uint8_t* vbase = smem + kSmemV + s * 32768;
-        for (int idx = row; idx < (kBN - first_bad) * 16; idx += 128) {
-          const int r = first_bad + idx / 16, c = idx % 16;
+        for (int idx = row; idx < (kBN - first_bad) * (D / 8); idx += 128) {
+          const int r = first_bad + idx / (D / 8), c = idx % (D / 8);
           *reinterpret_cast<uint4*>(vbase + (c >> 3) * 16384 + r * 128 + (((c & 7) ^ (r & 7)) << 4)) =
               make_uint4(0u, 0u, 0u, 0u);
         }
@@ -591,7 +595,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       __nv_bfloat16* orow = p.out + (static_cast<long long>(q_row0) + tl) * p.tok_stride +
                             static_cast<long long>(hq) * p.head_stride;
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 0; c < D / 32; ++c) {
         uint32_t o[32];
         if (n_tiles > 0) {
           tmem_ld32(o_addr + c * 32, o);
@@ -630,7 +634,9 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 
 // ---------------------------------------------------------------- host
 bool tcgen05_prefill_supported(const FwPrefillArgs* a) {
-  if (a->kv_dtype != FW_DTYPE_BF16 || a->head_dim != 128) return false;
+  const bool packed_kv = a->block_table == nullptr && a->v_packed != nullptr;
+  if (a->kv_dtype != FW_DTYPE_BF16) return false;
+  if (a->head_dim != 128 && !(a->head_dim == 64 && packed_kv)) return false;
   if (a->nheads_k <= 0 || a->nheads % a->nheads_k) return false;
   const int group = a->nheads / a->nheads_k;
   // 128 rows hold (128 / group) tokens x group heads; a group that does not
@@ -693,12 +699,13 @@ int tcgen05_prefill(const FwPrefillArgs* a, cudaStream_t stream) {
   p.out = static_cast<__nv_bfloat16*>(a->out);
   p.lse = a->lse;
   p.status = static_cast<int*>(a->workspace);
+  const int d = a->head_dim;
   if (a->token_major) {
-    p.tok_stride = static_cast<long long>(a->nheads) * 128;
-    p.head_stride = 128;
+    p.tok_stride = static_cast<long long>(a->nheads) * d;
+    p.head_stride = d;
   } else {
-    p.tok_stride = 128;
-    p.head_stride = static_cast<long long>(a->total_q) * 128;
+    p.tok_stride = d;
+    p.head_stride = static_cast<long long>(a->total_q) * d;
   }
   p.num_pages = a->num_pages;
   p.total_q = a->total_q;
@@ -721,7 +728,8 @@ int tcgen05_prefill(const FwPrefillArgs* a, cudaStream_t stream) {
   // q viewed as (head_dim, tokens, heads); a box is 64 elements x tpb tokens of one head.
   CUtensorMap map_q, map_kv, map_v;
   {
-    const uint64_t dims[3] = {128, static_cast<uint64_t>(a->total_q), static_cast<uint64_t>(a->nheads)};
+    const uint64_t dims[3] = {static_cast<uint64_t>(d), static_cast<uint64_t>(a->total_q),
+                              static_cast<uint64_t>(a->nheads)};
     const uint64_t strides[2] = {static_cast<uint64_t>(p.tok_stride) * 2, static_cast<uint64_t>(p.head_stride) * 2};
     const uint32_t box[3] = {64, static_cast<uint32_t>(tpb), 1};
     rc = encode_tensor_map_bf16(&map_q, 3, a->q, dims, strides, box);
@@ -729,9 +737,11 @@ int tcgen05_prefill(const FwPrefillArgs* a, cudaStream_t stream) {
   }
   if (packed) {
     // K and V viewed as (head_dim, tokens, heads); a box is 64 elements x 64 tokens of one head.
-    const uint64_t dims[3] = {128, static_cast<uint64_t>(a->total_k), static_cast<uint64_t>(a->nheads_k)};
-    const uint64_t tok = a->kv_token_major ? static_cast<uint64_t>(a->nheads_k) * 256 : 256;
-    const uint64_t head = a->kv_token_major ? 256 : static_cast<uint64_t>(a->total_k) * 256;
+    const uint64_t dims[3] = {static_cast<uint64_t>(d), static_cast<uint64_t>(a->total_k),
+                              static_cast<uint64_t>(a->nheads_k)};
+    const uint64_t row = static_cast<uint64_t>(d) * 2;
+    const uint64_t tok = a->kv_token_major ? static_cast<uint64_t>(a->nheads_k) * row : row;
+    const uint64_t head = a->kv_token_major ? row : static_cast<uint64_t>(a->total_k) * row;
     const uint64_t strides[2] = {tok, head};
     const uint32_t box[3] = {64, 64, 1};
     rc = encode_tensor_map_bf16(&map_kv, 3, a->kv_cache, dims, strides, box);
@@ -749,14 +759,14 @@ int tcgen05_prefill(const FwPrefillArgs* a, cudaStream_t stream) {
     if (rc != FW_OK) return rc;
     map_v = map_kv;
   }
-  cudaError_t err = cudaFuncSetAttribute(prefill_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         kSmemBytes);
+  auto kernel = d == 64 ? prefill_tcgen05_kernel<64> : prefill_tcgen05_kernel<128>;
+  cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
   if (err != cudaSuccess) {
     set_error("cudaFuncSetAttribute(%d bytes): %s", kSmemBytes, cudaGetErrorString(err));
     return FW_ERR_LAUNCH;
   }
   dim3 grid(a->nheads_k, max_items);
-  prefill_tcgen05_kernel<<<grid, 64 + kStreams * 128, kSmemBytes, stream>>>(map_q, map_kv, map_v, p);
+  kernel<<<grid, 64 + kStreams * 128, kSmemBytes, stream>>>(map_q, map_kv, map_v, p);
   err = cudaGetLastError();
   if (err != cudaSuccess) {
     set_error("tcgen05 prefill kernel launch: %s", cudaGetErrorString(err));

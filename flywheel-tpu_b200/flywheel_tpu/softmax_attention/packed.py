@@ -4,9 +4,9 @@ cu_seqlens_k branch of flash_attn_varlen_func.
 Mirrors flywheel_tpu/softmax_attention/prefill.py:62-341 (flash_attn_func) and
 :818-963 (packed flash_attn_varlen_func) of the reference project, forward
 only.  Both run the tcgen05 prefill kernel with K and V addressed by token row
-(fw_attention_packed).  Built: bfloat16, head_dim 128, nheads / nheads_k up to 128, causal / full / (left, right) window masks, softcap,
+(fw_attention_packed).  Built: bfloat16, head_dim 64 and 128, nheads / nheads_k up to 128, causal / full / (left, right) window masks, softcap,
 sinks, lse, fused RoPE on Q and K.  Not built (raise NotImplementedError):
-other head dims, head_dim_v != head_dim, heads_outer_fold, attention_chunk.
+head_dim 256 and others, head_dim_v != head_dim, heads_outer_fold, attention_chunk.
 """
 
 from __future__ import annotations
@@ -23,7 +23,7 @@ from flywheel_tpu.softmax_attention.inputs import (
     sinks_operand,
 )
 
-PACKED_HEAD_DIM = 128
+PACKED_HEAD_DIMS = (64, 128)
 MAX_PACKED_GROUP = 128
 
 
@@ -87,9 +87,9 @@ def parse_qkv(q, k, v, head_dim, token_major, expected_rank, layout):
     if head_dim_v != head_dim_qk:
         raise NotImplementedError(
             f"head_dim_v ({head_dim_v}) != head_dim ({head_dim_qk}) is not built.")
-    if head_dim_qk != PACKED_HEAD_DIM:
+    if head_dim_qk not in PACKED_HEAD_DIMS:
         raise NotImplementedError(
-            f"packed K/V attention is built for head_dim {PACKED_HEAD_DIM}; got {head_dim_qk}.")
+            f"packed K/V attention is built for head_dim {PACKED_HEAD_DIMS}; got {head_dim_qk}.")
     group = nheads // nheads_k
     if group > MAX_PACKED_GROUP:
         raise NotImplementedError(
@@ -155,7 +155,7 @@ def packed_attention_device(q, k, v, cu_seqlens_q, cu_seqlens_k, *, nheads, nhea
         v_packed=v.data_ptr(), cu_seqlens_q=cu_seqlens_q.data_ptr(), cu_seqlens_k=cu_seqlens_k.data_ptr(),
         sinks=_arrays.data_ptr(sinks), workspace=0, workspace_bytes=0, batch=batch, total_q=total_q,
         total_k=total_k, max_seqlen_q=int(max_seqlen_q), nheads=nheads, nheads_k=nheads_k,
-        head_dim=PACKED_HEAD_DIM, kv_dtype=_native.DTYPE_CODE["bfloat16"], causal=int(bool(causal)),
+        head_dim=q.shape[-1], kv_dtype=_native.DTYPE_CODE["bfloat16"], causal=int(bool(causal)),
         window_left=-1 if window_left is None else int(window_left), softmax_scale=float(softmax_scale),
         softcap=float(softcap), token_major=int(bool(token_major)), kv_token_major=int(bool(token_major)),
         sink_period=int(sink_period), window_right=int(window_right))
@@ -211,17 +211,17 @@ def flash_attn_func(
 ):
     """flash_attn.flash_attn_func, forward only.
 
-    Head-major (default): q (batch, nheads, seqlen_q, 128), k / v (batch,
-    nheads_k, seqlen_k, 128), out like q.  Token-major (token_major=True): the
-    heads fused into the last axis, (batch, seqlen, nheads * head_dim), with
-    head_dim=128.  All bfloat16; nheads / nheads_k up to 128.
+    Head-major (default): q (batch, nheads, seqlen_q, headdim), k / v (batch,
+    nheads_k, seqlen_k, headdim), out like q, headdim 64 or 128.  Token-major
+    (token_major=True): the heads fused into the last axis, (batch, seqlen,
+    nheads * head_dim), with head_dim= given.  All bfloat16; nheads / nheads_k up to 128.
     causal is bottom-right aligned: query i attends key j iff j <= i + seqlen_k -
     seqlen_q; window_size=(left, right) bounds the reach either side of that
     diagonal.  Rows with no
     reachable key return out = 0 and lse = -inf (or the sink).
     return_softmax_lse adds lse (batch, nheads, seqlen_q) float32, natural log.
     softcap > 0 applies tanh(scale * q k^T / softcap) * softcap.  rotary_cos /
-    rotary_sin: full-head RoPE tables (seqlen_ro, 64), q's dtype or float32; K
+    rotary_sin: full-head RoPE tables (seqlen_ro, headdim / 2), q's dtype or float32; K
     is rotated at positions 0..seqlen_k - 1 (unless rotary_k=False) and Q from
     seqlen_k - seqlen_q on.  learnable_sink: (nheads,) sink logits joining the
     softmax denominator.  Unlike the reference, seqlen_k needs no alignment.

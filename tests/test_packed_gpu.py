@@ -158,12 +158,40 @@ def test_two_sided_window(window, sq, sk):
     check(out.transpose(0, 2, 1, 3), lse, want, want_lse)
 
 
+@pytest.mark.parametrize("hq,hk", [(4, 4), (8, 2), (6, 1)])
+@pytest.mark.parametrize("sq,sk,causal", [(150, 150, True), (64, 333, True), (257, 100, False)])
+def test_head_dim_64(hq, hk, sq, sk, causal):
+    from flywheel_tpu import flash_attn_func, flash_attn_varlen_func
+    rng = np.random.default_rng(hq + sq)
+    d = 64
+    q, k, v = draw(rng, (2, hq, sq, d)), draw(rng, (2, hk, sk, d)), draw(rng, (2, hk, sk, d))
+    sinks = rng.standard_normal(hq).astype(np.float32)
+    angles = rng.uniform(0, 2 * np.pi, (max(sq, sk), d // 2)).astype(np.float32)
+    out, lse = flash_attn_func(q, k, v, causal=causal, softcap=12.0, learnable_sink=sinks, return_softmax_lse=True)
+    want, want_lse = oracle.dense_attention(
+        q.transpose(0, 2, 1, 3), k.transpose(0, 2, 1, 3), v.transpose(0, 2, 1, 3), causal=causal, softcap=12.0,
+        sinks=sinks)
+    check(out.transpose(0, 2, 1, 3), lse, want, want_lse)
+    if sq <= sk:
+        # packed varlen, token-major, with fused RoPE on q and k
+        cos, sin = np.cos(angles), np.sin(angles)
+        qt, kt, vt = (np.ascontiguousarray(x.transpose(0, 2, 1, 3)) for x in (q, k, v))
+        cu_q, cu_k = (np.arange(3) * sq).astype(np.int32), (np.arange(3) * sk).astype(np.int32)
+        out2 = flash_attn_varlen_func(
+            qt.reshape(2 * sq, hq * d), kt.reshape(2 * sk, hk * d), vt.reshape(2 * sk, hk * d), cu_q, cu_k, sq, sk,
+            causal=causal, head_dim=d, token_major=True, rotary_cos=cos, rotary_sin=sin)
+        q_rot = oracle.rotate_packed_q(qt.reshape(-1, hq, d), cos, sin, cu_q, np.full(2, sk))
+        k_rot = oracle.rotate_packed_q(kt.reshape(-1, hk, d), cos, sin, cu_k, np.full(2, sk))
+        want2, _ = oracle.packed_varlen_attention(q_rot, k_rot, vt.reshape(-1, hk, d), cu_q, cu_k, causal=causal)
+        np.testing.assert_allclose(out2.astype(np.float32).reshape(-1, hq, d), want2, **OUT_TOL)
+
+
 def test_rejections():
     from flywheel_tpu import flash_attn_func, flash_attn_varlen_func
     rng = np.random.default_rng(0)
     q, k = draw(rng, (1, 4, 8, D)), draw(rng, (1, 4, 8, D))
     with pytest.raises(NotImplementedError, match="head_dim"):
-        flash_attn_func(q[..., :64], k[..., :64], k[..., :64])
+        flash_attn_func(q[..., :32], k[..., :32], k[..., :32])
     with pytest.raises(NotImplementedError, match="up to 128"):
         flash_attn_func(draw(rng, (1, 130, 8, D)), k[:, :1], k[:, :1])
     with pytest.raises(ValueError, match="head_dim="):
