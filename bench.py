@@ -372,6 +372,55 @@ def bench_dense(ns, name, device):
                          "frac": tflops / tensor_peak if tensor_peak else None, "peak_kind": f"of {kind}"}}
 
 
+def bench_serving_prefill(ns, name, device):
+    """The reference's serving prefill scenario (docs/v7x.md:129-150 of the
+    reference): one 16K-token sequence prefilled in 1K chunks through
+    flash_attn_with_kvcache (append + attend, 16 calls), 32 q heads, head_dim
+    256, page 128 shuffled.  TFLOP/s over the 16 calls together."""
+    import torch
+    from flywheel_tpu import flash_attn_with_kvcache
+    hk = SERVING_PREFILL[name]["hk"]
+    hq, d, page, total, chunk = 32, 256, 128, 16384, 1024
+    pages = total // page
+    gen = torch.Generator(device=device)
+    gen.manual_seed(7)
+    pool = torch.zeros((pages + 8, page, 2 * hk, d), dtype=torch.bfloat16, device=device)
+    table = torch.randperm(pages + 8, generator=gen, device=device)[:pages].to(torch.int32)[None].contiguous()
+    q = torch.randn((1, chunk, hq, d), device=device).to(torch.bfloat16)
+    k = torch.randn((1, chunk, hk, d), device=device).to(torch.bfloat16)
+    v = torch.randn((1, chunk, hk, d), device=device).to(torch.bfloat16)
+    lens = [torch.tensor([i * chunk], dtype=torch.int32, device=device) for i in range(total // chunk)]
+
+    def sequence():
+        for cached in lens:
+            flash_attn_with_kvcache(q, pool, None, k, v, cache_seqlens=cached, block_table=table, causal=True)
+
+    flops = 4.0 * (total * (total + 1) / 2) * hq * d
+    steps = max(3, min(ns.steps, 10))
+    for _ in range(2):
+        sequence()
+    torch.cuda.synchronize()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(steps):
+        sequence()
+    end.record()
+    torch.cuda.synchronize()
+    ms = start.elapsed_time(end) / steps
+    _, tensor_peak, kind = measured_peaks()
+    tflops = flops / (ms * 1e-3) / 1e12
+    return {"metric": "serving_chunked_prefill_tflops", "config": {"workload": name, "nheads": hq, "nheads_k": hk,
+            "head_dim": d, "page_size": page, "sequence": total, "chunk": chunk,
+            "calls": "16 x flash_attn_with_kvcache (ragged append + chunked prefill)"},
+            "value": tflops, "unit": "TFLOP/s", "ms_per_sequence": ms, "steps": steps,
+            "algorithmic_flops_per_sequence": flops,
+            "roofline": {"bound": "tensor", "achieved": tflops, "peak": tensor_peak,
+                         "frac": tflops / tensor_peak if tensor_peak else None, "peak_kind": f"of {kind}"}}
+
+
+SERVING_PREFILL = {"serve-d256-prefill-gqa": dict(hk=4), "serve-d256-prefill-mha": dict(hk=32)}
+
+
 def bench_config(ns, name, device):
     """Secondary decode configurations (one JSON line each, device-resident):
     c1 = contiguous bf16 GQA decode (batch 8, 32:8 heads, capacity 2048, lengths
@@ -594,7 +643,7 @@ def main():
     parser.add_argument("--skip-cpu-baseline", action="store_true")
     parser.add_argument("--skip-e2e", action="store_true")
     parser.add_argument("--skip-prefill", action="store_true")
-    parser.add_argument("--config", choices=["c1", "c3", *SECONDARY_SHAPES, *DENSE_SHAPES], default=None,
+    parser.add_argument("--config", choices=["c1", "c3", *SECONDARY_SHAPES, *DENSE_SHAPES, *SERVING_PREFILL], default=None,
                         help="run one secondary decode configuration instead of the headline")
     parser.add_argument("--long-context", action="store_true",
                         help="run the single-request 128K-token decode split over the GPUs")
@@ -628,6 +677,9 @@ def main():
 
     if ns.config in DENSE_SHAPES:
         print(json.dumps(bench_dense(ns, ns.config, device)))
+        return
+    if ns.config in SERVING_PREFILL:
+        print(json.dumps(bench_serving_prefill(ns, ns.config, device)))
         return
     if ns.config:
         print(json.dumps(bench_config(ns, ns.config, device)))

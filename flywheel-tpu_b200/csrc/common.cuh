@@ -198,6 +198,12 @@ bool tcgen05_prefill_supported(const FwPrefillArgs* args);
 uint64_t tcgen05_prefill_workspace_bytes(const FwPrefillArgs* args);
 int tcgen05_prefill(const FwPrefillArgs* args, cudaStream_t stream);
 
+// The same at head_dim 256 (prefill_tcgen05_d256.cu); the three entry points
+// above hand over to these when head_dim is 256.
+bool tcgen05_d256_supported(const FwPrefillArgs* args);
+uint64_t tcgen05_d256_workspace_bytes(const FwPrefillArgs* args);
+int tcgen05_d256_prefill(const FwPrefillArgs* args, cudaStream_t stream);
+
 // Chunked prefill through the split-KV decode kernel (decode.cu).
 uint64_t splitkv_prefill_workspace_bytes(const FwPrefillArgs* args);
 int splitkv_prefill(const FwPrefillArgs* args, cudaStream_t stream);

@@ -19,7 +19,7 @@ static int check_prefill_args(const FwPrefillArgs* a) {
   }
   const bool packed_kv = a->block_table == nullptr && a->v_packed != nullptr;
   if (a->head_dim != 128 && a->head_dim != 256 && !(a->head_dim == 64 && packed_kv)) {
-    set_error("head_dim %d is not built; the paged paths serve head_dim 128 and 256, packed K/V 64 and 128.",
+    set_error("head_dim %d is not built; the paged paths serve head_dim 128 and 256, packed K/V also 64.",
               a->head_dim);
     return FW_ERR_UNSUPPORTED;
   }
@@ -382,7 +382,7 @@ static int check_packed_args(const FwPrefillArgs* a) {
     return FW_ERR_BAD_SHAPE;
   }
   if (!tcgen05_prefill_supported(a)) {
-    set_error("packed K/V attention is built for head_dim 64 and 128 and nheads / nheads_k up to 128;"
+    set_error("packed K/V attention is built for head_dim 64, 128 and 256 and nheads / nheads_k up to 128;"
               " got head_dim %d, nheads %d, nheads_k %d.", a->head_dim, a->nheads, a->nheads_k);
     return FW_ERR_UNSUPPORTED;
   }

@@ -1,0 +1,205 @@
+// Building blocks shared by the tcgen05 attention kernels: the launch
+// parameters, tcgen05 / tensor-memory PTX wrappers, shared-memory and
+// instruction descriptors, packed f32x2 arithmetic and the softmax passes.
+#pragma once
+
+#include <climits>
+#include <type_traits>
+
+#include "common.cuh"
+
+namespace fw {
+
+constexpr int kBM = 128;                   // query rows of one MMA tile (TMEM lanes)
+constexpr float kRescaleThreshold = 8.0f;  // log2 units a row max may drift before O is rescaled
+
+struct Tc05Params {
+  const int* items;  // 8 ints per query block: request, first q row, valid tokens, diagonal anchor, kv length
+  const int* block_table;
+  const float* k_descale;
+  const float* v_descale;
+  const float* sinks;
+  __nv_bfloat16* out;
+  float* lse;
+  int* status;
+  long long tok_stride, head_stride;  // elements, shared by q and out
+  long long num_pages;
+  int total_q, nheads, group, tpb, page_size, pages_per_seq;
+  int right, window_left;  // keys up to `right` past a row's diagonal are visible (0 = causal); -1 = no bound
+  float scale, softcap;
+  int packed;       // K and V are packed tensors addressed by token (no block table)
+  int sink_period;  // head h uses sinks[h % sink_period]; 0 = one sink per head
+};
+
+// ---------------------------------------------------------------- tcgen05 wrappers
+__device__ __forceinline__ void tmem_alloc(uint32_t* smem_slot, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_slot)),
+               "r"(cols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() {
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after() {
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+               : "memory");
+}
+// The MMAs are issued by one thread, so every instruction between two of them
+// is on the tensor pipe's critical path: descriptors are built once per tile
+// and advanced by adding a constant to their address field (low 32 bits never
+// carry: shared addresses stay below 2^18), and the accumulate predicate is
+// only materialised where it is not a constant.
+__device__ __forceinline__ uint64_t desc_advance(uint64_t desc, uint32_t bytes) { return desc + (bytes >> 4); }
+
+// D(tmem) (+)= A(tmem) * B(smem): A is 128 lanes x (K/2) 32-bit columns of packed bf16.
+__device__ __forceinline__ void tc_mma_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc,
+                                          uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t"
+      "}\n" ::"r"(tmem_d),
+      "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// D(tmem) (+)= A(smem) * B(smem), bf16 operands, f32 accumulate.
+__device__ __forceinline__ void tc_mma(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                       uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t"
+      "}\n" ::"r"(tmem_d),
+      "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,"
+      "%28,%29,%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]),
+        "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]),
+        "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,"
+      "%29,%30,%31,%32};" ::"r"(taddr),
+      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+      "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]),
+      "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]),
+      "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor, 128-byte swizzle, sm_100 version bits.
+// K-major operand: rows of 128 B, 8-row groups 1024 B apart (SBO); LBO unused.
+// MN-major operand: 64-element (128 B) runs along MN, next run LBO bytes away,
+// next group of 8 K-rows SBO bytes away.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((addr >> 4) & 0x3fff);
+  d |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3fff) << 16;
+  d |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3fff) << 32;
+  d |= 1ull << 46;  // descriptor version for sm_100
+  d |= 2ull << 61;  // SWIZZLE_128B
+  return d;
+}
+
+// kind::f16 instruction descriptor: f32 accumulate, bf16 A and B, M = 128.
+__host__ __device__ constexpr uint32_t instr_desc(int n, bool b_mn_major) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | (b_mn_major ? (1u << 16) : 0u) |
+         (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(kBM >> 4) << 24);
+}
+
+// Packed f32x2 arithmetic (two lanes per instruction on sm_100) and packed
+// bf16x2 max: they halve the issue slots the softmax spends around each exp2.
+__device__ __forceinline__ uint64_t pack2(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack2(uint64_t v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+  return r;
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ uint32_t max_bf16x2(uint32_t a, uint32_t b) {
+  uint32_t r;
+  asm("max.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+  return r;
+}
+
+// Pass 1 of the softmax over one 64-key row: optional softcap (scores become
+// log2-unit logits in place), optional mask (-inf in place), returns the row
+// max of what is left in `sr` (raw scores without a softcap).
+template <bool kSoftcap, bool kMask>
+__device__ __forceinline__ float transform_row(uint32_t (&sr)[2][32], float c1, float c2, int pos0, int kv_end,
+                                               int diag, int right, int window_left) {
+  float mx0 = -INFINITY, mx1 = -INFINITY;
+  const int hi = right >= 0 ? min(kv_end - 1, diag + right) : kv_end - 1;  // last visible key
+  const int lo = window_left >= 0 ? diag - window_left : INT_MIN;    // first visible key
+#pragma unroll
+  for (int c = 0; c < 2; ++c)
+#pragma unroll
+    for (int i = 0; i < 32; i += 2) {
+      float x0 = __uint_as_float(sr[c][i]), x1 = __uint_as_float(sr[c][i + 1]);
+      if constexpr (kSoftcap) {
+        x0 = accurate_tanh(x0 * c1) * c2;
+        x1 = accurate_tanh(x1 * c1) * c2;
+      }
+      if constexpr (kMask) {
+        const int key = pos0 + c * 32 + i;
+        if (key < lo || key > hi) x0 = -INFINITY;
+        if (key + 1 < lo || key + 1 > hi) x1 = -INFINITY;
+      }
+      if constexpr (kSoftcap || kMask) {
+        sr[c][i] = __float_as_uint(x0);
+        sr[c][i + 1] = __float_as_uint(x1);
+      }
+      mx0 = fmaxf(mx0, x0);
+      mx1 = fmaxf(mx1, x1);
+    }
+  return fmaxf(mx0, mx1);
+}
+
+// First waiter that gives up leaves where it was: status[1] = wait site,
+// status[2] = tile index, status[3] = item | kv head << 20.
+__device__ __forceinline__ void record_timeout(int* status, int site, int j) {
+  if (status != nullptr && atomicCAS(status + 1, 0, site) == 0) {
+    status[2] = j;
+    status[3] = static_cast<int>(blockIdx.y | (blockIdx.x << 20));
+  }
+}
+
+#define FW_WAIT(site, j, bar, parity) \
+  (mbar_wait_bounded(bar, parity, abort_flag) || (record_timeout(p.status, site, j), false))
+
+}  // namespace fw

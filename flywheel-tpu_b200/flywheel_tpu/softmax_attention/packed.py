@@ -4,9 +4,9 @@ cu_seqlens_k branch of flash_attn_varlen_func.
 Mirrors flywheel_tpu/softmax_attention/prefill.py:62-341 (flash_attn_func) and
 :818-963 (packed flash_attn_varlen_func) of the reference project, forward
 only.  Both run the tcgen05 prefill kernel with K and V addressed by token row
-(fw_attention_packed).  Built: bfloat16, head_dim 64 and 128, nheads / nheads_k up to 128, causal / full / (left, right) window masks, softcap,
+(fw_attention_packed).  Built: bfloat16, head_dim 64, 128 and 256, nheads / nheads_k up to 128, causal / full / (left, right) window masks, softcap,
 sinks, lse, fused RoPE on Q and K.  Not built (raise NotImplementedError):
-head_dim 256 and others, head_dim_v != head_dim, heads_outer_fold, attention_chunk.
+other head dims, head_dim_v != head_dim, heads_outer_fold, attention_chunk.
 """
 
 from __future__ import annotations
@@ -23,7 +23,7 @@ from flywheel_tpu.softmax_attention.inputs import (
     sinks_operand,
 )
 
-PACKED_HEAD_DIMS = (64, 128)
+PACKED_HEAD_DIMS = (64, 128, 256)
 MAX_PACKED_GROUP = 128
 
 
@@ -212,7 +212,7 @@ def flash_attn_func(
     """flash_attn.flash_attn_func, forward only.
 
     Head-major (default): q (batch, nheads, seqlen_q, headdim), k / v (batch,
-    nheads_k, seqlen_k, headdim), out like q, headdim 64 or 128.  Token-major
+    nheads_k, seqlen_k, headdim), out like q, headdim 64, 128 or 256.  Token-major
     (token_major=True): the heads fused into the last axis, (batch, seqlen,
     nheads * head_dim), with head_dim= given.  All bfloat16; nheads / nheads_k up to 128.
     causal is bottom-right aligned: query i attends key j iff j <= i + seqlen_k -

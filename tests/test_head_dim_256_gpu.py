@@ -100,10 +100,12 @@ def test_contiguous_pair():
     np.testing.assert_allclose(lse, want_lse, **LSE_TOL)
 
 
-@pytest.mark.parametrize("hq,hk", [(32, 4), (8, 8)])
+@pytest.mark.parametrize("kernel", ["tcgen05", "splitkv"])
+@pytest.mark.parametrize("hq,hk", [(32, 4), (8, 8), (6, 2)])
 @pytest.mark.parametrize("rotary", [False, True])
-def test_chunked_prefill(hq, hk, rotary):
+def test_chunked_prefill(hq, hk, rotary, kernel, monkeypatch):
     from flywheel_tpu import flash_attn_varlen_func
+    monkeypatch.setenv("FLYWHEEL_PREFILL_KERNEL", kernel)
     rng = np.random.default_rng(23)
     page = 128
     prefixes, chunks = (0, 300, 1000, 77), (200, 64, 130, 1)
@@ -128,11 +130,13 @@ def test_chunked_prefill(hq, hk, rotary):
         cos, sin = np.cos(angles), np.sin(angles)
         kwargs = dict(rotary_cos=cos, rotary_sin=sin, rotary_k=False)
         q_ref = oracle.rotate_packed_q(q, cos, sin, cu, seqused)
+    sinks = rng.standard_normal(hq).astype(np.float32)
     out, lse = flash_attn_varlen_func(
         np.ascontiguousarray(q.transpose(1, 0, 2)), to_cuda(pool), None, cu, None, int(max(chunks)),
-        int(seqused.max()), causal=True, return_softmax_lse=True, block_table=table, seqused_k=seqused,
-        **kwargs)
-    want, want_lse = oracle.ragged_paged_attention(q_ref, pool, cu, seqused, table, nheads_k=hk, causal=True)
+        int(seqused.max()), causal=True, window_size=(400, 0), softcap=20.0, learnable_sink=sinks,
+        return_softmax_lse=True, block_table=table, seqused_k=seqused, **kwargs)
+    want, want_lse = oracle.ragged_paged_attention(q_ref, pool, cu, seqused, table, nheads_k=hk, causal=True,
+                                                   window_left=400, softcap=20.0, sinks=sinks)
     end = int(cu[-1])
     np.testing.assert_allclose(out.astype(np.float32).transpose(1, 0, 2)[:end], want[:end], **TOL["bf16"])
     np.testing.assert_allclose(lse[:, :end], want_lse[:, :end], **LSE_TOL)

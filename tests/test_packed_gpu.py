@@ -158,12 +158,12 @@ def test_two_sided_window(window, sq, sk):
     check(out.transpose(0, 2, 1, 3), lse, want, want_lse)
 
 
+@pytest.mark.parametrize("d", [64, 256])
 @pytest.mark.parametrize("hq,hk", [(4, 4), (8, 2), (6, 1)])
-@pytest.mark.parametrize("sq,sk,causal", [(150, 150, True), (64, 333, True), (257, 100, False)])
-def test_head_dim_64(hq, hk, sq, sk, causal):
+@pytest.mark.parametrize("sq,sk,causal", [(150, 150, True), (64, 333, True), (257, 100, False), (1, 700, True)])
+def test_other_head_dims(d, hq, hk, sq, sk, causal):
     from flywheel_tpu import flash_attn_func, flash_attn_varlen_func
-    rng = np.random.default_rng(hq + sq)
-    d = 64
+    rng = np.random.default_rng(hq + sq + d)
     q, k, v = draw(rng, (2, hq, sq, d)), draw(rng, (2, hk, sk, d)), draw(rng, (2, hk, sk, d))
     sinks = rng.standard_normal(hq).astype(np.float32)
     angles = rng.uniform(0, 2 * np.pi, (max(sq, sk), d // 2)).astype(np.float32)
