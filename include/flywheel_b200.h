@@ -277,7 +277,7 @@ int fw_prefill_paged(const FwPrefillArgs* args, void* stream);
  * (batch, nheads, seqlen, head_dim) layout is this call with batch * nheads
  * heads over a single sequence, sink_period = nheads).  Causal and left-window
  * masks are bottom-right aligned per sequence (causal = 1 is a right bound of
- * 0, window_right a positive one).  bf16, head_dim 64 or 128, nheads /
+ * 0, window_right a positive one).  bf16, head_dim 64, 128 or 256, nheads /
  * nheads_k up to 128.  block_table, seqused_k, num_active and the descales must be NULL.
  * Rows past cu_seqlens_q[batch] return out 0, lse -inf.  With rotary tables q
  * (and K when rotary_k = 1) are rotated into scratch copies first.
