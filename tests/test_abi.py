@@ -90,3 +90,46 @@ def test_host_api_rejections_follow_the_reference():
         flash_attn_varlen_func(np.zeros((4, 5, 128), bf16), pool, None,
                                np.array([0, 2, 5], np.int32), None, 3, 64, block_table=table,
                                seqused_k=np.array([3, 4], np.int32), window_size=(-1, 5))
+
+
+def test_exchange_and_packed_entry_points_validate_without_a_gpu():
+    from flywheel_tpu.softmax_attention import _native
+    lib = _native.library()
+    # exchange buffer: header + 2 parities x world slots of rows * (d + 1) floats, slots 16-byte aligned
+    assert lib.fw_exchange_buffer_bytes(4, 64, 128) == 4096 + 2 * 4 * 64 * 129 * 4
+    assert lib.fw_exchange_buffer_bytes(2, 6, 128) == 4096 + 2 * 2 * ((6 * 129 + 3) // 4 * 4) * 4
+    assert lib.fw_exchange_buffer_bytes(0, 64, 128) == 0 and "world" in _native.last_error()
+    assert lib.fw_exchange_buffer_bytes(2, 64, 96) == 0
+    swap = _native.FwExchangeArgs(world=2, rank=0, rows=64, nheads=64, head_dim=128)
+    with pytest.raises(ValueError, match="must not be NULL"):
+        _native.check(lib.fw_state_exchange_merge(ctypes.byref(swap), None))
+    peers = (ctypes.c_void_p * 2)(1, 0)
+    swap = _native.FwExchangeArgs(peer_buffers=ctypes.cast(peers, ctypes.c_void_p), state_out=1, state_lse=1,
+                                  out=1, world=2, rank=3, rows=64, nheads=64, head_dim=128)
+    with pytest.raises(ValueError, match="rank inside"):
+        _native.check(lib.fw_state_exchange_merge(ctypes.byref(swap), None))
+    swap.rank = 1
+    with pytest.raises(ValueError, match=r"peer_buffers\[1\]"):
+        _native.check(lib.fw_state_exchange_merge(ctypes.byref(swap), None))
+
+    packed = _native.FwPrefillArgs(batch=1, total_q=8, total_k=8, nheads=4, nheads_k=4, head_dim=128,
+                                   kv_cache=1, v_packed=1, cu_seqlens_q=1, cu_seqlens_k=1, q=1, out=1,
+                                   softmax_scale=0.1)
+    assert lib.fw_attention_packed_workspace_bytes(ctypes.byref(packed)) > 0
+    packed.head_dim = 96
+    with pytest.raises(NotImplementedError, match="head_dim"):
+        _native.check(lib.fw_attention_packed(ctypes.byref(packed), None))
+    packed.head_dim, packed.block_table = 128, 1
+    with pytest.raises(ValueError, match="paged cache"):
+        _native.check(lib.fw_attention_packed(ctypes.byref(packed), None))
+    packed.block_table, packed.kv_dtype = 0, 1
+    with pytest.raises(NotImplementedError, match="bfloat16"):
+        _native.check(lib.fw_attention_packed(ctypes.byref(packed), None))
+    packed.kv_dtype, packed.nheads = 0, 4 * 130
+    with pytest.raises(NotImplementedError, match="up to 128"):
+        _native.check(lib.fw_attention_packed(ctypes.byref(packed), None))
+    # head_dim 64 is a packed-K/V size only
+    paged = _native.FwPrefillArgs(batch=1, total_q=8, nheads=4, nheads_k=4, head_dim=64, block_table=1,
+                                  page_size=64, pages_per_seq=1, num_pages=1, softmax_scale=0.1)
+    assert lib.fw_prefill_workspace_bytes(ctypes.byref(paged)) == 0
+    assert "head_dim 64" in _native.last_error()
