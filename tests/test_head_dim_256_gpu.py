@@ -164,3 +164,19 @@ def test_state_merge():
     torch.cuda.synchronize()
     np.testing.assert_allclose(out.float().cpu().numpy(), want, **TOL["bf16"])
     np.testing.assert_allclose(lse.cpu().numpy(), want_lse, **LSE_TOL)
+
+
+def test_multi_token_kvcache_call_appends_then_prefills():
+    """(batch, seqlen_q > fold limit) goes through the ragged append and the
+    head_dim 256 tensor-core prefill kernel."""
+    from flywheel_tpu import flash_attn_with_kvcache
+    from flywheel_tpu.softmax_attention import _arrays
+    hq, hk, sq = 8, 2, 100
+    q, pool, k, v, lens, table, kd, vd = paged_inputs(31, (0, 77, 300), sq, hq, hk, 128, oracle.BF16)
+    pool_t = to_cuda(pool)
+    out, lse, _ = flash_attn_with_kvcache(q, pool_t, None, k, v, cache_seqlens=lens, block_table=table,
+                                          causal=True, return_softmax_lse=True)
+    want, want_lse, want_pool = oracle.kvcache_paged(q, pool, k, v, lens, table, nheads_k=hk, causal=True)
+    np.testing.assert_array_equal(_arrays.to_host_numpy(pool_t).view(np.uint16), want_pool.view(np.uint16))
+    np.testing.assert_allclose(out.astype(np.float32), want, **TOL["bf16"])
+    np.testing.assert_allclose(lse, want_lse, **LSE_TOL)
