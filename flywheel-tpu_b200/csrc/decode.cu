@@ -627,7 +627,7 @@ combine_kernel(const CombineParams cp) {
   constexpr int NB = D / 128;  // a lane owns four columns of every 128-column block
   const DecodeParams& p = cp.d;
   __shared__ float4 red_acc[kWarps][NB][32];
-  __shared__ float red_den[kWarps];
+  __shared__ float red_den[kWarps], red_max[kWarps];
   const int b = blockIdx.x;
   const int warp_in_block = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int sub = warp_in_block % WPR, warp = warp_in_block / WPR;
@@ -673,79 +673,84 @@ combine_kernel(const CombineParams cp) {
     const int t = row / p.nheads, hq = row - t * p.nheads;
     if (t >= sp.q_valid) break;  // rows are token-major: the rest are not real query rows either
 
+    // One pass: every segment is folded into a running (max, sum, acc) state,
+    // so a row costs one round of loads, not a max pass and then a sum pass.
     float m_max = -INFINITY;
-    for (int c = c_lo + lane; c <= c_hi; c += 32) {
+    float4 acc[NB];
+#pragma unroll
+    for (int nb = 0; nb < NB; ++nb) acc[nb] = make_float4(0.f, 0.f, 0.f, 0.f);
+    float den = 0.f;
+#pragma unroll 4
+    for (int c = c_lo + sub; c <= c_hi; c += WPR) {
       bool has_tiles = true;
       if (all_live) {
       } else if (few) {
-        has_tiles = (live >> lane) & 1u;
+        has_tiles = (live >> (c - c_lo)) & 1u;
       } else {
         int f0, f1;
         cta_range(total_tiles, p.ncta, c, f0, f1);
         has_tiles = f1 > f0;
       }
-      if (!has_tiles) continue;
       const long long prow = (static_cast<long long>(b) + c) * rq + row;
-      m_max = fmaxf(m_max, p.part_ml[prow * 2]);
-    }
+      const float2 ml = *reinterpret_cast<const float2*>(p.part_ml + prow * 2);
+      float4 o[NB];
 #pragma unroll
-    for (int off = 16; off; off >>= 1) m_max = fmaxf(m_max, __shfl_xor_sync(0xffffffffu, m_max, off));
-
-    float4 acc[NB];
+      for (int nb = 0; nb < NB; ++nb)
+        o[nb] = *reinterpret_cast<const float4*>(p.part_o + prow * D + nb * 128 + lane * 4);
+      const float x = has_tiles ? ml.x : -INFINITY;  // a segment that saw no key carries -inf
+      const float m_new = fmaxf(m_max, x);
+      const float base = m_new == -INFINITY ? 0.f : m_new;
+      const float keep = fast_exp2(m_max - base), w = fast_exp2(x - base);  // 2^-inf = 0
+      den = den * keep + (w == 0.f ? 0.f : ml.y * w);
 #pragma unroll
-    for (int nb = 0; nb < NB; ++nb) acc[nb] = make_float4(0.f, 0.f, 0.f, 0.f);
-    float den = 0.f;
-    if (m_max != -INFINITY) {
-      // Branch-free body so the loads of several segments are in flight at once.
-#pragma unroll 4
-      for (int c = c_lo + sub; c <= c_hi; c += WPR) {
-        bool has_tiles = true;
-        if (all_live) {
-        } else if (few) {
-          has_tiles = (live >> (c - c_lo)) & 1u;
-        } else {
-          int f0, f1;
-          cta_range(total_tiles, p.ncta, c, f0, f1);
-          has_tiles = f1 > f0;
-        }
-        const long long prow = (static_cast<long long>(b) + c) * rq + row;
-        const float2 ml = *reinterpret_cast<const float2*>(p.part_ml + prow * 2);
-        float4 o[NB];
-#pragma unroll
-        for (int nb = 0; nb < NB; ++nb)
-          o[nb] = *reinterpret_cast<const float4*>(p.part_o + prow * D + nb * 128 + lane * 4);
-        const float w = (has_tiles && ml.x != -INFINITY) ? fast_exp2(ml.x - m_max) : 0.f;
-        den += w == 0.f ? 0.f : ml.y * w;
-#pragma unroll
-        for (int nb = 0; nb < NB; ++nb) {
-          acc[nb].x += w == 0.f ? 0.f : o[nb].x * w;
-          acc[nb].y += w == 0.f ? 0.f : o[nb].y * w;
-          acc[nb].z += w == 0.f ? 0.f : o[nb].z * w;
-          acc[nb].w += w == 0.f ? 0.f : o[nb].w * w;
-        }
+      for (int nb = 0; nb < NB; ++nb) {
+        acc[nb].x = acc[nb].x * keep + (w == 0.f ? 0.f : o[nb].x * w);
+        acc[nb].y = acc[nb].y * keep + (w == 0.f ? 0.f : o[nb].y * w);
+        acc[nb].z = acc[nb].z * keep + (w == 0.f ? 0.f : o[nb].z * w);
+        acc[nb].w = acc[nb].w * keep + (w == 0.f ? 0.f : o[nb].w * w);
       }
+      m_max = m_new;
     }
     if constexpr (WPR > 1) {
       // A block of the wide form holds one row, so its warps take every branch
-      // of this loop together.
+      // of this loop together.  Their states merge like segments do.
       __syncthreads();
 #pragma unroll
       for (int nb = 0; nb < NB; ++nb) red_acc[warp_in_block][nb][lane] = acc[nb];
-      if (lane == 0) red_den[warp_in_block] = den;
+      if (lane == 0) {
+        red_den[warp_in_block] = den;
+        red_max[warp_in_block] = m_max;
+      }
       __syncthreads();
       if (sub != 0) continue;
+      float top = m_max;
+#pragma unroll
+      for (int w = 1; w < WPR; ++w) top = fmaxf(top, red_max[warp * WPR + w]);
+      const float base = top == -INFINITY ? 0.f : top;
+      const float keep = fast_exp2(m_max - base);
+      den *= keep;
+#pragma unroll
+      for (int nb = 0; nb < NB; ++nb) {
+        acc[nb].x *= keep;
+        acc[nb].y *= keep;
+        acc[nb].z *= keep;
+        acc[nb].w *= keep;
+      }
 #pragma unroll
       for (int w = 1; w < WPR; ++w) {
+        const float scale = fast_exp2(red_max[warp * WPR + w] - base);
+        if (scale == 0.f) continue;
 #pragma unroll
         for (int nb = 0; nb < NB; ++nb) {
           const float4 o = red_acc[warp * WPR + w][nb][lane];
-          acc[nb].x += o.x;
-          acc[nb].y += o.y;
-          acc[nb].z += o.z;
-          acc[nb].w += o.w;
+          acc[nb].x += o.x * scale;
+          acc[nb].y += o.y * scale;
+          acc[nb].z += o.z * scale;
+          acc[nb].w += o.w * scale;
         }
-        den += red_den[warp * WPR + w];
+        den += red_den[warp * WPR + w] * scale;
       }
+      m_max = top;
     }
 
     if (cp.partial_out != nullptr) {

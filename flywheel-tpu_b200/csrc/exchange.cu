@@ -12,7 +12,8 @@
 //
 // Layout of a rank's exchange buffer (same on every rank, cudaMalloc'ed here so
 // its IPC handle can be opened by the peers):
-//   [0, 256)            step counter and bookkeeping of this rank (local use)
+//   [0, 256)            this rank's own bookkeeping: step counter, merge blocks done,
+//                       scatter blocks done per peer
 //   [256, 256 + 4 W)    flags[r]: last epoch rank r has delivered
 //   [4096, ...)         2 x W slots of rows * (head_dim + 1) floats: [o | lse],
 //                       indexed [epoch parity][source rank]
@@ -57,19 +58,30 @@ __device__ __forceinline__ float* slot_of(uint8_t* buffer, uint32_t epoch, int w
          (static_cast<uint64_t>(epoch & 1) * world + source) * slot_floats;
 }
 
-// Block p delivers this rank's state to rank p and then raises its flag there.
-__global__ void __launch_bounds__(256) scatter_state_kernel(const ExchangeParams p) {
+constexpr int kScatterBlocks = 8;  // blocks that share the copy to one peer
+
+// Blocks (p, 0 .. kScatterBlocks) deliver this rank's state to rank p; the last
+// of them to finish raises this rank's flag there.
+__global__ void __launch_bounds__(128) scatter_state_kernel(const ExchangeParams p) {
   const int peer = blockIdx.x;
-  const uint32_t epoch = *reinterpret_cast<const uint32_t*>(p.peers[p.rank]) + 1;
+  uint32_t* header = reinterpret_cast<uint32_t*>(p.peers[p.rank]);
+  const uint32_t epoch = header[0] + 1;
   float* dst = slot_of(p.peers[peer], epoch, p.world, p.rank, p.slot_floats);
   const int n_out = p.rows * p.head_dim;
-  for (int i = threadIdx.x * 4; i < n_out; i += blockDim.x * 4)
+  const int first = (blockIdx.y * blockDim.x + threadIdx.x) * 4, stride = gridDim.y * blockDim.x * 4;
+  for (int i = first; i < n_out; i += stride)
     *reinterpret_cast<float4*>(dst + i) = *reinterpret_cast<const float4*>(p.state_out + i);
-  for (int i = threadIdx.x; i < p.rows; i += blockDim.x) dst[n_out + i] = p.state_lse[i];
+  if (blockIdx.y == 0)
+    for (int i = threadIdx.x; i < p.rows; i += blockDim.x) dst[n_out + i] = p.state_lse[i];
   __syncthreads();
   if (threadIdx.x == 0) {
-    __threadfence_system();
-    store_release_sys(reinterpret_cast<uint32_t*>(p.peers[peer] + 256) + p.rank, epoch);
+    __threadfence_system();  // this block's stores are out before it is counted
+    uint32_t* arrived = header + 2 + peer;
+    if (atomicAdd(arrived, 1u) == gridDim.y - 1) {
+      *arrived = 0;
+      __threadfence_system();
+      store_release_sys(reinterpret_cast<uint32_t*>(p.peers[peer] + 256) + p.rank, epoch);
+    }
   }
 }
 
@@ -262,7 +274,7 @@ extern "C" int fw_state_exchange_merge(const FwExchangeArgs* a, void* stream_ptr
   p.lse_token_stride = a->lse_token_stride;
   p.slot_floats = slot_floats_of(a->rows, a->head_dim);
   cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
-  scatter_state_kernel<<<a->world, 256, 0, stream>>>(p);
+  scatter_state_kernel<<<dim3(a->world, kScatterBlocks), 128, 0, stream>>>(p);
   gather_merge_kernel<<<(a->rows + 3) / 4, 128, 0, stream>>>(p);
   cudaError_t err = cudaGetLastError();
   if (err != cudaSuccess) {

@@ -103,7 +103,7 @@ class ShardedDecoder:
         self.peers = None
         if self.exchange not in ("p2p", "nccl"):
             raise ValueError(f"exchange must be 'p2p' or 'nccl'; got {self.exchange!r}.")
-        if self.exchange == "p2p":
+        if self.exchange == "p2p" and self.world > 1:
             self._open_exchange_buffers()
 
     def _open_exchange_buffers(self):
@@ -187,11 +187,15 @@ class ShardedDecoder:
         rows, d = self.nheads, self.head_dim
         partial_out = self.state[: rows * d]
         partial_lse = self.state[rows * d:]
+        alone = self.world == 1   # one rank holds every page: no partial state, no exchange
         args = _native.FwDecodeArgs(
-            q=q.data_ptr(), out=0, lse=0, kv_cache=self.pool.data_ptr(), v_cache=0,
+            q=q.data_ptr(), out=self.out.data_ptr() if alone else 0, lse=self.lse.data_ptr() if alone else 0,
+            kv_cache=self.pool.data_ptr(), v_cache=0,
             k_new=k.data_ptr() if appends else 0, v_new=v.data_ptr() if appends else 0,
             cache_seqlens=self.local_len.data_ptr(), block_table=self.table.data_ptr(),
-            partial_out=partial_out.data_ptr(), partial_lse=partial_lse.data_ptr(),
+            sinks=_arrays.data_ptr(self.sinks) if alone else 0,
+            partial_out=0 if alone else partial_out.data_ptr(),
+            partial_lse=0 if alone else partial_lse.data_ptr(),
             num_pages=self.pool.shape[0], page_size=self.page_size,
             pages_per_seq=self.table.shape[1], batch=1, seqlen_q=1, nheads=self.nheads,
             nheads_k=self.nheads_k, head_dim=d,
@@ -206,6 +210,8 @@ class ShardedDecoder:
             self.scratch = torch.zeros(nbytes, dtype=torch.uint8, device=self.device)
         args.workspace, args.workspace_bytes = self.scratch.data_ptr(), self.scratch.numel()
         _native.check(self.lib.fw_decode_kvcache(ctypes.byref(args), stream))
+        if alone:
+            return self.out, self.lse
         if self.exchange == "p2p":
             if self.peers is None:
                 raise RuntimeError("the exchange buffers were closed.")
