@@ -23,6 +23,15 @@ is one decode call over the whole batch.
 With N > 1 (torchrun) every rank runs its own copy of the workload with its own
 seed (requests shard with no communication); value is the sum of bytes over
 ranks divided by the slowest rank's time.
+
+Other workloads, one JSON line each (device-resident inputs):
+    --config c1 | c3                     contiguous bf16 decode; paged fp8 verify window
+    --config serve-d256-gqa | serve-d256-mha | gate-decode | gate-verify
+                                         the reference's serving / perf-gate decode shapes
+    --config dense-causal-8k | dense-causal-32k      flash_attn_func, causal
+    --config serve-d256-prefill-gqa | -mha           16K sequence in 1K chunks, head_dim 256
+    --prefill-only [FW_PREFILL_POOL=e4m3]            the chunked-prefill workload alone
+    --long-context [FLYWHEEL_EXCHANGE=p2p|nccl]      one 128K-token request split over the GPUs
 """
 
 from __future__ import annotations
