@@ -30,7 +30,7 @@ Other workloads, one JSON line each (device-resident inputs):
                                          the reference's serving / perf-gate decode shapes
     --config dense-causal-8k | dense-causal-32k      flash_attn_func, causal
     --config serve-d256-prefill-gqa | -mha           16K sequence in 1K chunks, head_dim 256
-    --prefill-only [FW_PREFILL_POOL=e4m3]            the chunked-prefill workload alone
+    --prefill-only [FW_PREFILL_POOL=e4m3] [FW_PREFILL_HEAD_DIM=256]   the chunked-prefill workload alone
     --long-context [FLYWHEEL_EXCHANGE=p2p|nccl]      one 128K-token request split over the GPUs
 """
 
@@ -143,6 +143,7 @@ def build_workload(seed, device):
 
 
 PF_BATCH, PF_HQ, PF_HK = 16, 32, 8
+PF_D = int(os.environ.get("FW_PREFILL_HEAD_DIM", "128"))  # 256 for the head_dim 256 variant of the workload
 
 
 def build_prefill_workload(seed, device):
@@ -159,7 +160,7 @@ def build_prefill_workload(seed, device):
     table, pool_pages = workloads.paged_table(rng, seqused, 0, PAGE, slack=0.10)
     gen = torch.Generator(device=device)
     gen.manual_seed(1000 + seed)
-    pool = torch.randn((pool_pages, PAGE, 2 * PF_HK, D), generator=gen, device=device,
+    pool = torch.randn((pool_pages, PAGE, 2 * PF_HK, PF_D), generator=gen, device=device,
                        dtype=torch.float32).to(torch.bfloat16)
     # FW_PREFILL_POOL=e4m3 re-types the pool for the fp8 variant of the workload
     # (same shapes; per-tensor descale 5.5 / 448).
@@ -169,10 +170,10 @@ def build_prefill_workload(seed, device):
         descale = torch.tensor([5.5 / 448.0], dtype=torch.float32, device=device)
     cu = np.concatenate(([0], np.cumsum(chunk))).astype(np.int32)
     total_q = int(cu[-1])
-    q_host = torch.randn((PF_HQ, total_q, D), dtype=torch.float32).to(torch.bfloat16).pin_memory()
+    q_host = torch.randn((PF_HQ, total_q, PF_D), dtype=torch.float32).to(torch.bfloat16).pin_memory()
     return {"pool": pool, "descale": descale, "q_host": q_host, "q": q_host.to(device), "cu": cu, "seqused": seqused,
             "table": table, "prefix": prefix, "chunk": chunk, "total_q": total_q,
-            "flops": workloads.prefill_flops(prefix, chunk, PF_HQ, D),
+            "flops": workloads.prefill_flops(prefix, chunk, PF_HQ, PF_D),
             "cu_dev": torch.from_numpy(cu).to(device), "seqused_dev": torch.from_numpy(seqused).to(device),
             "table_dev": torch.from_numpy(table).to(device)}
 
@@ -186,9 +187,9 @@ def make_prefill_call(work, device):
         cu_seqlens_q=work["cu_dev"].data_ptr(), seqused_k=work["seqused_dev"].data_ptr(),
         block_table=work["table_dev"].data_ptr(), num_pages=work["pool"].shape[0], page_size=PAGE,
         pages_per_seq=work["table_dev"].shape[1], batch=PF_BATCH, total_q=work["total_q"],
-        max_seqlen_q=int(work["chunk"].max()), nheads=PF_HQ, nheads_k=PF_HK, head_dim=D,
+        max_seqlen_q=int(work["chunk"].max()), nheads=PF_HQ, nheads_k=PF_HK, head_dim=PF_D,
         kv_dtype=0 if work["descale"] is None else 1,
-        causal=1, window_left=-1, softmax_scale=D ** -0.5, softcap=0.0, token_major=0)
+        causal=1, window_left=-1, softmax_scale=PF_D ** -0.5, softcap=0.0, token_major=0)
     if work["descale"] is not None:
         args.k_descale = args.v_descale = work["descale"].data_ptr()
     lib = _native.library()
@@ -261,7 +262,7 @@ def bench_prefill(ns, device, rank, world, barrier):
             np.arange(len(pages), dtype=np.int32)[None], nheads_k=PF_HK, causal=True)
         cpu_s = time.perf_counter() - t0
         got = out[:, lo:hi].float().cpu().numpy().transpose(1, 0, 2)
-        flops_r = 4 * int(work["chunk"][r]) * (int(work["prefix"][r]) + (int(work["chunk"][r]) + 1) / 2) * PF_HQ * D
+        flops_r = 4 * int(work["chunk"][r]) * (int(work["prefix"][r]) + (int(work["chunk"][r]) + 1) / 2) * PF_HQ * PF_D
         check = {"max_abs_err_vs_cpu": float(np.abs(got - want).max()),
                  "cpu_tflops": flops_r / cpu_s / 1e12, "cpu_sample": f"request {r} of {PF_BATCH}, {cpu_s:.2f} s"}
     return {"ms": ms, "flops": work["flops"], "e2e_ms": e2e_ms, "total_q": work["total_q"],
