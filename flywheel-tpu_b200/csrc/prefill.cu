@@ -210,7 +210,7 @@ static constexpr int kGatherMinChunk = 256;
 enum class PrefillRoute { kTensorCore, kGatherTensorCore, kSplitKv };
 
 static bool gather_route_possible(const FwPrefillArgs* a) {
-  if (a->head_dim != 128 || a->block_table == nullptr || a->page_size <= 0 || a->pages_per_seq <= 0) return false;
+  if (a->block_table == nullptr || a->page_size <= 0 || a->pages_per_seq <= 0) return false;
   if (a->page_size % 16) return false;  // the split-KV kernel reports the shape error
   FwPrefillArgs as_packed = *a;
   as_packed.kv_dtype = FW_DTYPE_BF16;

@@ -180,3 +180,39 @@ def test_multi_token_kvcache_call_appends_then_prefills():
     np.testing.assert_array_equal(_arrays.to_host_numpy(pool_t).view(np.uint16), want_pool.view(np.uint16))
     np.testing.assert_allclose(out.astype(np.float32), want, **TOL["bf16"])
     np.testing.assert_allclose(lse, want_lse, **LSE_TOL)
+
+
+@pytest.mark.parametrize("kernel", ["tcgen05", "splitkv"])
+@pytest.mark.parametrize("kind", ["e4m3", "e5m2"])
+def test_chunked_prefill_fp8_pool(kind, kernel, monkeypatch):
+    """fp8 pools at head_dim 256: widened into bf16 scratch and run on the
+    tensor-core kernel, or read in place by the split-KV kernel."""
+    from flywheel_tpu import flash_attn_varlen_func
+    monkeypatch.setenv("FLYWHEEL_PREFILL_KERNEL", kernel)
+    dtype = oracle.E4M3 if kind == "e4m3" else oracle.E5M2
+    rng = np.random.default_rng(29)
+    hq, hk, page = 8, 2, 64
+    prefixes, chunks = (0, 500, 90), (300, 70, 129)
+    cu = np.concatenate(([0], np.cumsum(chunks))).astype(np.int32)
+    seqused = (np.asarray(prefixes) + np.asarray(chunks)).astype(np.int32)
+    pages_b = [-(-int(n) // page) for n in seqused]
+    n_pages = sum(pages_b) + 1
+    perm = rng.permutation(n_pages)
+    table = np.full((len(chunks), max(pages_b)), -1, np.int32)
+    cursor = 0
+    for b, n in enumerate(pages_b):
+        table[b, :n] = perm[cursor:cursor + n]
+        cursor += n
+    kd, vd = 2.0 ** -3, 2.0 ** -2
+    k_pages = oracle.quantize_per_tensor(rng.standard_normal((n_pages, page, hk, D), dtype=np.float32), dtype, descale=kd)[0]
+    v_pages = oracle.quantize_per_tensor(rng.standard_normal((n_pages, page, hk, D), dtype=np.float32), dtype, descale=vd)[0]
+    pool = oracle.merge_kv_heads(k_pages, v_pages)
+    q = rng.standard_normal((int(cu[-1]), hq, D), dtype=np.float32).astype(oracle.BF16)
+    out, lse = flash_attn_varlen_func(
+        np.ascontiguousarray(q.transpose(1, 0, 2)), to_cuda(pool), None, cu, None, int(max(chunks)),
+        int(seqused.max()), causal=True, return_softmax_lse=True, block_table=table, seqused_k=seqused,
+        k_descale=kd, v_descale=vd, nheads_k=hk)
+    want, want_lse = oracle.ragged_paged_attention(q, pool, cu, seqused, table, nheads_k=hk, causal=True,
+                                                   k_descale=kd, v_descale=vd)
+    np.testing.assert_allclose(out.astype(np.float32).transpose(1, 0, 2), want, **TOL["fp8"])
+    np.testing.assert_allclose(lse, want_lse, **LSE_TOL)
