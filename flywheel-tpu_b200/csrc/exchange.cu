@@ -40,7 +40,7 @@ struct ExchangeParams {
   int* status;
   int world, rank, rows, nheads, head_dim;
   int lse_head_stride, lse_token_stride;
-  uint64_t slot_floats;  // rows * (head_dim + 1)
+  uint64_t slot_floats;  // rows * (head_dim + 1), rounded up to a multiple of 4
 };
 
 __device__ __forceinline__ void store_release_sys(uint32_t* addr, uint32_t value) {

@@ -212,6 +212,8 @@ enum class PrefillRoute { kTensorCore, kGatherTensorCore, kSplitKv };
 static bool gather_route_possible(const FwPrefillArgs* a) {
   if (a->block_table == nullptr || a->page_size <= 0 || a->pages_per_seq <= 0) return false;
   if (a->page_size % 16) return false;  // the split-KV kernel reports the shape error
+  // what the tensor-core kernel will be asked after the copy: bf16, and no page
+  // size to object to (64 stands for "any")
   FwPrefillArgs as_packed = *a;
   as_packed.kv_dtype = FW_DTYPE_BF16;
   as_packed.page_size = 64;

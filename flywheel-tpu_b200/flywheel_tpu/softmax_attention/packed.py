@@ -136,7 +136,7 @@ def packed_attention_device(q, k, v, cu_seqlens_q, cu_seqlens_k, *, nheads, nhea
                             total_k, token_major, max_seqlen_q, softmax_scale, causal, window_left,
                             softcap, return_lse, sinks, sink_period=0, rotary=None, window_right=0):
     """Launches fw_attention_packed on contiguous CUDA tensors.  q is (nheads,
-    total_q, 128) or, token-major, (total_q, nheads, 128); k / v likewise with
+    total_q, d) or, token-major, (total_q, nheads, d); k / v likewise with
     nheads_k and total_k.  Returns (out shaped like q, lse (nheads, total_q) or
     None)."""
     device = q.device
@@ -254,7 +254,7 @@ def flash_attn_func(
     q_dev, k_dev, v_dev = (_arrays.to_device(x, device).contiguous() for x in (q, k, v))
     int32 = dict(dtype=torch.int32, device=device)
     if token_major:
-        # packed tokens (batch * seqlen, nheads, 128): one sequence per batch row
+        # packed tokens (batch * seqlen, nheads, d): one sequence per batch row
         cu_q = torch.arange(batch + 1, **int32) * seqlen_q
         cu_k = torch.arange(batch + 1, **int32) * seqlen_k
         out, lse = packed_attention_device(
@@ -289,7 +289,7 @@ def packed_varlen_attn(q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_se
                        causal, window_size, softcap, return_softmax_lse, head_dim, token_major,
                        rotary_cos, rotary_sin, rotary_interleaved, rotary_k, learnable_sink):
     """The cu_seqlens_k branch of flash_attn_varlen_func (prefill.py:818-963 of
-    the reference): q (nheads, total_q, 128), k / v (nheads_k, total_k, 128), or
+    the reference): q (nheads, total_q, d), k / v (nheads_k, total_k, d), or
     token-major (total, nheads * head_dim)."""
     expected_rank = 2 if token_major else 3
     nheads, nheads_k, head_dim_qk = parse_qkv(

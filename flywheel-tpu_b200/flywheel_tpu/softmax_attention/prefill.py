@@ -119,9 +119,9 @@ def flash_attn_varlen_func(
 ):
     """Packed-sequence attention, forward only.
 
-    Packed K/V (no block_table): q (nheads, total_q, 128), k / v (nheads_k,
-    total_k, 128) bf16, or token-major (total, nheads * head_dim) with
-    head_dim=128; cu_seqlens_q / cu_seqlens_k are (num_seqs + 1,) cumulative
+    Packed K/V (no block_table): q (nheads, total_q, d), k / v (nheads_k,
+    total_k, d) bf16 with d 64, 128 or 256, or token-major (total, nheads *
+    head_dim) with head_dim= given; cu_seqlens_q / cu_seqlens_k are (num_seqs + 1,) cumulative
     offsets; causal / window masks are bottom-right aligned per sequence (right
     bound -1 or 0); rows past cu_seqlens_q[-1] return out = 0, lse = -inf; RoPE
     rotates K at its own positions and Q from len_k - len_q on.
