@@ -336,7 +336,10 @@ def _native_status(decoder, device):
 # of the reference.  Paged bf16, single-token decode unless q_len says otherwise.
 SECONDARY_SHAPES = {
     "serve-d256-gqa": dict(batch=128, hq=32, hk=4, d=256, page=128, q_len=1, lens=(15360, 15360)),
+    "serve-d256-gqa-b32": dict(batch=32, hq=32, hk=4, d=256, page=128, q_len=1, lens=(15360, 15360)),
+    "serve-d256-gqa-b256": dict(batch=256, hq=32, hk=4, d=256, page=128, q_len=1, lens=(15360, 15360)),
     "serve-d256-mha": dict(batch=32, hq=32, hk=32, d=256, page=128, q_len=1, lens=(15360, 15360)),
+    "serve-d256-mha-b128": dict(batch=128, hq=32, hk=32, d=256, page=128, q_len=1, lens=(15360, 15360)),
     "gate-decode": dict(batch=64, hq=32, hk=8, d=128, page=128, q_len=1, lens=(6144, 10239)),
     "gate-verify": dict(batch=32, hq=32, hk=8, d=128, page=128, q_len=4, lens=(6144, 10239)),
 }
