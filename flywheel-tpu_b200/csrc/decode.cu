@@ -197,6 +197,8 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
     fence_barrier_init();
   }
   scan_tiles(p, n_active, pre);  // contains __syncthreads
+  // the combine grid may be set up from here on; it still waits for this grid to finish
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
   const long long nt = pre[p.batch];
   if (cta == 0 && hg == 0)
@@ -631,6 +633,8 @@ combine_kernel(const CombineParams cp) {
   const int b = blockIdx.x;
   const int warp_in_block = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int sub = warp_in_block % WPR, warp = warp_in_block / WPR;
+  // everything below reads what the decode kernel wrote
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   const int n_active = load_num_active(p);
   const int before = p.tile_prefix[b];
   const int total_tiles = p.tile_prefix[p.batch];
@@ -1053,22 +1057,35 @@ static int launch_decode(DecodePlan& plan, void* workspace, cudaStream_t stream,
   // warps share a row, so its ~150 segments are read in a few rounds.
   const bool wide = static_cast<long long>(p.batch) * plan.rows_q <= 2048;
   const bool d256 = p.head_dim == kMaxHeadDim;
+  // The combine is launched as a programmatic dependent of the decode kernel:
+  // its grid is set up while the decode kernel still runs and its blocks wait
+  // (griddepcontrol.wait) for the decode grid to complete and flush, which
+  // takes the launch latency out of the step.
+  cudaLaunchAttribute pdl{};
+  pdl.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  pdl.val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchConfig_t cfg{};
+  cfg.stream = stream;
+  cfg.attrs = &pdl;
+  cfg.numAttrs = 1;
   if (wide) {
-    dim3 cgrid(p.batch, plan.rows_q);
+    cfg.gridDim = dim3(p.batch, plan.rows_q);
+    cfg.blockDim = dim3(16 * 32);
     if (d256)
-      combine_kernel<16, 256><<<cgrid, 16 * 32, 0, stream>>>(cp);
+      cudaLaunchKernelEx(&cfg, combine_kernel<16, 256>, cp);
     else
-      combine_kernel<16, 128><<<cgrid, 16 * 32, 0, stream>>>(cp);
+      cudaLaunchKernelEx(&cfg, combine_kernel<16, 128>, cp);
   } else {
     // Each warp walks several rows of its request, so the per-request
     // bookkeeping is paid once per warp; enough blocks to fill the machine.
     const int blocks_per_request = (plan.rows_q + kCombineWarps - 1) / kCombineWarps;
     const int wanted = (8 * sm_count() + p.batch - 1) / p.batch;
-    dim3 cgrid(p.batch, max(1, min(blocks_per_request, wanted)));
+    cfg.gridDim = dim3(p.batch, max(1, min(blocks_per_request, wanted)));
+    cfg.blockDim = dim3(kCombineWarps * 32);
     if (d256)
-      combine_kernel<1, 256><<<cgrid, kCombineWarps * 32, 0, stream>>>(cp);
+      cudaLaunchKernelEx(&cfg, combine_kernel<1, 256>, cp);
     else
-      combine_kernel<1, 128><<<cgrid, kCombineWarps * 32, 0, stream>>>(cp);
+      cudaLaunchKernelEx(&cfg, combine_kernel<1, 128>, cp);
   }
   err = cudaGetLastError();
   if (err != cudaSuccess) {
