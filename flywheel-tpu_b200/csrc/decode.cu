@@ -635,6 +635,7 @@ combine_kernel(const CombineParams cp) {
   const int sub = warp_in_block % WPR, warp = warp_in_block / WPR;
   // everything below reads what the decode kernel wrote
   asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // e.g. the state exchange
   const int n_active = load_num_active(p);
   const int before = p.tile_prefix[b];
   const int total_tiles = p.tile_prefix[p.batch];

@@ -65,6 +65,10 @@ constexpr int kScatterBlocks = 8;  // blocks that share the copy to one peer
 __global__ void __launch_bounds__(128) scatter_state_kernel(const ExchangeParams p) {
   const int peer = blockIdx.x;
   uint32_t* header = reinterpret_cast<uint32_t*>(p.peers[p.rank]);
+  // Launched as a programmatic dependent of the kernel that writes the state
+  // (and, through it, of the previous step's merge, which advances the epoch).
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const uint32_t epoch = header[0] + 1;
   float* dst = slot_of(p.peers[peer], epoch, p.world, p.rank, p.slot_floats);
   const int n_out = p.rows * p.head_dim;
@@ -91,6 +95,7 @@ __global__ void __launch_bounds__(128) gather_merge_kernel(const ExchangeParams 
   __shared__ int failed;
   uint8_t* mine = p.peers[p.rank];
   uint32_t* header = reinterpret_cast<uint32_t*>(mine);
+  asm volatile("griddepcontrol.wait;" ::: "memory");  // the scatter kernel of this rank is done
   const uint32_t epoch = header[0] + 1;
   if (threadIdx.x == 0) failed = 0;
   __syncthreads();
@@ -274,9 +279,24 @@ extern "C" int fw_state_exchange_merge(const FwExchangeArgs* a, void* stream_ptr
   p.lse_token_stride = a->lse_token_stride;
   p.slot_floats = slot_floats_of(a->rows, a->head_dim);
   cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
-  scatter_state_kernel<<<dim3(a->world, kScatterBlocks), 128, 0, stream>>>(p);
-  gather_merge_kernel<<<(a->rows + 3) / 4, 128, 0, stream>>>(p);
-  cudaError_t err = cudaGetLastError();
+  // Both kernels are programmatic dependents of the kernel before them in the
+  // stream: their launch latency hides under it, and each starts with
+  // griddepcontrol.wait before it reads anything.
+  cudaLaunchAttribute pdl{};
+  pdl.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  pdl.val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchConfig_t cfg{};
+  cfg.stream = stream;
+  cfg.attrs = &pdl;
+  cfg.numAttrs = 1;
+  cfg.gridDim = dim3(a->world, kScatterBlocks);
+  cfg.blockDim = dim3(128);
+  cudaError_t err = cudaLaunchKernelEx(&cfg, scatter_state_kernel, p);
+  if (err == cudaSuccess) {
+    cfg.gridDim = dim3((a->rows + 3) / 4);
+    err = cudaLaunchKernelEx(&cfg, gather_merge_kernel, p);
+  }
+  if (err == cudaSuccess) err = cudaGetLastError();
   if (err != cudaSuccess) {
     set_error("exchange kernels launch: %s", cudaGetErrorString(err));
     return FW_ERR_LAUNCH;
