@@ -1162,6 +1162,8 @@ struct PrefillPlanParams {
 __global__ void __launch_bounds__(256) prefill_plan_kernel(const PrefillPlanParams pp) {
   __shared__ int off[kMaxInlineBatch + 1];
   __shared__ int bucket[kSortBuckets];
+  // the attention kernel behind this one may be set up now; it waits for this grid to finish
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int n_active = pp.num_active ? min(pp.batch, max(0, *pp.num_active)) : pp.batch;
   auto used_of = [&](int r) { return pp.cu_k ? max(0, pp.cu_k[r + 1] - pp.cu_k[r]) : pp.seqused[r]; };
   if (blockIdx.x == 0) {

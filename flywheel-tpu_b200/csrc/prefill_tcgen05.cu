@@ -62,6 +62,8 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 
   // An item is up to kStreams * tpb query tokens of one request; stream t owns
   // tokens [t * tpb, (t + 1) * tpb) x the `group` heads of KV head h.
+  // launched as a programmatic dependent of the plan kernel, which writes the item table
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   const int4 it = *reinterpret_cast<const int4*>(p.items + 8 * item);
   const int req = it.x, q_row0 = it.y, q_valid = it.z, anchor = it.w;
   const int kv_limit = p.items[8 * item + 4];
@@ -575,7 +577,17 @@ int tcgen05_prefill(const FwPrefillArgs* a, cudaStream_t stream) {
     return FW_ERR_LAUNCH;
   }
   dim3 grid(a->nheads_k, max_items);
-  kernel<<<grid, 64 + kStreams * 128, kSmemBytes, stream>>>(map_q, map_kv, map_v, p);
+  cudaLaunchAttribute pdl{};
+  pdl.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  pdl.val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = grid;
+  cfg.blockDim = dim3(64 + kStreams * 128);
+  cfg.dynamicSmemBytes = kSmemBytes;
+  cfg.stream = stream;
+  cfg.attrs = &pdl;
+  cfg.numAttrs = 1;
+  cudaLaunchKernelEx(&cfg, kernel, map_q, map_kv, map_v, p);
   err = cudaGetLastError();
   if (err != cudaSuccess) {
     set_error("tcgen05 prefill kernel launch: %s", cudaGetErrorString(err));
