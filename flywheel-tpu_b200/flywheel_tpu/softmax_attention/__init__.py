@@ -1,13 +1,9 @@
-"""Softmax attention: the flash-attention API on the B200 CUDA kernels."""
+"""The flash-attention entry points, served by the B200 CUDA kernels."""
 
-from flywheel_tpu.softmax_attention.decode import flash_attn_with_kvcache
-from flywheel_tpu.softmax_attention.prefill import (
-    flash_attn_func,
-    flash_attn_varlen_func,
-)
+from flywheel_tpu.softmax_attention import decode, packed, prefill
 
-__all__ = [
-    "flash_attn_func",
-    "flash_attn_varlen_func",
-    "flash_attn_with_kvcache",
-]
+flash_attn_with_kvcache = decode.flash_attn_with_kvcache
+flash_attn_varlen_func = prefill.flash_attn_varlen_func
+flash_attn_func = packed.flash_attn_func
+
+__all__ = ["flash_attn_func", "flash_attn_varlen_func", "flash_attn_with_kvcache"]
