@@ -13,7 +13,8 @@ launches, no collective library on the data path); "nccl" - an NCCL
 all-gather followed by `fw_lse_combine`.  The rank that owns the page holding
 position `cache_len` appends the new token.
 
-Requests and KV heads need none of this: they shard with no communication.
+Requests and KV heads need none of this: they shard with no communication
+(`request_shard`, `kv_head_shard`).
 """
 
 from __future__ import annotations
@@ -49,6 +50,35 @@ def local_length(global_len: int, page_size: int, first_page: int, last_page: in
     [first_page, last_page)."""
     lo, hi = first_page * page_size, last_page * page_size
     return max(0, min(global_len, hi) - lo)
+
+
+def kv_head_shard(nheads: int, nheads_k: int, world: int, rank: int) -> tuple[slice, slice]:
+    """(query-head slice, KV-head slice) of `rank` when the KV heads are split
+    over `world` GPUs: each GPU keeps nheads_k / world KV heads of every page
+    (its pool is (num_pages, page_size, 2 * nheads_k / world, d), same block
+    table everywhere) and the query heads that share them.  No communication:
+    the ranks' outputs are disjoint head slices of the full output."""
+    if nheads_k % world:
+        raise ValueError(f"nheads_k={nheads_k} must be a multiple of the {world} ranks.")
+    if nheads % nheads_k:
+        raise ValueError(f"{nheads=} must be a multiple of {nheads_k=}.")
+    per_rank, group = nheads_k // world, nheads // nheads_k
+    kv = slice(rank * per_rank, (rank + 1) * per_rank)
+    return slice(kv.start * group, kv.stop * group), kv
+
+
+def request_shard(lengths, world: int, rank: int) -> list[int]:
+    """Requests of `rank` when the batch is split over `world` GPUs with no
+    communication: longest first, each to the GPU with the fewest cached tokens
+    so far, so the ranks stream about the same number of KV bytes."""
+    order = sorted(range(len(lengths)), key=lambda i: (-int(lengths[i]), i))
+    load, mine = [0] * world, []
+    for index in order:
+        target = min(range(world), key=lambda r: (load[r], r))
+        load[target] += int(lengths[index])
+        if target == rank:
+            mine.append(index)
+    return sorted(mine)
 
 
 def pack_state(partial_out: torch.Tensor, partial_lse: torch.Tensor) -> torch.Tensor:

@@ -112,3 +112,37 @@ def test_two_hundred_nat_jump_mid_stream():
     np.testing.assert_allclose(out.astype(np.float32), -3.0, atol=2e-2)
     k512 = keys[512, 0].astype(oracle.BF16).astype(np.float32)
     np.testing.assert_allclose(lse, float(k512.sum() * d ** -0.5), rtol=2e-3)
+
+
+def test_kv_head_shards_reproduce_the_full_call():
+    """KV-head sharding needs no communication: each shard's decode over its own
+    heads of every page is a slice of the full output (two shards run one after
+    the other on this GPU)."""
+    import torch
+    from flywheel_tpu import flash_attn_with_kvcache
+    from flywheel_tpu.softmax_attention import distributed as d
+    from flywheel_tpu.testing import workloads
+    from oracle import paged_attention as oracle
+    case = workloads.host_case(5, lens=(3, 64, 700, 1500), hq=16, hk=4, page_size=64)
+    to_t = lambda a: torch.from_numpy(a.view(np.int16)).cuda().view(torch.bfloat16)
+    full_pool = to_t(case.pool)
+    full, full_lse, _ = flash_attn_with_kvcache(
+        case.q, full_pool, None, case.k_new, case.v_new, cache_seqlens=case.cache_seqlens,
+        block_table=case.block_table, causal=True, return_softmax_lse=True)
+    k_pages, v_pages = oracle.split_kv_heads(case.pool, 4)
+    for rank in range(2):
+        q_heads, kv_heads = d.kv_head_shard(16, 4, 2, rank)
+        shard_pool = to_t(oracle.merge_kv_heads(k_pages[:, :, kv_heads], v_pages[:, :, kv_heads]))
+        out, lse, _ = flash_attn_with_kvcache(
+            np.ascontiguousarray(case.q[:, :, q_heads]), shard_pool, None,
+            np.ascontiguousarray(case.k_new[:, :, kv_heads]), np.ascontiguousarray(case.v_new[:, :, kv_heads]),
+            cache_seqlens=case.cache_seqlens, block_table=case.block_table, causal=True,
+            return_softmax_lse=True)
+        # the same math per head; only the split of the key range over CTAs may differ
+        np.testing.assert_allclose(out.astype(np.float32), full[:, :, q_heads].astype(np.float32), rtol=0, atol=1e-2)
+        np.testing.assert_allclose(lse, full_lse[:, q_heads], rtol=0, atol=1e-4)
+        # the shard's pool after the append = the shard's heads of the full pool
+        got_k, got_v = oracle.split_kv_heads(shard_pool.cpu().view(torch.int16).numpy().view(oracle.BF16), 2)
+        want_k, want_v = oracle.split_kv_heads(full_pool.cpu().view(torch.int16).numpy().view(oracle.BF16), 4)
+        np.testing.assert_array_equal(got_k.view(np.uint16), want_k[:, :, kv_heads].view(np.uint16))
+        np.testing.assert_array_equal(got_v.view(np.uint16), want_v[:, :, kv_heads].view(np.uint16))

@@ -84,3 +84,20 @@ def test_sharded_state_gather_and_merge_on_two_cpu_ranks():
     mp.spawn(_rank_main, args=(world, port, results), nprocs=world, join=True)
     assert results[0][0] + results[1][0] == 500
     assert results[0][1] == results[1][1] == 1      # page 7 of 9 lives on rank 1
+
+
+def test_kv_head_and_request_sharding_partition_the_work():
+    from flywheel_tpu.softmax_attention import distributed as d
+    # KV-head sharding: disjoint slices that cover every head, groups kept together
+    q_slices, kv_slices = zip(*(d.kv_head_shard(64, 8, 4, r) for r in range(4)))
+    assert [s.start for s in kv_slices] == [0, 2, 4, 6] and kv_slices[-1].stop == 8
+    assert [(s.start, s.stop) for s in q_slices] == [(0, 16), (16, 32), (32, 48), (48, 64)]
+    with pytest.raises(ValueError):
+        d.kv_head_shard(64, 8, 3, 0)
+    # request sharding: every request exactly once, token loads within one request of each other
+    rng = np.random.default_rng(0)
+    lens = rng.integers(1024, 32769, 128)
+    shards = [d.request_shard(lens, 8, r) for r in range(8)]
+    assert sorted(i for shard in shards for i in shard) == list(range(128))
+    loads = [int(lens[shard].sum()) for shard in shards]
+    assert max(loads) - min(loads) <= int(lens.max())
