@@ -168,9 +168,24 @@ __device__ __forceinline__ uint32_t fp8x2_to_f16x2(uint16_t v) {
   return r;
 }
 
-// Records a failure in the device status word (first writer wins).
+// Records a failure in the device status word.  The codes are distinct bits and
+// the word is their OR, so a clamped page id reported by an earlier launch does
+// not hide a later timeout.  The word stays set until the host reads it.
 __device__ __forceinline__ void report_status(int* status, int code) {
-  if (status != nullptr) atomicCAS(status, FW_STATUS_OK, code);
+  if (status != nullptr) atomicOr(status, code);
+}
+// Word 4 of the status block says "the launch in flight is void": a bounded
+// wait of this launch gave up, so CTAs that have not started yet may leave at
+// once.  Unlike word 0 it is cleared at the head of every launch that uses it,
+// so nothing an earlier launch reported can switch a later one off.
+constexpr int kStatusLaunchVoidWord = 4;
+__device__ __forceinline__ void report_timeout(int* status) {
+  if (status == nullptr) return;
+  atomicOr(status, FW_STATUS_WAIT_TIMEOUT);
+  *reinterpret_cast<volatile int*>(status + kStatusLaunchVoidWord) = 1;
+}
+__device__ __forceinline__ bool launch_is_void(const int* status) {
+  return status != nullptr && *reinterpret_cast<const volatile int*>(status + kStatusLaunchVoidWord) != 0;
 }
 
 // ---------------------------------------------------------------- host side
@@ -188,10 +203,11 @@ int encode_tensor_map_bf16(CUtensorMap* map, int rank, const void* base, const u
                            const uint64_t* strides, const uint32_t* box);
 
 // Query-block table for chunked prefill (decode.cu): cuts every active request
-// into blocks of qb tokens, writes 8 ints per block into items[0..max_items)
-// and clears the packed rows no active request owns.
+// into blocks of qb tokens, writes 8 ints per block into items[0..max_items),
+// clears the packed rows no active request owns and clears the "launch is void"
+// word of the status block for the attention kernel that follows.
 int launch_prefill_plan(const FwPrefillArgs* args, int qb, int max_items, int* items, long long tok_stride,
-                        long long head_stride, cudaStream_t stream);
+                        long long head_stride, int* status, cudaStream_t stream);
 
 // Chunked prefill on tcgen05 tensor cores (prefill_tcgen05.cu).
 bool tcgen05_prefill_supported(const FwPrefillArgs* args);

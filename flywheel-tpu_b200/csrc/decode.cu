@@ -44,6 +44,7 @@ struct DecodeParams {
   const int* block_table;
   const int* cache_batch_idx;
   const int* num_active;
+  const int* append_enable;  // NULL, or one device int: 0 = treat this call as if there were no new tokens
   const float* k_descale;
   float* part_o;
   float* part_ml;
@@ -100,7 +101,8 @@ __device__ __forceinline__ Span request_span(const DecodeParams& p, int b, int n
   if (b >= n_active) return s;
   int len = max(p.cache_seqlens[b], 0);
   s.cache_len = len;
-  s.total = len + (p.has_new ? p.seqlen_q : 0);
+  const bool has_new = p.has_new && (p.append_enable == nullptr || *p.append_enable != 0);
+  s.total = len + (has_new ? p.seqlen_q : 0);
   s.kv_end = s.total;
   s.diag_base = s.total - p.seqlen_q;
   if (s.total <= 0) return s;
@@ -227,11 +229,15 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
         const int page_idx = pos0 / p.page_size;
         if (page_idx != cur_page_idx) {
           cur_page_idx = page_idx;
-          int page = p.merged ? p.block_table[static_cast<long long>(sp.req) * p.pages_per_seq + page_idx]
-                              : (p.cache_batch_idx ? p.cache_batch_idx[b] : b);
+          // A position past the table row (or past a contiguous cache's capacity)
+          // has no page: the table is not read there.
+          int page = -1;
+          if (page_idx < p.pages_per_seq)
+            page = p.merged ? p.block_table[static_cast<long long>(sp.req) * p.pages_per_seq + page_idx]
+                            : (p.cache_batch_idx ? p.cache_batch_idx[b] : b);
           if (page < 0 || page >= p.num_pages) {
             report_status(p.status, FW_STATUS_BAD_PAGE);
-            page = 0;
+            page = 0;  // some page must be read; the result of this request is void
           }
           cur_page = page;
         }
@@ -366,18 +372,28 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
           uint8_t* gk = nullptr;
           uint8_t* gv = nullptr;
           if (is_new && mti == 0) {
+            // The new row goes to its page only when that page exists: a table
+            // entry outside the pool, or a position past the table row / the
+            // contiguous capacity, is reported and nothing is stored (the row is
+            // still attended from shared memory), so no other request's page is
+            // ever overwritten.
             const int page_idx = pos / p.page_size;
-            int page = p.merged ? p.block_table[static_cast<long long>(sp.req) * p.pages_per_seq + page_idx]
-                                : (p.cache_batch_idx ? p.cache_batch_idx[b] : b);
-            if (page < 0 || page >= p.num_pages) page = 0;
-            const long long row = (static_cast<long long>(page) * p.page_size + (pos - page_idx * p.page_size)) *
-                                  p.row_bytes;
-            if (p.merged) {
-              gk = p.k_base + row + static_cast<long long>(2 * h) * p.plane_bytes;
-              gv = gk + p.plane_bytes;
+            int page = -1;
+            if (page_idx < p.pages_per_seq)
+              page = p.merged ? p.block_table[static_cast<long long>(sp.req) * p.pages_per_seq + page_idx]
+                              : (p.cache_batch_idx ? p.cache_batch_idx[b] : b);
+            if (page < 0 || page >= p.num_pages) {
+              if (lane == 0) report_status(p.status, FW_STATUS_BAD_PAGE);
             } else {
-              gk = p.k_base + row + static_cast<long long>(h) * p.plane_bytes;
-              gv = p.v_base + row + static_cast<long long>(h) * p.plane_bytes;
+              const long long row = (static_cast<long long>(page) * p.page_size + (pos - page_idx * p.page_size)) *
+                                    p.row_bytes;
+              if (p.merged) {
+                gk = p.k_base + row + static_cast<long long>(2 * h) * p.plane_bytes;
+                gv = gk + p.plane_bytes;
+              } else {
+                gk = p.k_base + row + static_cast<long long>(h) * p.plane_bytes;
+                gv = p.v_base + row + static_cast<long long>(h) * p.plane_bytes;
+              }
             }
           }
           for (int i = lane; i < 2 * chunks; i += 32) {
@@ -770,8 +786,10 @@ combine_kernel(const CombineParams cp) {
       continue;
     }
 
-    // Fold the sink: it joins the denominator only.
-    const float sink2 = cp.sinks ? cp.sinks[hq] * kLog2e : -INFINITY;
+    // Fold the sink: it joins the denominator only.  Rows of requests past
+    // num_active are not attention rows at all: out 0, lse -inf, sink or not.
+    const bool live_request = p.items != nullptr || b < n_active;
+    const float sink2 = cp.sinks && live_request ? cp.sinks[hq] * kLog2e : -INFINITY;
     const float m_all = fmaxf(m_max, sink2);
     float out_scale = 0.f, lse = -INFINITY;
     if (m_all != -INFINITY) {
@@ -952,6 +970,7 @@ static int plan_decode(const FwDecodeArgs* a, DecodePlan* plan, int max_batch = 
   p.block_table = a->block_table;
   p.cache_batch_idx = a->cache_batch_idx;
   p.num_active = a->num_active;
+  p.append_enable = a->k_new != nullptr ? a->append_enable : nullptr;
   p.k_descale = a->k_descale;
   p.num_pages = a->num_pages;
   p.page_size = a->page_size;
@@ -1149,6 +1168,7 @@ struct PrefillPlanParams {
   const int* seqused;  // paged: request r's key count
   const int* num_active;
   int* items;
+  int* status;  // status block of the launch that follows, or NULL
   __nv_bfloat16* out;
   float* lse;
   long long tok_stride, head_stride;
@@ -1167,6 +1187,8 @@ __global__ void __launch_bounds__(256) prefill_plan_kernel(const PrefillPlanPara
   const int n_active = pp.num_active ? min(pp.batch, max(0, *pp.num_active)) : pp.batch;
   auto used_of = [&](int r) { return pp.cu_k ? max(0, pp.cu_k[r + 1] - pp.cu_k[r]) : pp.seqused[r]; };
   if (blockIdx.x == 0) {
+    // nothing an earlier launch reported may switch the coming one off
+    if (threadIdx.x == 0 && pp.status != nullptr) pp.status[kStatusLaunchVoidWord] = 0;
     for (int r = threadIdx.x; r < pp.batch; r += blockDim.x) {
       const int c = r < n_active ? max(0, pp.cu[r + 1] - pp.cu[r]) : 0;
       off[r + 1] = (c + pp.qb - 1) / pp.qb;
@@ -1244,7 +1266,7 @@ __global__ void __launch_bounds__(256) prefill_plan_kernel(const PrefillPlanPara
 }
 
 int launch_prefill_plan(const FwPrefillArgs* a, int qb, int max_items, int* items, long long tok_stride,
-                        long long head_stride, cudaStream_t stream) {
+                        long long head_stride, int* status, cudaStream_t stream) {
   if (a->batch > kMaxInlineBatch) {
     set_error("batch %d exceeds %d per call; split the batch.", a->batch, kMaxInlineBatch);
     return FW_ERR_UNSUPPORTED;
@@ -1256,6 +1278,7 @@ int launch_prefill_plan(const FwPrefillArgs* a, int qb, int max_items, int* item
   pp.seqused = a->seqused_k;
   pp.num_active = a->num_active;
   pp.items = items;
+  pp.status = status;
   pp.out = static_cast<__nv_bfloat16*>(a->out);
   pp.lse = a->lse;
   pp.tok_stride = tok_stride;
@@ -1375,7 +1398,8 @@ int splitkv_prefill(const FwPrefillArgs* a, cudaStream_t stream) {
   int* items = reinterpret_cast<int*>(static_cast<uint8_t*>(a->workspace) + sp.off_items);
   p.q = static_cast<const __nv_bfloat16*>(a->q);
   p.items = items;
-  rc = launch_prefill_plan(a, sp.qb, sp.max_items, items, p.q_tok_stride, p.q_head_stride, stream);
+  rc = launch_prefill_plan(a, sp.qb, sp.max_items, items, p.q_tok_stride, p.q_head_stride,
+                           static_cast<int*>(a->workspace), stream);
   if (rc != FW_OK) return rc;
   return launch_decode(sp.decode, a->workspace, stream, a->kv_dtype, a->out, a->lse, nullptr, nullptr,
                        a->v_descale, a->sinks);
@@ -1444,4 +1468,13 @@ extern "C" int fw_decode_kvcache_static(const FwDecodeArgs* a, void* stream_ptr)
   with_scratch.workspace = scratch;
   with_scratch.workspace_bytes = FW_STATIC_SCRATCH_BYTES;
   return fw_decode_kvcache(&with_scratch, stream_ptr);
+}
+
+// The status word of the built-in scratch on the current device.  It describes
+// the most recent fw_decode_kvcache_static call there, which cleared it first.
+extern "C" int fw_read_status_static(void* stream_ptr, int32_t* status) {
+  void* scratch = nullptr;
+  int rc = static_scratch_address(&scratch);
+  if (rc != FW_OK) return rc;
+  return fw_read_status(scratch, stream_ptr, status);
 }

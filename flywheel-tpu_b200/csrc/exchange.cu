@@ -303,3 +303,43 @@ extern "C" int fw_state_exchange_merge(const FwExchangeArgs* a, void* stream_ptr
   }
   return FW_OK;
 }
+
+// ---------------------------------------------------------------- round-robin page ownership
+namespace fw {
+
+// Tokens of the first `len` positions that fall in pages p with p % world == rank.
+__host__ __device__ inline int round_robin_local_length(int len, int page_size, int world, int rank) {
+  const int full_pages = len / page_size, tail = len - full_pages * page_size;
+  // full pages owned: those p < full_pages with p % world == rank
+  const int owned_full = full_pages > rank ? (full_pages - rank + world - 1) / world : 0;
+  return owned_full * page_size + (full_pages % world == rank ? tail : 0);
+}
+
+__global__ void shard_step_kernel(const FwShardStepArgs a) {
+  if (threadIdx.x != 0 || blockIdx.x != 0) return;
+  const int len = max(*a.global_len, 0);
+  *a.local_len = round_robin_local_length(len, a.page_size, a.world, a.rank);
+  *a.append_enable = (len / a.page_size) % a.world == a.rank ? 1 : 0;
+  *a.global_len = len + a.advance;
+}
+
+}  // namespace fw
+
+extern "C" int fw_shard_step(const FwShardStepArgs* a, void* stream_ptr) {
+  if (a == nullptr || a->global_len == nullptr || a->local_len == nullptr || a->append_enable == nullptr) {
+    fw::set_error("global_len, local_len and append_enable must be device pointers, not NULL.");
+    return FW_ERR_BAD_SHAPE;
+  }
+  if (a->page_size <= 0 || a->world <= 0 || a->rank < 0 || a->rank >= a->world || a->advance < 0) {
+    fw::set_error("page_size and world must be positive, 0 <= rank < world, advance >= 0; got %d, %d, %d, %d.",
+                  a->page_size, a->world, a->rank, a->advance);
+    return FW_ERR_BAD_SHAPE;
+  }
+  fw::shard_step_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream_ptr)>>>(*a);
+  cudaError_t err = cudaGetLastError();
+  if (err != cudaSuccess) {
+    fw::set_error("shard step launch: %s", cudaGetErrorString(err));
+    return FW_ERR_LAUNCH;
+  }
+  return FW_OK;
+}

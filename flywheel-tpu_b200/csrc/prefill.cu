@@ -1,9 +1,6 @@
 // fw_prefill_paged: chunked prefill over the paged merged cache
 // (flash_attn_varlen_func with block_table; reference
 // flywheel_tpu/softmax_attention/prefill.py:437-661).  Picks the kernel.
-#include <cstdlib>
-#include <cstring>
-
 #include "common.cuh"
 
 using namespace fw;
@@ -33,6 +30,10 @@ static int check_prefill_args(const FwPrefillArgs* a) {
   }
   if (a->rotary_cos != nullptr && a->rotary_len <= 0) {
     set_error("rotary tables need a positive rotary_len.");
+    return FW_ERR_BAD_SHAPE;
+  }
+  if (a->route != FW_ROUTE_AUTO && a->route != FW_ROUTE_TENSOR_CORE && a->route != FW_ROUTE_SPLIT_KV) {
+    set_error("route must be FW_ROUTE_AUTO, FW_ROUTE_TENSOR_CORE or FW_ROUTE_SPLIT_KV; got %d.", a->route);
     return FW_ERR_BAD_SHAPE;
   }
   return FW_OK;
@@ -202,8 +203,8 @@ __global__ void __launch_bounds__(256) gather_kv_kernel(const GatherParams p) {
 // ones are KV-streaming work and go to the split-KV kernel.  Pools the
 // tensor-core kernel cannot read in place take the gather above first, which
 // pays off once a chunk is a few hundred tokens (the copy is linear in the key
-// count, the attention is chunk times that).  The environment variable
-// FLYWHEEL_PREFILL_KERNEL=tcgen05|splitkv pins the choice (tests and profiling).
+// count, the attention is chunk times that).  FwPrefillArgs.route pins the
+// choice for one call (tests and profiling); nothing process-wide is consulted.
 static constexpr int kTensorCoreMinChunk = 64;
 static constexpr int kGatherMinChunk = 256;
 
@@ -223,9 +224,8 @@ static bool gather_route_possible(const FwPrefillArgs* a) {
 }
 
 static PrefillRoute pick_route(const FwPrefillArgs* a) {
-  const char* pin = std::getenv("FLYWHEEL_PREFILL_KERNEL");
-  const bool pin_split = pin != nullptr && std::strcmp(pin, "splitkv") == 0;
-  const bool pin_tensor = pin != nullptr && std::strcmp(pin, "tcgen05") == 0;
+  const bool pin_split = a->route == FW_ROUTE_SPLIT_KV;
+  const bool pin_tensor = a->route == FW_ROUTE_TENSOR_CORE;
   if (pin_split) return PrefillRoute::kSplitKv;
   if (tcgen05_prefill_supported(a))
     return pin_tensor || a->max_seqlen_q >= kTensorCoreMinChunk ? PrefillRoute::kTensorCore : PrefillRoute::kSplitKv;

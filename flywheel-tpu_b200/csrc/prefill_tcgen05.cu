@@ -38,6 +38,7 @@ struct Bars {
   uint64_t q_full;
   uint64_t k_full[kKvStages], v_full[kKvStages], k_empty[kKvStages], v_empty[kKvStages];
   uint64_t s_full[kStreams], p_full[kStreams], pv_done[kStreams];
+  uint64_t drain;  // abort path: completion of the MMAs issued so far
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -72,7 +73,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   if (q_valid <= 0) return;  // uniform across the CTA: nothing allocated yet
   // Once any CTA has reported a failed wait the launch is void: later CTAs
   // leave at once instead of each running into its own time limit.
-  if (p.status != nullptr && *reinterpret_cast<volatile int*>(p.status) != FW_STATUS_OK) return;
+  if (launch_is_void(p.status)) return;
   const int n_streams = q_valid > p.tpb ? kStreams : 1;
   const int diag_base = anchor - kStreams * p.tpb;  // token t of the item sits on diagonal diag_base + t
   const int first_key = p.window_left >= 0 ? max(0, diag_base - p.window_left) : 0;
@@ -93,6 +94,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       mbar_init(&bars->p_full[t], 4);
       mbar_init(&bars->pv_done[t], 1);
     }
+    mbar_init(&bars->drain, 1);
     bars->abort_flag = 0;
     fence_barrier_init();
   }
@@ -118,6 +120,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             tma_load_3d(smem + kSmemQ + t * 32768 + half * 16384 + g * p.tpb * 128, &map_q, &bars->q_full,
                         half * 64, q_row0 + t * p.tpb, h * p.group + g);
       bool ok = true;
+      int k_armed = 0, v_armed = 0;  // tiles whose K / V copies have been issued
       for (int j = 0; j < n_tiles && ok; ++j) {
         const int s = j % kKvStages;
         const uint32_t round = j / kKvStages;
@@ -158,6 +161,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             if (p.packed) tma_load_3d(dst, &map_kv, &bars->k_full[s], half * 64, tok[sub], h);
             else tma_load_4d(dst, &map_kv, &bars->k_full[s], half * 64, 2 * h, tok[sub], page[sub]);
           }
+        k_armed = j + 1;
         if (!FW_WAIT(18, j, &bars->v_empty[s], (round & 1) ^ 1)) {
           ok = false;
           break;
@@ -169,10 +173,18 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             if (p.packed) tma_load_3d(dst, &map_v, &bars->v_full[s], half * 64, tok[sub], h);
             else tma_load_4d(dst, &map_kv, &bars->v_full[s], half * 64, 2 * h + 1, tok[sub], page[sub]);
           }
+        v_armed = j + 1;
       }
       if (!ok) {
+        // A wait gave up: record it, tell the other warps, and let the copies
+        // that are still in flight land before this CTA's shared memory goes away.
         *abort_flag = 1;
-        report_status(p.status, FW_STATUS_WAIT_TIMEOUT);
+        report_timeout(p.status);
+        drain_wait(&bars->q_full, 0);
+        for (int j = max(0, k_armed - kKvStages); j < k_armed; ++j)
+          drain_wait(&bars->k_full[j % kKvStages], (j / kKvStages) & 1);
+        for (int j = max(0, v_armed - kKvStages); j < v_armed; ++j)
+          drain_wait(&bars->v_full[j % kKvStages], (j / kKvStages) & 1);
       }
     }
   } else if (n_tiles > 0 && warp == 1) {
@@ -231,8 +243,11 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         }
       }
       if (!ok) {
+        // The MMAs issued so far must have drained before tensor memory is freed.
         *abort_flag = 1;
-        report_status(p.status, FW_STATUS_WAIT_TIMEOUT);
+        report_timeout(p.status);
+        tc_commit(&bars->drain);
+        drain_wait(&bars->drain, 0);
       }
     }
   } else if (warp >= 2 && (warp - 2) / 4 < n_streams) {
@@ -428,7 +443,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       tc_fence_before();
     } else if (lane == 0) {
       *abort_flag = 1;
-      report_status(p.status, FW_STATUS_WAIT_TIMEOUT);
+      report_timeout(p.status);
     }
   }
 
@@ -533,7 +548,7 @@ int tcgen05_prefill(const FwPrefillArgs* a, cudaStream_t stream) {
   p.sink_period = a->sink_period;
 
   int rc = launch_prefill_plan(a, kStreams * tpb, max_items, const_cast<int*>(p.items), p.tok_stride,
-                               p.head_stride, stream);
+                               p.head_stride, p.status, stream);
   if (rc != FW_OK) return rc;
 
   // q viewed as (head_dim, tokens, heads); a box is 64 elements x tpb tokens of one head.

@@ -43,6 +43,7 @@ struct Bars {
   uint64_t q_full;
   uint64_t k_full[kStages], k_empty[kStages], v_full[kStages], v_empty[kStages];
   uint64_t s_full[2], p_full[2], pv_done;
+  uint64_t drain;  // abort path: completion of the MMAs issued so far
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -71,7 +72,7 @@ prefill_tcgen05_d256_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   const int kv_start = p.items[8 * item + 5];
   const int kv_end = p.right >= 0 ? min(anchor + p.right, kv_limit) : kv_limit;
   if (q_valid <= 0) return;
-  if (p.status != nullptr && *reinterpret_cast<volatile int*>(p.status) != FW_STATUS_OK) return;
+  if (launch_is_void(p.status)) return;
   const int diag_base = anchor - p.tpb;  // token t of the item sits on diagonal diag_base + t
   const int first_key = p.window_left >= 0 ? max(0, diag_base - p.window_left) : 0;
   const int tile_lo = first_key / kBN;
@@ -91,6 +92,7 @@ prefill_tcgen05_d256_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       mbar_init(&bars->p_full[b], 4);
     }
     mbar_init(&bars->pv_done, 1);
+    mbar_init(&bars->drain, 1);
     bars->abort_flag = 0;
     fence_barrier_init();
   }
@@ -115,6 +117,7 @@ prefill_tcgen05_d256_kernel(const __grid_constant__ CUtensorMap map_q, const __g
           tma_load_3d(smem + kSmemQ + blk * 16384 + g * p.tpb * 128, &map_q, &bars->q_full, blk * 64, q_row0,
                       h * p.group + g);
       bool ok = true;
+      int k_armed = 0, v_armed = 0;  // tiles whose K / V copies have been issued
       for (int j = 0; j < n_tiles && ok; ++j) {
         const int s = j % kStages;
         const uint32_t round = j / kStages;
@@ -152,6 +155,7 @@ prefill_tcgen05_d256_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             if (p.packed) tma_load_3d(dst, &map_kv, &bars->k_full[s], blk * 64, tok[sub], h);
             else tma_load_4d(dst, &map_kv, &bars->k_full[s], blk * 64, 2 * h, tok[sub], page[sub]);
           }
+        k_armed = j + 1;
         if (!FW_WAIT(18, j, &bars->v_empty[s], (round & 1) ^ 1)) {
           ok = false;
           break;
@@ -163,10 +167,18 @@ prefill_tcgen05_d256_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             if (p.packed) tma_load_3d(dst, &map_v, &bars->v_full[s], blk * 64, tok[sub], h);
             else tma_load_4d(dst, &map_kv, &bars->v_full[s], blk * 64, 2 * h + 1, tok[sub], page[sub]);
           }
+        v_armed = j + 1;
       }
       if (!ok) {
+        // A wait gave up: record it, tell the other warps, and let the copies
+        // that are still in flight land before this CTA's shared memory goes away.
         *abort_flag = 1;
-        report_status(p.status, FW_STATUS_WAIT_TIMEOUT);
+        report_timeout(p.status);
+        drain_wait(&bars->q_full, 0);
+        for (int j = max(0, k_armed - kStages); j < k_armed; ++j)
+          drain_wait(&bars->k_full[j % kStages], (j / kStages) & 1);
+        for (int j = max(0, v_armed - kStages); j < v_armed; ++j)
+          drain_wait(&bars->v_full[j % kStages], (j / kStages) & 1);
       }
     }
   } else if (n_tiles > 0 && warp == 1) {
@@ -218,8 +230,11 @@ prefill_tcgen05_d256_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         tc_commit(&bars->v_empty[s]);
       }
       if (!ok) {
+        // The MMAs issued so far must have drained before tensor memory is freed.
         *abort_flag = 1;
-        report_status(p.status, FW_STATUS_WAIT_TIMEOUT);
+        report_timeout(p.status);
+        tc_commit(&bars->drain);
+        drain_wait(&bars->drain, 0);
       }
     }
   } else if (warp >= 2) {
@@ -400,7 +415,7 @@ prefill_tcgen05_d256_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       tc_fence_before();
     } else if (lane == 0) {
       *abort_flag = 1;
-      report_status(p.status, FW_STATUS_WAIT_TIMEOUT);
+      report_timeout(p.status);
     }
   }
 
@@ -502,7 +517,8 @@ static int launch_single_tile(const FwPrefillArgs* a, cudaStream_t stream) {
   p.packed = packed;
   p.sink_period = a->sink_period;
 
-  int rc = launch_prefill_plan(a, tpb, max_items, const_cast<int*>(p.items), p.tok_stride, p.head_stride, stream);
+  int rc = launch_prefill_plan(a, tpb, max_items, const_cast<int*>(p.items), p.tok_stride, p.head_stride, p.status,
+                               stream);
   if (rc != FW_OK) return rc;
 
   CUtensorMap map_q, map_kv, map_v;

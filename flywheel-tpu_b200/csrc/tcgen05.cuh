@@ -199,6 +199,12 @@ __device__ __forceinline__ void record_timeout(int* status, int site, int j) {
   }
 }
 
+// Abort path only: a short bounded wait that lets copies or MMAs that are
+// already in flight land before the CTA gives its shared and tensor memory up.
+__device__ __forceinline__ void drain_wait(uint64_t* bar, uint32_t parity) {
+  for (uint32_t spin = 0; spin < (1u << 16) && !mbar_try_wait(bar, parity); ++spin) __nanosleep(64);
+}
+
 #define FW_WAIT(site, j, bar, parity) \
   (mbar_wait_bounded(bar, parity, abort_flag) || (record_timeout(p.status, site, j), false))
 

@@ -25,6 +25,7 @@ ERRORS = {
     -6: ValueError,            # FW_ERR_WORKSPACE
 }
 DTYPE_CODE = {"bfloat16": 0, "float8_e4m3fn": 1, "float8_e5m2": 2}
+ROUTE_CODE = {"auto": 0, "tcgen05": 1, "splitkv": 2}   # FwPrefillArgs.route
 
 c_ptr = ctypes.c_void_p
 i32, i64, u64, f32 = ctypes.c_int32, ctypes.c_int64, ctypes.c_uint64, ctypes.c_float
@@ -43,6 +44,7 @@ class FwDecodeArgs(ctypes.Structure):
         ("nheads", i32), ("nheads_k", i32), ("head_dim", i32),
         ("kv_dtype", i32), ("causal", i32), ("window_left", i32),
         ("softmax_scale", f32), ("softcap", f32), ("num_ctas", i32),
+        ("append_enable", c_ptr),
     ]
 
 
@@ -81,7 +83,7 @@ class FwPrefillArgs(ctypes.Structure):
         ("rotary_interleaved", i32), ("rotary_bf16", i32),
         ("v_packed", c_ptr), ("cu_seqlens_k", c_ptr), ("total_k", i32),
         ("kv_token_major", i32), ("rotary_k", i32), ("sink_period", i32),
-        ("window_right", i32), ("kv_request_stride", i32),
+        ("window_right", i32), ("kv_request_stride", i32), ("route", i32),
     ]
 
 
@@ -104,6 +106,13 @@ class FwExchangeArgs(ctypes.Structure):
     ]
 
 
+class FwShardStepArgs(ctypes.Structure):
+    _fields_ = [
+        ("global_len", c_ptr), ("local_len", c_ptr), ("append_enable", c_ptr),
+        ("page_size", i32), ("world", i32), ("rank", i32), ("advance", i32),
+    ]
+
+
 EXPORTS = {
     "fw_decode_workspace_bytes": (u64, [ctypes.POINTER(FwDecodeArgs)]),
     "fw_decode_kvcache": (ctypes.c_int, [ctypes.POINTER(FwDecodeArgs), c_ptr]),
@@ -121,8 +130,10 @@ EXPORTS = {
     "fw_peer_close": (ctypes.c_int, [c_ptr]),
     "fw_peer_free": (ctypes.c_int, [c_ptr]),
     "fw_state_exchange_merge": (ctypes.c_int, [ctypes.POINTER(FwExchangeArgs), c_ptr]),
+    "fw_shard_step": (ctypes.c_int, [ctypes.POINTER(FwShardStepArgs), c_ptr]),
     "fw_selftest_wait_timeout": (ctypes.c_int, [c_ptr, ctypes.c_uint32, c_ptr]),
     "fw_read_status": (ctypes.c_int, [c_ptr, c_ptr, ctypes.POINTER(i32)]),
+    "fw_read_status_static": (ctypes.c_int, [c_ptr, ctypes.POINTER(i32)]),
     "fw_last_error": (ctypes.c_char_p, []),
     "fw_version": (ctypes.c_int, []),
 }
@@ -176,7 +187,40 @@ def workspace(device, nbytes: int) -> torch.Tensor:
 
 
 def read_status(buf: torch.Tensor, device) -> int:
+    """The device status word at the head of workspace `buf` (the OR of the
+    FW_STATUS_* bits reported since the last read), cleared once read.
+    Synchronises the current stream."""
     status = i32(0)
     check(library().fw_read_status(buf.data_ptr(), current_stream(device),
                                    ctypes.byref(status)))
     return status.value
+
+
+STATUS_TEXT = {
+    1: "a bounded device-side wait gave up (FW_STATUS_WAIT_TIMEOUT): the results"
+       " of that launch are void",
+    2: "a block-table entry outside the pool, or a position past the table row /"
+       " the cache capacity, was met (FW_STATUS_BAD_PAGE): reads were clamped to"
+       " page 0 and an append there stored nothing",
+}
+
+
+def status_check_enabled() -> bool:
+    """FLYWHEEL_CHECK_STATUS=1 makes every entry point read the device status
+    word after its launch and raise on a non-zero one.  Off by default: the read
+    synchronises the stream, which a serving step cannot afford; the reference
+    has no runtime error channel at all."""
+    return os.environ.get("FLYWHEEL_CHECK_STATUS", "0") not in ("", "0")
+
+
+def raise_on_status(buf: torch.Tensor, device) -> None:
+    """Reads the status word of `buf` when the check is enabled and raises
+    TimeoutError (a wait gave up) or RuntimeError (bad page) if it is set."""
+    if not status_check_enabled():
+        return
+    status = read_status(buf, device)
+    if status == 0:
+        return
+    text = "; ".join(msg for bit, msg in STATUS_TEXT.items() if status & bit)
+    raise (TimeoutError if status & 1 else RuntimeError)(
+        f"device status {status}: {text}")

@@ -349,6 +349,7 @@ def flash_attn_with_kvcache(
             scratch = _native.workspace(device, nbytes)
             part.workspace, part.workspace_bytes = scratch.data_ptr(), scratch.numel()
             _native.check(lib.fw_decode_kvcache(ctypes.byref(part), stream))
+            _native.raise_on_status(scratch, device)
     else:
         from flywheel_tpu.softmax_attention.prefill import paged_prefill_device
         if is_ragged:

@@ -2,8 +2,8 @@
 
 The reference library is single-device; its serving patch merges per-device
 attention states with `_merge_states` (patches/tpu-inference.patch:7174-7186 of
-the reference project).  Here one process per GPU holds a contiguous range of
-the request's logical pages in its own pool; every decode step each rank runs
+the reference project).  Here one process per GPU holds every world-th logical
+page of the request (round-robin) in its own pool; every decode step each rank runs
 the split-KV decode kernel over its own pages in partial-state mode; then the
 sink-free `(o, lse)` states (33 KB per rank for 64 heads) are exchanged and
 merged.  Two exchanges are built: "p2p" (default) - every rank stores its
@@ -11,7 +11,9 @@ state into each peer's exchange buffer over NVLink and raises a flag there,
 and the merge kernel waits for all flags (fw_state_exchange_merge: two
 launches, no collective library on the data path); "nccl" - an NCCL
 all-gather followed by `fw_lse_combine`.  The rank that owns the page holding
-position `cache_len` appends the new token.
+position `cache_len` appends the new token; which rank that is, and how many
+tokens each rank holds, is worked out on the device every step (fw_shard_step),
+so one captured CUDA graph serves a whole generation.
 
 Requests and KV heads need none of this: they shard with no communication
 (`request_shard`, `kv_head_shard`).
@@ -28,28 +30,25 @@ import torch.distributed as dist
 from flywheel_tpu.softmax_attention import _arrays, _native
 
 
-def page_range(total_pages: int, world: int, rank: int) -> tuple[int, int]:
-    """[first, last) logical pages of `rank`: contiguous, sizes differ by at
-    most one, earlier ranks take the extra page."""
-    base, extra = divmod(total_pages, world)
-    first = rank * base + min(rank, extra)
-    return first, first + base + (1 if rank < extra else 0)
+def owned_pages(total_pages: int, world: int, rank: int) -> range:
+    """Logical pages of `rank`: page p lives on rank p % world, as that rank's
+    local page p // world.  Round-robin keeps the growing tail of a generation
+    moving from GPU to GPU, so every rank holds the same number of pages to
+    within one at every length."""
+    return range(rank, total_pages, world)
 
 
-def owner_of_page(total_pages: int, world: int, page: int) -> int:
-    """Rank whose page_range holds logical page `page`."""
-    base, extra = divmod(total_pages, world)
-    boundary = extra * (base + 1)
-    if page < boundary:
-        return page // (base + 1)
-    return extra + (page - boundary) // max(base, 1)
+def owner_of_page(page: int, world: int) -> int:
+    """Rank that holds logical page `page`."""
+    return page % world
 
 
-def local_length(global_len: int, page_size: int, first_page: int, last_page: int) -> int:
-    """Tokens of a request of `global_len` tokens that live in logical pages
-    [first_page, last_page)."""
-    lo, hi = first_page * page_size, last_page * page_size
-    return max(0, min(global_len, hi) - lo)
+def local_length(global_len: int, page_size: int, world: int, rank: int) -> int:
+    """How many of the first `global_len` tokens live in `rank`'s pages.  They
+    fill a prefix of its local page list, so this is the rank's cache_seqlens."""
+    full_pages, tail = divmod(global_len, page_size)
+    owned_full = len(range(rank, full_pages, world))
+    return owned_full * page_size + (tail if full_pages % world == rank else 0)
 
 
 def kv_head_shard(nheads: int, nheads_k: int, world: int, rank: int) -> tuple[slice, slice]:
@@ -98,13 +97,13 @@ def unpack_states(gathered: torch.Tensor, world: int, rows: int, d: int):
 
 @dataclasses.dataclass
 class ShardedDecoder:
-    """Per-rank state of a long-context decode whose pages are split over the
-    ranks of `group`.  `pool` holds this rank's pages (any physical order);
-    `table` is this rank's (1, local_pages) block table over its own pool."""
+    """Per-rank state of a long-context decode whose pages are dealt round-robin
+    over the ranks of `group`.  `pool` holds this rank's pages (any physical
+    order); `table` is this rank's (1, local_pages) block table over its own
+    pool, local page i being logical page rank + i * world."""
 
     pool: torch.Tensor
     table: torch.Tensor
-    total_pages: int
     nheads: int
     nheads_k: int
     group: dist.ProcessGroup | None = None
@@ -114,16 +113,17 @@ class ShardedDecoder:
 
     def __post_init__(self):
         self.device = self.pool.device
-        self.world = dist.get_world_size(self.group)
-        self.rank = dist.get_rank(self.group)
+        # without a process group there is one rank: it holds every page
+        self.world = dist.get_world_size(self.group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(self.group) if dist.is_initialized() else 0
         self.page_size = self.pool.shape[1]
         self.head_dim = self.pool.shape[3]
-        self.first_page, self.last_page = page_range(self.total_pages, self.world, self.rank)
         rows = self.nheads
         f32 = dict(dtype=torch.float32, device=self.device)
         self.state = torch.empty(rows * (self.head_dim + 1), **f32)
         self.gathered = torch.empty(self.world * rows * (self.head_dim + 1), **f32)
-        self.local_len = torch.zeros(1, dtype=torch.int32, device=self.device)
+        # [tokens cached (all ranks), tokens on this rank, does this rank append]
+        self.counters = torch.zeros(3, dtype=torch.int32, device=self.device)
         self.out = torch.empty((1, 1, self.nheads, self.head_dim), dtype=torch.bfloat16,
                                device=self.device)
         self.lse = torch.empty((1, self.nheads, 1), **f32)
@@ -175,54 +175,59 @@ class ShardedDecoder:
             _native.check(self.lib.fw_peer_free(self.peers[self.rank]))
         self.peers = None
 
-    def step(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, global_len: int):
-        """One decode step: q (1, 1, nheads, d), new k / v (1, 1, nheads_k, d),
-        `global_len` tokens cached before the step.  Returns (out, lse); the new
-        token is appended on the rank that owns its page."""
-        owner = owner_of_page(self.total_pages, self.world, global_len // self.page_size)
-        self.local_len.fill_(local_length(global_len, self.page_size, self.first_page, self.last_page))
-        return self._enqueue(q, k, v, owner == self.rank)
+    def set_length(self, global_len: int) -> None:
+        """Sets the number of tokens cached so far (over all ranks).  Every step
+        that carries a new token advances it on the device."""
+        self.counters[0:1].fill_(int(global_len))
 
-    def capture(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, global_len: int,
-                steps: int) -> torch.cuda.CUDAGraph:
-        """A CUDA graph of one decode step for the next `steps` positions, which
-        must all fall in pages of one rank (so which rank appends is fixed).  The
-        cached length lives on the device and the owning rank advances it inside
-        the graph; q / k / v are read from the given tensors at every replay, so
-        refill them in place between replays.  A step is latency-bound (tens of
-        microseconds of HBM time), so launching it as one graph matters."""
-        first_owner = owner_of_page(self.total_pages, self.world, global_len // self.page_size)
-        last_owner = owner_of_page(self.total_pages, self.world,
-                                   (global_len + steps - 1) // self.page_size)
-        if first_owner != last_owner:
-            raise ValueError("the captured steps must stay within one rank's pages")
-        appends = first_owner == self.rank
-        self.local_len.fill_(local_length(global_len, self.page_size, self.first_page, self.last_page))
+    def step(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, global_len: int | None = None):
+        """One decode step: q (1, 1, nheads, d), new k / v (1, 1, nheads_k, d).
+        `global_len`, when given, resets the cached length first; otherwise the
+        device counter carries on from the previous step.  Returns (out, lse);
+        the new token is appended on the rank that owns its page."""
+        if global_len is not None:
+            self.set_length(global_len)
+        return self._enqueue(q, k, v)
+
+    def capture(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
+                global_len: int) -> torch.cuda.CUDAGraph:
+        """A CUDA graph of one decode step starting at `global_len` cached tokens.
+        The cached length, each rank's share of it and which rank appends all
+        live on the device and are advanced inside the graph, so the graph can be
+        replayed for as long as the block tables have pages; q / k / v are read
+        from the given tensors at every replay, so refill them in place between
+        replays.  A step is latency-bound (tens of microseconds of HBM time), so
+        launching it as one graph matters."""
+        self.set_length(global_len)
         side = torch.cuda.Stream(self.device)
         side.wait_stream(torch.cuda.current_stream(self.device))
         with torch.cuda.stream(side):            # warm-up outside capture
-            self._enqueue(q, k, v, appends)
+            self._enqueue(q, k, v, advance=0)
         torch.cuda.current_stream(self.device).wait_stream(side)
         torch.cuda.synchronize(self.device)
-        self.local_len.fill_(local_length(global_len, self.page_size, self.first_page, self.last_page))
         graph = torch.cuda.CUDAGraph()
         # thread_local: the process group's watchdog thread may query events meanwhile
         with torch.cuda.graph(graph, capture_error_mode="thread_local"):
-            self._enqueue(q, k, v, appends)
-            if appends:
-                self.local_len.add_(1)
+            self._enqueue(q, k, v)
         return graph
 
-    def _enqueue(self, q, k, v, appends):
+    def _enqueue(self, q, k, v, advance=1):
         rows, d = self.nheads, self.head_dim
         partial_out = self.state[: rows * d]
         partial_lse = self.state[rows * d:]
         alone = self.world == 1   # one rank holds every page: no partial state, no exchange
+        stream = _native.current_stream(self.device)
+        base = self.counters.data_ptr()
+        shard = _native.FwShardStepArgs(
+            global_len=base, local_len=base + 4, append_enable=base + 8,
+            page_size=self.page_size, world=self.world, rank=self.rank,
+            advance=advance if k is not None else 0)
+        _native.check(self.lib.fw_shard_step(ctypes.byref(shard), stream))
         args = _native.FwDecodeArgs(
             q=q.data_ptr(), out=self.out.data_ptr() if alone else 0, lse=self.lse.data_ptr() if alone else 0,
             kv_cache=self.pool.data_ptr(), v_cache=0,
-            k_new=k.data_ptr() if appends else 0, v_new=v.data_ptr() if appends else 0,
-            cache_seqlens=self.local_len.data_ptr(), block_table=self.table.data_ptr(),
+            k_new=_arrays.data_ptr(k), v_new=_arrays.data_ptr(v), append_enable=base + 8,
+            cache_seqlens=base + 4, block_table=self.table.data_ptr(),
             sinks=_arrays.data_ptr(self.sinks) if alone else 0,
             partial_out=0 if alone else partial_out.data_ptr(),
             partial_lse=0 if alone else partial_lse.data_ptr(),
@@ -232,7 +237,6 @@ class ShardedDecoder:
             kv_dtype=_native.DTYPE_CODE[_arrays.dtype_name(self.pool.dtype)],
             # one query token on the last position: every local key is visible
             causal=0, window_left=-1, softmax_scale=self.scale, softcap=0.0, num_ctas=0)
-        stream = _native.current_stream(self.device)
         if self.scratch is None:
             nbytes = self.lib.fw_decode_workspace_bytes(ctypes.byref(args))
             if nbytes == 0:

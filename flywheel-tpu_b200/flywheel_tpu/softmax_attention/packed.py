@@ -175,6 +175,7 @@ def packed_attention_device(q, k, v, cu_seqlens_q, cu_seqlens_k, *, nheads, nhea
     scratch = _native.workspace(device, nbytes)
     args.workspace, args.workspace_bytes = scratch.data_ptr(), scratch.numel()
     _native.check(lib.fw_attention_packed(ctypes.byref(args), stream))
+    _native.raise_on_status(scratch, device)
     return out, lse
 
 

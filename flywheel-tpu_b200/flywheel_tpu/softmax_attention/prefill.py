@@ -30,6 +30,11 @@ from flywheel_tpu.softmax_attention.packed import flash_attn_func, packed_varlen
 
 __all__ = ["flash_attn_func", "flash_attn_varlen_func", "paged_prefill_device"]
 
+# Kernel a paged call runs on: "auto" (the library chooses by chunk length),
+# "tcgen05" or "splitkv".  Tests and profiling sessions set this attribute to
+# pin one; it travels to the library in FwPrefillArgs.route with every call.
+FORCED_ROUTE = "auto"
+
 
 def paged_prefill_device(q, kv_cache, cu_seqlens_q, seqused_k, block_table,
                          num_active, *, max_seqlen_q, nheads_k, softmax_scale,
@@ -63,7 +68,8 @@ def paged_prefill_device(q, kv_cache, cu_seqlens_q, seqused_k, block_table,
         causal=int(bool(causal)),
         window_left=-1 if window_left is None else int(window_left),
         softmax_scale=float(softmax_scale), softcap=float(softcap),
-        token_major=int(bool(token_major)))
+        token_major=int(bool(token_major)),
+        route=_native.ROUTE_CODE[FORCED_ROUTE])
     if rotary is not None:
         cos, sin, interleaved = rotary
         args.rotary_cos, args.rotary_sin = cos.data_ptr(), sin.data_ptr()
@@ -79,6 +85,7 @@ def paged_prefill_device(q, kv_cache, cu_seqlens_q, seqused_k, block_table,
     scratch = _native.workspace(device, nbytes)
     args.workspace, args.workspace_bytes = scratch.data_ptr(), scratch.numel()
     _native.check(lib.fw_prefill_paged(ctypes.byref(args), stream))
+    _native.raise_on_status(scratch, device)
     return out, lse
 
 

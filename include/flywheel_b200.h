@@ -49,8 +49,15 @@ extern "C" {
 #define FW_DTYPE_E4M3 1
 #define FW_DTYPE_E5M2 2
 
-/* Device status word written at workspace offset 0 by kernels whose bounded
- * waits gave up; 0 = clean.  Read it with fw_read_status after a sync. */
+/* Device status word at workspace offset 0: the OR of the bits below, 0 = clean.
+ * It stays set until fw_read_status reports and clears it, so it covers every
+ * launch since the last read.  WAIT_TIMEOUT: a bounded device-side wait gave up
+ * and the results of that launch are void.  BAD_PAGE: a block-table entry
+ * outside the pool, or a position past the table row / the contiguous capacity,
+ * was met; reads were clamped to page 0 (that request's output is void) and
+ * an append to such a position stored nothing.  The first 256 bytes of a
+ * workspace belong to this status block and must be zero when the workspace is
+ * first used (afterwards the library maintains them). */
 #define FW_STATUS_OK 0
 #define FW_STATUS_WAIT_TIMEOUT 1
 #define FW_STATUS_BAD_PAGE 2
@@ -120,6 +127,11 @@ typedef struct FwDecodeArgs {
   float softmax_scale;
   float softcap;
   int32_t num_ctas;         /* 0 = pick from the device; tests may pin it */
+  /* NULL, or one device int read by the kernel: 0 makes the call behave as if
+   * k_new / v_new were NULL (nothing appended, the new tokens not attended).
+   * Lets one enqueued or graph-captured call serve steps in which this GPU does
+   * and does not own the page the new token falls in (see fw_shard_step). */
+  const int32_t* append_enable;
 } FwDecodeArgs;
 
 uint64_t fw_decode_workspace_bytes(const FwDecodeArgs* args);
@@ -148,9 +160,18 @@ int fw_decode_kvcache(const FwDecodeArgs* args, void* stream);
  * two calls that overlap on the GPU (different streams, no dependency) race on
  * it, so keep them ordered.  The array keeps the previous call's contents;
  * the entry point clears the status word itself, nothing else needs zeroing.
+ * Read that word with fw_read_status_static (fw_read_status needs a workspace
+ * pointer, which callers of this entry point never hold).
  */
 #define FW_STATIC_SCRATCH_BYTES (32ull << 20)
 int fw_decode_kvcache_static(const FwDecodeArgs* args, void* stream);
+
+/* The status word of the built-in scratch on the current device, copied to
+ * *status (host) after synchronising `stream`, then cleared if it was set.  It
+ * describes the most recent fw_decode_kvcache_static call on that device only,
+ * because each such call starts by clearing the word.  (No counterpart in the
+ * reference.) */
+int fw_read_status_static(void* stream, int32_t* status);
 
 /*
  * Packed new K/V rows -> merged pages (append_ragged, kv_append.py:116-184).
@@ -265,7 +286,16 @@ typedef struct FwPrefillArgs {
   /* Packed K/V in fixed-size request slots instead of cu_seqlens_k: n > 0 puts
    * request r's keys at rows [r * n, r * n + seqused_k[r]) (cu_seqlens_k NULL). */
   int32_t kv_request_stride;
+  /* Which kernel serves a paged call: FW_ROUTE_AUTO lets the library choose by
+   * chunk length (tensor-core kernel for chunks of 64 tokens and more, the
+   * split-KV kernel below that); the other two pin it for this call where the
+   * pinned kernel can take the shapes.  Per call, no process-wide switch. */
+  int32_t route;
 } FwPrefillArgs;
+
+#define FW_ROUTE_AUTO 0
+#define FW_ROUTE_TENSOR_CORE 1
+#define FW_ROUTE_SPLIT_KV 2
 
 uint64_t fw_prefill_workspace_bytes(const FwPrefillArgs* args);
 int fw_prefill_paged(const FwPrefillArgs* args, void* stream);
@@ -353,14 +383,44 @@ typedef struct FwExchangeArgs {
 } FwExchangeArgs;
 
 uint64_t fw_exchange_buffer_bytes(int32_t world, int32_t rows, int32_t head_dim);
+
+/*
+ * Per-step bookkeeping of one request whose logical pages are dealt round-robin
+ * over the GPUs: logical page p lives on GPU p % world as that GPU's local page
+ * p / world, so the growing tail of a long generation keeps moving from GPU to
+ * GPU and every GPU holds the same number of pages to within one.  One thread
+ * reads *global_len (tokens cached before this step) and writes
+ *   *local_len     = how many of those tokens live in this rank's pages (they
+ *                    are a prefix of its local page list), and
+ *   *append_enable = 1 on the rank whose page holds position *global_len (for
+ *                    that rank local_len is exactly the new token's local
+ *                    position), 0 elsewhere,
+ * then adds `advance` to *global_len.  Enqueue it before fw_decode_kvcache
+ * (cache_seqlens = local_len, append_enable as given) every step: the same
+ * captured sequence then serves a whole generation, across page and rank
+ * boundaries.  (No counterpart in the reference, whose library is
+ * single-device.)
+ */
+typedef struct FwShardStepArgs {
+  int32_t* global_len;
+  int32_t* local_len;
+  int32_t* append_enable;
+  int32_t page_size;
+  int32_t world;
+  int32_t rank;
+  int32_t advance;
+} FwShardStepArgs;
+
+int fw_shard_step(const FwShardStepArgs* args, void* stream);
 int fw_peer_alloc(uint64_t bytes, void** ptr, void* handle64);
 int fw_peer_open(const void* handle64, void** ptr);
 int fw_peer_close(void* ptr);
 int fw_peer_free(void* ptr);
 int fw_state_exchange_merge(const FwExchangeArgs* args, void* stream);
 
-/* Copies the device status word at the head of `workspace` to *status (host).
- * Synchronises `stream`; meant for tests and debugging, not the hot path. */
+/* Copies the device status word at the head of `workspace` to *status (host)
+ * and clears it on the device if it was set.  Synchronises `stream`; meant for
+ * tests and debugging, not the hot path. */
 int fw_read_status(const void* workspace, void* stream, int32_t* status);
 
 /* Failure-detection self test: launches one CTA whose bounded wait can never

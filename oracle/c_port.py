@@ -2,7 +2,6 @@
 infrastructure only: the checker and the timed CPU baseline."""
 
 import ctypes
-import os
 import pathlib
 import subprocess
 
@@ -26,11 +25,10 @@ def paged_decode(q, pool, k_new, v_new, cache_seqlens, block_table, *, nheads_k,
                  window_left=None, softcap=0.0, softmax_scale=None, sinks=None, threads=None,
                  in_place=False):
     """Runs the C port.  q (batch, q_len, heads, d), pool merged bf16 (copied
-    unless in_place; the updated pool is returned).  Returns (out f32, lse
+    unless in_place; the updated pool is returned).  threads: OpenMP team size
+    for this call (None = the runtime's own default).  Returns (out f32, lse
     (batch, heads, q_len), pool)."""
     lib = ctypes.CDLL(str(build()))
-    if threads:
-        os.environ["OMP_NUM_THREADS"] = str(threads)
     batch, q_len, heads, d = q.shape
     pool = np.ascontiguousarray(pool) if in_place else np.ascontiguousarray(pool).copy()
     out = np.zeros((batch, q_len, heads, d), np.float32)
@@ -40,10 +38,11 @@ def paged_decode(q, pool, k_new, v_new, cache_seqlens, block_table, *, nheads_k,
             for x in (q, k_new, v_new, np.asarray(cache_seqlens, np.int32), np.asarray(block_table, np.int32),
                       None if sinks is None else np.asarray(sinks, np.float32))]
     scale = d ** -0.5 if softmax_scale is None else softmax_scale
-    lib.fw_ref_paged_decode.argtypes = [ctypes.c_void_p] * 9 + [ctypes.c_int] * 9 + [ctypes.c_float] * 2
+    lib.fw_ref_paged_decode.argtypes = [ctypes.c_void_p] * 9 + [ctypes.c_int] * 9 + [ctypes.c_float] * 2 + [ctypes.c_int]
     lib.fw_ref_paged_decode(
         ptr(keep[0]), pool.ctypes.data_as(ctypes.c_void_p), ptr(keep[1]), ptr(keep[2]), ptr(keep[3]),
         ptr(keep[4]), ptr(keep[5]), out.ctypes.data_as(ctypes.c_void_p), lse.ctypes.data_as(ctypes.c_void_p),
         batch, q_len, heads, nheads_k, d, pool.shape[1], keep[4].shape[1], int(causal),
-        -1 if window_left is None else int(window_left), ctypes.c_float(scale), ctypes.c_float(softcap))
+        -1 if window_left is None else int(window_left), ctypes.c_float(scale), ctypes.c_float(softcap),
+        int(threads or 0))
     return out, lse, pool

@@ -16,6 +16,7 @@
  * Build: gcc -O3 -march=native -fopenmp -shared -fPIC (see oracle/Makefile).
  */
 #include <math.h>
+#include <omp.h>
 #include <stdint.h>
 #include <stdlib.h>
 #include <string.h>
@@ -32,14 +33,17 @@ static inline float bf16_to_f32(uint16_t v) {
  * pool:   (pages, page_size, 2*kv_heads, d) bf16 (updated in place by the append)
  * k_new, v_new: (batch, q_len, kv_heads, d) bf16 or NULL
  * lse:    (batch, heads, q_len) f32 or NULL; sinks: (heads,) f32 or NULL
- * window_left < 0: unbounded.  Returns 0.
+ * window_left < 0: unbounded.  threads > 0 sets the OpenMP team size for this
+ * call (the environment's OMP_NUM_THREADS is read only when the runtime loads,
+ * and launchers such as torchrun set it to 1); 0 leaves it alone.  Returns 0.
  */
 int fw_ref_paged_decode(const uint16_t* q, uint16_t* pool, const uint16_t* k_new, const uint16_t* v_new,
                         const int32_t* cache_seqlens, const int32_t* block_table, const float* sinks,
                         float* out, float* lse, int batch, int q_len, int heads, int kv_heads, int d,
                         int page_size, int pages_per_seq, int causal, int window_left, float scale,
-                        float softcap) {
+                        float softcap, int threads) {
   const int group = heads / kv_heads;
+  if (threads > 0) omp_set_num_threads(threads);
   const size_t row = (size_t)2 * kv_heads * d;
   /* append: whole merged rows, bits moved as they are */
   if (k_new != NULL) {

@@ -7,7 +7,7 @@ import sys
 import pytest
 
 ROOT = pathlib.Path(__file__).resolve().parent.parent
-for path in (ROOT, ROOT / "flywheel-tpu_b200", ROOT / "tests" / "golden"):
+for path in (ROOT, ROOT / "flywheel-tpu_b200", ROOT / "tests", ROOT / "tests" / "golden"):
     if str(path) not in sys.path:
         sys.path.insert(0, str(path))
 

@@ -26,12 +26,30 @@ def test_library_exports_every_declared_symbol():
     assert set(names) == set(_native.EXPORTS), set(names) ^ set(_native.EXPORTS)
 
 
-def test_struct_sizes_match_header_layout():
+def test_struct_layouts_match_the_header(tmp_path):
+    """Every ctypes mirror has the size and the field offsets a C compiler gives
+    the struct declared in the header."""
+    import subprocess
     from flywheel_tpu.softmax_attention import _native
-    # 17 pointers + u64 + i64 + 11 i32/f32 fields + 1 i32 (padded to 8)
-    assert ctypes.sizeof(_native.FwDecodeArgs) == 17 * 8 + 8 + 8 + 14 * 4
-    assert ctypes.sizeof(_native.FwAppendArgs) == 7 * 8 + 8 + 7 * 4 + 4
-    assert ctypes.sizeof(_native.FwCombineArgs) == 5 * 8 + 6 * 4 + 2 * 8
+    structs = ["FwDecodeArgs", "FwAppendArgs", "FwWritePagesArgs", "FwPrefillArgs", "FwCombineArgs",
+               "FwExchangeArgs", "FwShardStepArgs"]
+    lines = ['#include <stddef.h>', '#include <stdio.h>', '#include "flywheel_b200.h"', 'int main(void) {']
+    for name in structs:
+        lines.append(f'  printf("{name} %zu\\n", sizeof({name}));')
+        for field, _ in getattr(_native, name)._fields_:
+            lines.append(f'  printf("{name}.{field} %zu\\n", offsetof({name}, {field}));')
+    lines += ['  return 0;', '}']
+    source = tmp_path / "layout.c"
+    source.write_text("\n".join(lines))
+    binary = tmp_path / "layout"
+    subprocess.run(["gcc", "-I", str(ROOT / "include"), "-o", str(binary), str(source)], check=True)
+    want = dict(line.split() for line in subprocess.run([str(binary)], check=True, capture_output=True,
+                                                        text=True).stdout.splitlines())
+    for name in structs:
+        mirror = getattr(_native, name)
+        assert ctypes.sizeof(mirror) == int(want[name]), name
+        for field, _ in mirror._fields_:
+            assert getattr(mirror, field).offset == int(want[f"{name}.{field}"]), f"{name}.{field}"
 
 
 def test_argument_errors_mirror_reference_exception_types():

@@ -62,7 +62,7 @@ def run_case(case, *, causal=True, window_left=None, softcap=0.0, sinks=None,
 
 
 def host_case(*args, **kwargs):
-    from flywheel_tpu.testing import workloads
+    import paged_cases as workloads
     return workloads.host_case(*args, **kwargs)
 
 

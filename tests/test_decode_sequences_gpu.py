@@ -23,7 +23,7 @@ def test_step_after_step_appends_track_the_oracle():
     for bit after every step."""
     import torch
     from flywheel_tpu import flash_attn_with_kvcache
-    from flywheel_tpu.testing import workloads
+    import paged_cases as workloads
     # pages are allocated for the final lengths, so every appended token has a page of its own request
     case = workloads.host_case(51, lens=(40, 90, 160), hq=8, hk=2, page_size=64, max_pages=4)
     rng = np.random.default_rng(1)
@@ -121,7 +121,7 @@ def test_kv_head_shards_reproduce_the_full_call():
     import torch
     from flywheel_tpu import flash_attn_with_kvcache
     from flywheel_tpu.softmax_attention import distributed as d
-    from flywheel_tpu.testing import workloads
+    import paged_cases as workloads
     from oracle import paged_attention as oracle
     case = workloads.host_case(5, lens=(3, 64, 700, 1500), hq=16, hk=4, page_size=64)
     to_t = lambda a: torch.from_numpy(a.view(np.int16)).cuda().view(torch.bfloat16)

@@ -18,21 +18,30 @@ def free_port():
         return sock.getsockname()[1]
 
 
-def test_page_ranges_cover_and_balance():
+def test_round_robin_pages_cover_and_balance():
     from flywheel_tpu.softmax_attention import distributed as d
     for total in (1, 7, 8, 2049, 2052):
         for world in (1, 2, 4, 8):
-            ranges = [d.page_range(total, world, r) for r in range(world)]
-            assert ranges[0][0] == 0 and ranges[-1][1] == total
-            assert all(a[1] == b[0] for a, b in zip(ranges, ranges[1:]))
-            sizes = [hi - lo for lo, hi in ranges]
+            owned = [list(d.owned_pages(total, world, r)) for r in range(world)]
+            assert sorted(page for pages in owned for page in pages) == list(range(total))
+            sizes = [len(pages) for pages in owned]
             assert max(sizes) - min(sizes) <= 1
             for page in range(0, total, max(1, total // 50)):
-                owner = d.owner_of_page(total, world, page)
-                assert ranges[owner][0] <= page < ranges[owner][1]
-    assert d.local_length(100, 64, 0, 1) == 64
-    assert d.local_length(100, 64, 1, 2) == 36
-    assert d.local_length(100, 64, 2, 3) == 0
+                assert page in owned[d.owner_of_page(page, world)]
+    # a rank's share of the first n tokens, against counting them one by one
+    page = 64
+    for world in (1, 2, 3, 8):
+        for n in (0, 1, 63, 64, 65, 100, 500, 64 * world, 64 * world + 1, 4000):
+            shares = [d.local_length(n, page, world, r) for r in range(world)]
+            brute = [sum(1 for t in range(n) if (t // page) % world == r) for r in range(world)]
+            assert shares == brute
+            assert sum(shares) == n
+    # the growing tail moves from rank to rank: over 8 pages of decode steps on 4
+    # ranks every rank appends two pages' worth
+    appends = [0] * 4
+    for position in range(1000, 1000 + 8 * page):
+        appends[d.owner_of_page(position // page, 4)] += 1
+    assert appends == [2 * page] * 4
 
 
 def _rank_main(rank, world, port, results):
@@ -55,10 +64,12 @@ def _rank_main(rank, world, port, results):
         values = rng.standard_normal((total_pages * page, kv_heads, dim), dtype=np.float32)
         q = rng.standard_normal((1, heads, dim), dtype=np.float32)
         sinks = rng.standard_normal(heads).astype(np.float32)
-        first, last = d.page_range(total_pages, world, rank)
-        local = d.local_length(length, page, first, last)
-        lo = first * page
-        out, lse = oracle.attend_rows(q, keys[lo:lo + local], values[lo:lo + local], total=local,
+        local = d.local_length(length, page, world, rank)
+        # this rank's tokens: its pages in local order, the valid prefix of them
+        mine = np.concatenate([np.arange(p * page, (p + 1) * page)
+                               for p in d.owned_pages(total_pages, world, rank)])[:local]
+        assert np.all(mine < length)
+        out, lse = oracle.attend_rows(q, keys[mine], values[mine], total=local,
                                       causal=False, window_left=None, softcap=0.0,
                                       scale=dim ** -0.5, sinks=None)
         state = d.pack_state(torch.from_numpy(out[0]), torch.from_numpy(lse[:, 0].copy()))
@@ -71,7 +82,7 @@ def _rank_main(rank, world, port, results):
                                             scale=dim ** -0.5, sinks=sinks)
         np.testing.assert_allclose(merged, want[0], rtol=1e-4, atol=1e-6)
         np.testing.assert_allclose(merged_lse, want_lse[:, 0], rtol=1e-5)
-        owner = d.owner_of_page(total_pages, world, length // page)
+        owner = d.owner_of_page(length // page, world)
         results[rank] = (int(local), int(owner))
     finally:
         dist.destroy_process_group()
@@ -83,7 +94,7 @@ def test_sharded_state_gather_and_merge_on_two_cpu_ranks():
     results = manager.dict()
     mp.spawn(_rank_main, args=(world, port, results), nprocs=world, join=True)
     assert results[0][0] + results[1][0] == 500
-    assert results[0][1] == results[1][1] == 1      # page 7 of 9 lives on rank 1
+    assert results[0][1] == results[1][1] == 1      # position 500 is in page 7, an odd page: rank 1
 
 
 def test_kv_head_and_request_sharding_partition_the_work():

@@ -40,26 +40,27 @@ def _rank_main(rank, world, port, results, exchange):
         bf16 = np.dtype(ml_dtypes.bfloat16)
         rng = np.random.default_rng(1)                      # same draws on every rank
         heads, kv_heads, dim, page, total_pages = 16, 2, 128, 64, 11
-        length, steps = 4 * page + 60, 8                    # crosses a page edge and a rank edge
+        length, steps = 4 * page + 60, 8                    # crosses a page edge, so the appending rank changes
         draw = lambda shape: rng.standard_normal(shape, dtype=np.float32).astype(bf16)
         keys, values = draw((total_pages * page, kv_heads, dim)), draw((total_pages * page, kv_heads, dim))
         sinks = rng.standard_normal(heads).astype(np.float32)
-        first, last = d.page_range(total_pages, world, rank)
-        local_pages = last - first
+        owned = np.asarray(d.owned_pages(total_pages, world, rank))
+        local_pages = len(owned)
         perm = np.random.default_rng(10 + rank).permutation(local_pages + 2)[:local_pages]
         pool = np.zeros((local_pages + 2, page, 2 * kv_heads, dim), bf16)
         rows = oracle.merge_kv_heads(keys, values).reshape(total_pages, page, 2 * kv_heads, dim)
-        pool[perm] = rows[first:last]
+        pool[perm] = rows[owned]
         pool_t = torch.from_numpy(pool.view(np.int16)).to(device).view(torch.bfloat16)
         table = torch.from_numpy(perm.astype(np.int32)[None]).to(device)
-        decoder = d.ShardedDecoder(pool=pool_t, table=table, total_pages=total_pages, nheads=heads,
+        decoder = d.ShardedDecoder(pool=pool_t, table=table, nheads=heads,
                                    nheads_k=kv_heads, sinks=torch.from_numpy(sinks).to(device),
                                    exchange=exchange)
         to_t = lambda a: torch.from_numpy(a.view(np.int16)).to(device).view(torch.bfloat16)
         worst = 0.0
         for step in range(steps):
             q, k, v = draw((1, 1, heads, dim)), draw((1, 1, kv_heads, dim)), draw((1, 1, kv_heads, dim))
-            out, lse = decoder.step(to_t(q), to_t(k), to_t(v), length)
+            # the first step sets the cached length; afterwards the device counter carries on
+            out, lse = decoder.step(to_t(q), to_t(k), to_t(v), length if step == 0 else None)
             torch.cuda.synchronize()
             keys[length], values[length] = k[0, 0], v[0, 0]
             length += 1
@@ -74,18 +75,23 @@ def _rank_main(rank, world, port, results, exchange):
         # appended rows landed bit-exact on the owning rank only
         got_pool = pool_t.cpu().view(torch.int16).numpy()
         want_rows = oracle.merge_kv_heads(keys, values).reshape(total_pages, page, 2 * kv_heads, dim)
-        np.testing.assert_array_equal(got_pool[perm], want_rows[first:last].view(np.int16))
+        np.testing.assert_array_equal(got_pool[perm], want_rows[owned].view(np.int16))
         # the same step replayed as a CUDA graph: the cached length lives on the device
         # (peer-store exchange only: a capture right after eager NCCL work trips over
         # the process group's watchdog thread, which is not this library's concern)
         q, k, v = draw((1, 1, heads, dim)), draw((1, 1, kv_heads, dim)), draw((1, 1, kv_heads, dim))
         q_t, k_t, v_t = to_t(q), to_t(k), to_t(v)
-        graph = decoder.capture(q_t, k_t, v_t, length, 3) if exchange == "p2p" else None
-        for _ in range(3 if graph is not None else 0):
+        # 70 replays of one graph: the position crosses a page edge again, so the
+        # appending rank changes under the captured launches
+        replays = 70
+        graph = decoder.capture(q_t, k_t, v_t, length) if exchange == "p2p" else None
+        for replay in range(replays if graph is not None else 0):
             graph.replay()
             torch.cuda.synchronize()
             keys[length], values[length] = k[0, 0], v[0, 0]
             length += 1
+            if replay % 23 and replay != replays - 1:
+                continue
             want, _ = oracle.attend_rows(
                 q[0].astype(np.float32), keys[:length].astype(np.float32),
                 values[:length].astype(np.float32), total=length, causal=True, window_left=None,

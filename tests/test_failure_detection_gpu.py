@@ -12,7 +12,7 @@ def test_bounded_wait_runs_out_and_reports_status():
     import torch
     from flywheel_tpu import flash_attn_with_kvcache
     from flywheel_tpu.softmax_attention import _native
-    from flywheel_tpu.testing import workloads
+    import paged_cases as workloads
     from oracle import paged_attention as oracle
     lib = _native.library()
     dev = torch.device("cuda", torch.cuda.current_device())
@@ -38,7 +38,7 @@ def test_bad_page_id_is_reported_not_dereferenced():
     import ctypes
     import torch
     from flywheel_tpu.softmax_attention import _native
-    from flywheel_tpu.testing import workloads
+    import paged_cases as workloads
     case = workloads.host_case(32, lens=(200,), hq=8, hk=2)
     table = case.block_table.copy()
     table[0, 1] = 10 ** 6

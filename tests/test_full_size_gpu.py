@@ -18,7 +18,7 @@ def test_serving_scale_decode_properties():
     from flywheel_tpu.softmax_attention import _arrays, _native
     from oracle import paged_attention as oracle
     dev = torch.device("cuda", torch.cuda.current_device())
-    work = bench.build_workload(seed=0, device=dev)
+    work = bench.build_workload(0, dev)
     pool, lens, table = work["pool"], work["lens"], work["table"]
     dv = work["dev"]
     lens_l = torch.from_numpy(lens.astype(np.int64)).to(dev)
@@ -28,10 +28,10 @@ def test_serving_scale_decode_properties():
     bits = lambda t: t.contiguous().view(torch.int16).to(torch.int64)
     before = sum(int(bits(pool[lo:lo + 4096]).sum()) for lo in range(0, pool.shape[0], 4096))
 
-    call, out, scratch = bench.make_decode_call(work, dev)
+    (call, status), out = bench.make_decode_call(work, dev)
     call()
     torch.cuda.synchronize()
-    assert _native.read_status(scratch, dev) == 0
+    assert status() == 0
     after = sum(int(bits(pool[lo:lo + 4096]).sum()) for lo in range(0, pool.shape[0], 4096))
     new_rows = torch.stack([dv["k"][:, 0], dv["v"][:, 0]], dim=2).reshape(bench.BATCH, 2 * bench.HK, bench.D)
     assert torch.equal(pool[pages, slots].view(torch.int16), new_rows.view(torch.int16))
@@ -77,8 +77,7 @@ def test_chunked_prefill_kernels_agree_at_full_size(monkeypatch):
     work = bench.build_prefill_workload(0, dev)
     results = {}
     for kernel in ("tcgen05", "splitkv"):
-        monkeypatch.setenv("FLYWHEEL_PREFILL_KERNEL", kernel)
-        call, out, scratch = bench.make_prefill_call(work, dev)
+        call, out, scratch = bench.make_prefill_call(work, dev, route=kernel)
         call()
         torch.cuda.synchronize()
         assert _native.read_status(scratch, dev) == 0

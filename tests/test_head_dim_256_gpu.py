@@ -105,7 +105,7 @@ def test_contiguous_pair():
 @pytest.mark.parametrize("rotary", [False, True])
 def test_chunked_prefill(hq, hk, rotary, kernel, monkeypatch):
     from flywheel_tpu import flash_attn_varlen_func
-    monkeypatch.setenv("FLYWHEEL_PREFILL_KERNEL", kernel)
+    monkeypatch.setattr("flywheel_tpu.softmax_attention.prefill.FORCED_ROUTE", kernel)
     rng = np.random.default_rng(23)
     page = 128
     prefixes, chunks = (0, 300, 1000, 77), (200, 64, 130, 1)
@@ -188,7 +188,7 @@ def test_chunked_prefill_fp8_pool(kind, kernel, monkeypatch):
     """fp8 pools at head_dim 256: widened into bf16 scratch and run on the
     tensor-core kernel, or read in place by the split-KV kernel."""
     from flywheel_tpu import flash_attn_varlen_func
-    monkeypatch.setenv("FLYWHEEL_PREFILL_KERNEL", kernel)
+    monkeypatch.setattr("flywheel_tpu.softmax_attention.prefill.FORCED_ROUTE", kernel)
     dtype = oracle.E4M3 if kind == "e4m3" else oracle.E5M2
     rng = np.random.default_rng(29)
     hq, hk, page = 8, 2, 64

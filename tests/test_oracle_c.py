@@ -10,7 +10,7 @@ from oracle import paged_attention as oracle
 @pytest.mark.parametrize("kwargs", [
     dict(), dict(window_left=40, softcap=30.0), dict(sinks=True), dict(q_len=4), dict(append=False)])
 def test_c_port_matches_numpy_oracle(kwargs):
-    from flywheel_tpu.testing import workloads
+    import paged_cases as workloads
     q_len = kwargs.get("q_len", 1)
     case = workloads.host_case(41, lens=(0, 63, 64, 300), q_len=q_len, hq=8, hk=2)
     rng = np.random.default_rng(2)

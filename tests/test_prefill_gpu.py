@@ -22,7 +22,7 @@ GOLDEN_DIR = pathlib.Path(cases.__file__).resolve().parent
 def prefill_kernel(request, monkeypatch):
     """Every case runs once per prefill kernel; shapes the tensor-core kernel
     does not take (fp8 pools, odd GQA groups) stay on the split-KV kernel."""
-    monkeypatch.setenv("FLYWHEEL_PREFILL_KERNEL", request.param)
+    monkeypatch.setattr("flywheel_tpu.softmax_attention.prefill.FORCED_ROUTE", request.param)
     return request.param
 
 
@@ -164,7 +164,7 @@ def test_multi_token_batch_call_takes_prefill_route():
     """A (batch, seqlen_q, ...) call too tall for the decode kernel's query
     tile appends and runs the packed kernel."""
     from flywheel_tpu import flash_attn_with_kvcache
-    from flywheel_tpu.testing import workloads
+    import paged_cases as workloads
     case = workloads.host_case(15, lens=(0, 100, 777), q_len=48, hq=32, hk=8)
     pool_t = to_cuda(case.pool)
     out, lse, _ = flash_attn_with_kvcache(

@@ -38,7 +38,7 @@ def decode_args(case, tensors, out, lse):
 def test_static_scratch_entry_matches_workspace_entry_twice():
     import torch
     from flywheel_tpu.softmax_attention import _native
-    from flywheel_tpu.testing import workloads
+    import paged_cases as workloads
     lib = _native.library()
     dev = torch.device("cuda", torch.cuda.current_device())
     for seed, lens in ((21, (700, 0, 3000, 65, 1290)), (22, (15, 2500, 64, 9, 4000))):
