@@ -167,6 +167,50 @@ __device__ __forceinline__ uint32_t fp8x2_to_f16x2(uint16_t v) {
   }
   return r;
 }
+// The two fp8 values in the low (kHigh = false) or high half of a 32-bit word
+// -> f16x2.  e5m2 is the top byte of an f16 (same sign, exponent and bias, two
+// mantissa bits), so widening it is a byte placement: one prmt, no conversion,
+// NaN and infinity patterns included.
+template <int KVT, bool kHigh>
+__device__ __forceinline__ uint32_t fp8_half_to_f16x2(uint32_t word) {
+  if constexpr (KVT == FW_DTYPE_E5M2) {
+    // result bytes (low to high): 0, b0, 0, b1 (or b2, b3); selector 4 picks a zero byte of the second operand
+    return __byte_perm(word, 0u, kHigh ? 0x3424 : 0x1404);
+  } else {
+    return fp8x2_to_f16x2<KVT>(static_cast<uint16_t>(kHigh ? word >> 16 : word & 0xffffu));
+  }
+}
+
+// Packed f32x2 arithmetic (two lanes per instruction on sm_100) and packed
+// bf16x2 max: they halve the issue slots the softmax spends around each exp2.
+__device__ __forceinline__ uint64_t pack2(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack2(uint64_t v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+  return r;
+}
+__device__ __forceinline__ uint64_t mul2(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ uint32_t max_bf16x2(uint32_t a, uint32_t b) {
+  uint32_t r;
+  asm("max.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+  return r;
+}
 
 // Records a failure in the device status word.  The codes are distinct bits and
 // the word is their OR, so a clamped page id reported by an earlier launch does

@@ -29,6 +29,9 @@
 namespace fw {
 
 constexpr int kTile = 16;          // smallest stage: tokens per MMA k-step; page sizes are multiples of it
+#ifndef FW_VERIFY_STAGE_TOKENS
+#define FW_VERIFY_STAGE_TOKENS 32  // fp8 stage size when two or more warps share a KV head (16, 32 or 64)
+#endif
 constexpr int kMaxStages = 8;
 constexpr int kMaxConsumerWarps = 8;
 constexpr int kMaxHeadDim = 256;   // head_dim 128 and 256 are built
@@ -166,8 +169,11 @@ __device__ __forceinline__ int v_seg(const DecodeParams& p, int hl) {
 
 // D = head_dim.  At 256 a thread carries 128 output and 64 query registers, so
 // the block is sized for four consumer warps instead of eight.
+// The register cap is what the block size allows with one CTA per SM (65536 /
+// 288 threads, 65536 / 160 threads capped at 255); given outright because the
+// compiler's own choice under __launch_bounds__ stopped at 168 and spilled.
 template <int KVT, int TILE, int D = 128>
-__global__ void __launch_bounds__(((D > 128 ? kMaxConsumerWarps / 2 : kMaxConsumerWarps) + 1) * 32, 1)
+__global__ void __maxnreg__(D > 128 ? 255 : 224)
 decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
               const DecodeParams p) {
   constexpr bool kFp8 = KVT != FW_DTYPE_BF16;
@@ -455,25 +461,42 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
                                 (((chunk & 7) ^ (key & 7)) << 4);
           uint32_t r0, r1, r2, r3;  // (keys 0-7, c), (keys 8-15, c), (keys 0-7, c+1), (keys 8-15, c+1)
           ldmatrix_x4(addr, r0, r1, r2, r3);
-          mma_f16(s[u][0], qa[2 * kp], fp8x2_to_f16x2<KVT>(r0 & 0xffff), fp8x2_to_f16x2<KVT>(r0 >> 16));
-          mma_f16(s[u][1], qa[2 * kp], fp8x2_to_f16x2<KVT>(r1 & 0xffff), fp8x2_to_f16x2<KVT>(r1 >> 16));
-          mma_f16(s[u][0], qa[2 * kp + 1], fp8x2_to_f16x2<KVT>(r2 & 0xffff), fp8x2_to_f16x2<KVT>(r2 >> 16));
-          mma_f16(s[u][1], qa[2 * kp + 1], fp8x2_to_f16x2<KVT>(r3 & 0xffff), fp8x2_to_f16x2<KVT>(r3 >> 16));
+          mma_f16(s[u][0], qa[2 * kp], fp8_half_to_f16x2<KVT, false>(r0), fp8_half_to_f16x2<KVT, true>(r0));
+          mma_f16(s[u][1], qa[2 * kp], fp8_half_to_f16x2<KVT, false>(r1), fp8_half_to_f16x2<KVT, true>(r1));
+          mma_f16(s[u][0], qa[2 * kp + 1], fp8_half_to_f16x2<KVT, false>(r2), fp8_half_to_f16x2<KVT, true>(r2));
+          mma_f16(s[u][1], qa[2 * kp + 1], fp8_half_to_f16x2<KVT, false>(r3), fp8_half_to_f16x2<KVT, true>(r3));
         }
       }
       }
 
-      // ---- scale (+ softcap), mask
+      // ---- scale (+ softcap), mask.  With a softcap the logit is
+      // c2 * tanh(s * c1) = c2 - 2 c2 / (2^(s * c1 * 2 log2e) + 1): the constants
+      // are folded so a score costs mul, min, ex2, add, rcp, fma, and the
+      // multiplies / adds run two scores per instruction (f32x2).
+      if (p.softcap > 0.f) {
+        const float a = c1 * (2.0f * kLog2e), m2c2 = -2.0f * c2;
+        const uint64_t a2 = pack2(a, a), one2 = pack2(1.f, 1.f), m2c22 = pack2(m2c2, m2c2), c22 = pack2(c2, c2);
 #pragma unroll
-      for (int u = 0; u < NU; ++u)
+        for (int u = 0; u < NU; ++u)
 #pragma unroll
-      for (int nt = 0; nt < 2; ++nt)
+          for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          float x = s[u][nt][i] * c1;
-          if (p.softcap > 0.f) x = accurate_tanh(x) * c2;
-          s[u][nt][i] = x;
-        }
+            for (int i = 0; i < 4; i += 2) {
+              float x0, x1;
+              unpack2(mul2(pack2(s[u][nt][i], s[u][nt][i + 1]), a2), x0, x1);
+              const float e0 = fast_exp2(fminf(x0, 80.0f)), e1 = fast_exp2(fminf(x1, 80.0f));
+              float d0, d1;
+              unpack2(add2(pack2(e0, e1), one2), d0, d1);
+              unpack2(fma2(pack2(fast_rcp(d0), fast_rcp(d1)), m2c22, c22), s[u][nt][i], s[u][nt][i + 1]);
+            }
+      } else {
+#pragma unroll
+        for (int u = 0; u < NU; ++u)
+#pragma unroll
+          for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) s[u][nt][i] *= c1;
+      }
       const bool mask_right = pos0 + TILE > min(sp.diag_base, sp.kv_end);
       const bool mask_left = p.window_left >= 0 && pos0 < sp.total - 1 - p.window_left;
       if (mask_right || mask_left) {
@@ -491,7 +514,8 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
           }
       }
 
-      // ---- online softmax (rows quad and quad + 8)
+      // ---- online softmax (rows quad and quad + 8); the subtraction of the row
+      // base and the row sum run two scores per instruction
       float alpha[2];
 #pragma unroll
       for (int r = 0; r < 2; ++r) {
@@ -505,16 +529,21 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
         const float base = m_new == -INFINITY ? 0.f : m_new;
         alpha[r] = fast_exp2(m_run[r] - base);
         m_run[r] = m_new;
-        float sum = 0.f;
+        const uint64_t nbase2 = pack2(-base, -base);
+        uint64_t sum2 = pack2(0.f, 0.f);
 #pragma unroll
         for (int u = 0; u < NU; ++u)
 #pragma unroll
         for (int nt = 0; nt < 2; ++nt) {
-          s[u][nt][2 * r] = fast_exp2(s[u][nt][2 * r] - base);
-          s[u][nt][2 * r + 1] = fast_exp2(s[u][nt][2 * r + 1] - base);
-          sum += s[u][nt][2 * r] + s[u][nt][2 * r + 1];
+          float y0, y1;
+          unpack2(add2(pack2(s[u][nt][2 * r], s[u][nt][2 * r + 1]), nbase2), y0, y1);
+          s[u][nt][2 * r] = fast_exp2(y0);
+          s[u][nt][2 * r + 1] = fast_exp2(y1);
+          sum2 = add2(sum2, pack2(s[u][nt][2 * r], s[u][nt][2 * r + 1]));
         }
-        l_run[r] = l_run[r] * alpha[r] + sum;
+        float sum_lo, sum_hi;
+        unpack2(sum2, sum_lo, sum_hi);
+        l_run[r] = l_run[r] * alpha[r] + (sum_lo + sum_hi);
       }
       if (__any_sync(0xffffffffu, alpha[0] != 1.f || alpha[1] != 1.f)) {
 #pragma unroll
@@ -567,10 +596,10 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
           r1 = __byte_perm(r1, 0, 0x3120);
           r2 = __byte_perm(r2, 0, 0x3120);
           r3 = __byte_perm(r3, 0, 0x3120);
-          mma_f16(o[4 * cp + 0], pa, fp8x2_to_f16x2<KVT>(r0 & 0xffff), fp8x2_to_f16x2<KVT>(r1 & 0xffff));
-          mma_f16(o[4 * cp + 1], pa, fp8x2_to_f16x2<KVT>(r0 >> 16), fp8x2_to_f16x2<KVT>(r1 >> 16));
-          mma_f16(o[4 * cp + 2], pa, fp8x2_to_f16x2<KVT>(r2 & 0xffff), fp8x2_to_f16x2<KVT>(r3 & 0xffff));
-          mma_f16(o[4 * cp + 3], pa, fp8x2_to_f16x2<KVT>(r2 >> 16), fp8x2_to_f16x2<KVT>(r3 >> 16));
+          mma_f16(o[4 * cp + 0], pa, fp8_half_to_f16x2<KVT, false>(r0), fp8_half_to_f16x2<KVT, false>(r1));
+          mma_f16(o[4 * cp + 1], pa, fp8_half_to_f16x2<KVT, true>(r0), fp8_half_to_f16x2<KVT, true>(r1));
+          mma_f16(o[4 * cp + 2], pa, fp8_half_to_f16x2<KVT, false>(r2), fp8_half_to_f16x2<KVT, false>(r3));
+          mma_f16(o[4 * cp + 3], pa, fp8_half_to_f16x2<KVT, true>(r2), fp8_half_to_f16x2<KVT, true>(r3));
         }
       }
       }
@@ -944,7 +973,7 @@ static int plan_decode(const FwDecodeArgs* a, DecodePlan* plan, int max_batch = 
   const int smem_for_stages = 200 * 1024;
   if (itemsize == 1) {
     // Verify windows (two or more 16-row slices per head) measured best at 32.
-    const int max_tile = a->head_dim > 128 ? kTile : mt >= 2 ? 32 : 64;
+    const int max_tile = a->head_dim > 128 ? kTile : mt >= 2 ? FW_VERIFY_STAGE_TOKENS : 64;
     while (p.tile < max_tile && segs_per_stage * (p.tile * 2) * 128 <= 64 * 1024 && a->page_size % (p.tile * 2) == 0)
       p.tile *= 2;
   }

@@ -131,32 +131,6 @@ __host__ __device__ constexpr uint32_t instr_desc(int n, bool b_mn_major) {
          (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(kBM >> 4) << 24);
 }
 
-// Packed f32x2 arithmetic (two lanes per instruction on sm_100) and packed
-// bf16x2 max: they halve the issue slots the softmax spends around each exp2.
-__device__ __forceinline__ uint64_t pack2(float lo, float hi) {
-  uint64_t r;
-  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
-  return r;
-}
-__device__ __forceinline__ void unpack2(uint64_t v, float& lo, float& hi) {
-  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
-}
-__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
-  uint64_t r;
-  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
-  return r;
-}
-__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
-  uint64_t r;
-  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
-  return r;
-}
-__device__ __forceinline__ uint32_t max_bf16x2(uint32_t a, uint32_t b) {
-  uint32_t r;
-  asm("max.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
-  return r;
-}
-
 // Pass 1 of the softmax over one 64-key row: optional softcap (scores become
 // log2-unit logits in place), optional mask (-inf in place), returns the row
 // max of what is left in `sr` (raw scores without a softcap).

@@ -40,8 +40,7 @@ def load_reference_functions(reference_root):
     return scope["ragged_reference"]
 
 
-def digest(pages_f32):
-    bits = np.ascontiguousarray(pages_f32.astype(cases.BF16)).view(np.uint16)
+def digest(bits):
     return np.frombuffer(hashlib.sha256(bits.tobytes()).digest(), np.uint8)
 
 
@@ -52,17 +51,21 @@ def main():
     ragged_reference = load_reference_functions(reference_root)
     for name in cases.CASES:
         c = cases.build(name)
+        # fp8 cases: the reference's oracle is handed stored * descale, as its own
+        # fp8 tests do (tests/softmax_attention/test_prefill.py:614-625)
+        k_pages, v_pages, k_new, v_new = cases.dequantized(c)
         out, lse, kc, vc, _ = ragged_reference(
-            c["q"], c["k_pages"], c["v_pages"], c["k"], c["v"], c["cu"],
+            c["q"], k_pages, v_pages, k_new, v_new, c["cu"],
             c["lengths"], c["table"], causal=c["causal"],
             window_left=c["window_left"], softcap=c["softcap"],
             sinks=c["sinks"])
         np.savez_compressed(
             HERE / f"{name}.npz", out=out.astype(np.float32),
             lse=lse.astype(np.float32),
-            # The appended pages are bf16-exact; a digest of their 16-bit
-            # patterns pins them bit for bit without storing the pools.
-            k_pages_sha256=digest(kc), v_pages_sha256=digest(vc))
+            # The appended pages are exact in the cache type; a digest of their
+            # bit patterns pins them bit for bit without storing the pools.
+            k_pages_sha256=digest(cases.stored_bits(kc, c, "k")),
+            v_pages_sha256=digest(cases.stored_bits(vc, c, "v")))
         print(name, out.shape, float(np.abs(out).max()))
 
 

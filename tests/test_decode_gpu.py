@@ -113,6 +113,18 @@ def test_decode_sinks():
     run_case(host_case(8, lens=(0, 0, 9)), sinks=sinks, append=False)
 
 
+@pytest.mark.parametrize("q_len", [1, 4])
+def test_decode_sinks_leave_inactive_rows_alone(q_len):
+    """Rows of requests past num_active are not attention rows: out 0 and lse
+    -inf even when sinks are given (decode.py:600-617 of the reference masks the
+    lse of inactive rows to -inf)."""
+    rng = np.random.default_rng(10)
+    sinks = rng.uniform(-2, 8, 8).astype(np.float32)
+    case = host_case(10, lens=(40, 0, 100, 9, 0), q_len=q_len)
+    run_case(case, sinks=sinks, num_active=3)
+    run_case(case, sinks=sinks, num_active=3, append=False)
+
+
 @pytest.mark.parametrize("q_len,hq,hk", [(4, 32, 8), (16, 32, 8), (16, 8, 1), (3, 6, 3), (2, 64, 8)])
 def test_verify_window_on_decode_kernel(q_len, hq, hk):
     case = host_case(9, lens=(0, 60, 61, 64, 127, 129, 700), q_len=q_len, hq=hq, hk=hk)
@@ -137,26 +149,40 @@ def test_decode_fp8_poisoned():
     run_case(case, tol=FP8_TOL)
 
 
-def test_golden_single_token_and_verify_cases():
+@pytest.mark.parametrize("name,q_len", [("page64_gqa8", 1), ("verify4_window", 4),
+                                        ("fp8_e4m3_pow2_decode", 1), ("fp8_e4m3_amax_verify4", 4)])
+def test_golden_single_token_and_verify_cases(name, q_len):
+    """The decode kernel (single token and folded verify window) on the golden
+    cases whose requests all have q_len tokens; outputs come from the reference's
+    own NumPy oracle.  The fp8 ones include the serving verify-window setting in
+    small (window 4095, softcap 50, sinks, 4 query tokens, amax descales)."""
     import torch
     from flywheel_tpu import flash_attn_with_kvcache
-    for name, q_len in (("page64_gqa8", 1), ("verify4_window", 4)):
-        c = cases.build(name)
-        golden = np.load(f"{cases.__file__.rsplit('/', 1)[0]}/{name}.npz")
-        batch = len(c["lengths"])
-        pool = oracle.merge_kv_heads(c["k_pages"], c["v_pages"])
-        pool_t = torch.from_numpy(pool.view(np.int16)).cuda().view(torch.bfloat16)
-        shape = (batch, q_len, -1, 128)
-        out, lse, _ = flash_attn_with_kvcache(
-            c["q"].reshape(shape), pool_t, None, c["k"].reshape(shape),
-            c["v"].reshape(shape), cache_seqlens=c["lengths"],
-            block_table=c["table"], causal=c["causal"], softcap=c["softcap"],
-            window_size=(-1 if c["window_left"] is None else c["window_left"], -1),
-            learnable_sink=c["sinks"], return_softmax_lse=True)
-        want = golden["out"].reshape(out.shape)
-        np.testing.assert_allclose(out.astype(np.float32), want, **BF16_TOL)
-        want_lse = golden["lse"].reshape(-1, batch, q_len).transpose(1, 0, 2)
-        np.testing.assert_allclose(lse, want_lse, **LSE_TOL)
+    from flywheel_tpu.softmax_attention import _arrays
+    c = cases.build(name)
+    golden = np.load(f"{cases.__file__.rsplit('/', 1)[0]}/{name}.npz")
+    batch = len(c["lengths"])
+    fp8 = c["kv_dtype"] != oracle.BF16
+    pool = oracle.merge_kv_heads(c["k_pages"], c["v_pages"])
+    carrier = np.uint8 if fp8 else np.int16
+    torch_dtype = {oracle.BF16: torch.bfloat16, oracle.E4M3: torch.float8_e4m3fn,
+                   oracle.E5M2: torch.float8_e5m2}[c["kv_dtype"]]
+    pool_t = torch.from_numpy(pool.view(carrier)).cuda().view(torch_dtype)
+    shape = (batch, q_len, -1, 128)
+    extra = dict(k_descale=c["k_descale"], v_descale=c["v_descale"], nheads_k=c["kv_heads"]) if fp8 else {}
+    out, lse, new_pool = flash_attn_with_kvcache(
+        c["q"].reshape(shape), pool_t, None, c["k"].reshape(shape),
+        c["v"].reshape(shape), cache_seqlens=c["lengths"],
+        block_table=c["table"], causal=c["causal"], softcap=c["softcap"],
+        window_size=(-1 if c["window_left"] is None else c["window_left"], -1),
+        learnable_sink=c["sinks"], return_softmax_lse=True, **extra)
+    want = golden["out"].reshape(out.shape)
+    np.testing.assert_allclose(out.astype(np.float32), want, **(FP8_TOL if fp8 else BF16_TOL))
+    want_lse = golden["lse"].reshape(-1, batch, q_len).transpose(1, 0, 2)
+    np.testing.assert_allclose(lse, want_lse, **LSE_TOL)
+    want_pool = oracle.append_to_pool(pool, c["k"], c["v"], c["cu"], c["lengths"], c["table"],
+                                      nheads_k=c["kv_heads"])
+    np.testing.assert_array_equal(_arrays.to_host_numpy(new_pool).view(carrier), want_pool.view(carrier))
 
 
 def test_contiguous_pair_with_cache_batch_idx():

@@ -19,7 +19,8 @@ def load(name):
 
 
 def digest(pages):
-    bits = np.ascontiguousarray(pages).view(np.uint16)
+    carrier = np.uint16 if pages.dtype.itemsize == 2 else np.uint8
+    bits = np.ascontiguousarray(pages).view(carrier)
     return np.frombuffer(hashlib.sha256(bits.tobytes()).digest(), np.uint8)
 
 
@@ -31,13 +32,13 @@ def run_oracle(case):
             case["q"], pool, case["k"], case["v"], lengths, case["table"],
             nheads_k=case["kv_heads"], cu_seqlens_q=cu, causal=case["causal"],
             window_left=case["window_left"], softcap=case["softcap"],
-            sinks=case["sinks"])
+            sinks=case["sinks"], k_descale=case["k_descale"], v_descale=case["v_descale"])
     else:
         out, lse = oracle.ragged_paged_attention(
             case["q"], pool, cu, lengths, case["table"],
             nheads_k=case["kv_heads"], causal=case["causal"],
             window_left=case["window_left"], softcap=case["softcap"],
-            sinks=case["sinks"])
+            sinks=case["sinks"], k_descale=case["k_descale"], v_descale=case["v_descale"])
         new_pool = pool
     return out, lse, new_pool
 

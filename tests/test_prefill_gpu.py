@@ -44,13 +44,28 @@ def check_rows(out, lse, want, want_lse, tol):
     np.testing.assert_allclose(lse[finite], want_lse[finite], **LSE_TOL)
 
 
+def fp8_kwargs(c):
+    """Descales and the KV head count an fp8 golden case needs (an fp8 pool's
+    head axis may carry a pad head, so nheads_k is always passed)."""
+    if c["kv_dtype"] == oracle.BF16:
+        return {}
+    return dict(k_descale=c["k_descale"], v_descale=c["v_descale"], nheads_k=c["kv_heads"])
+
+
+def bits(array):
+    return np.ascontiguousarray(array).view(np.uint16 if array.dtype.itemsize == 2 else np.uint8)
+
+
 @pytest.mark.parametrize("name", sorted(cases.CASES))
 def test_packed_kvcache_call_matches_golden(name):
-    """flash_attn_with_kvcache with cu_seqlens_q: append, then attend."""
+    """flash_attn_with_kvcache with cu_seqlens_q: append, then attend.  The
+    golden outputs come from the reference's own NumPy oracle (fp8 cases: fed
+    stored * descale, as the reference's fp8 tests do)."""
     from flywheel_tpu import flash_attn_with_kvcache
     from flywheel_tpu.softmax_attention import _arrays
     c = cases.build(name)
     golden = np.load(GOLDEN_DIR / f"{name}.npz")
+    tol = OUT_TOL if c["kv_dtype"] == oracle.BF16 else FP8_TOL
     pool = oracle.merge_kv_heads(c["k_pages"], c["v_pages"])
     pool_t = to_cuda(pool)
     max_q = max(1, int(np.diff(c["cu"]).max(initial=0)))
@@ -59,14 +74,14 @@ def test_packed_kvcache_call_matches_golden(name):
         block_table=c["table"], cu_seqlens_q=c["cu"], max_seqlen_q=max_q,
         causal=c["causal"], softcap=c["softcap"],
         window_size=(-1 if c["window_left"] is None else c["window_left"], -1),
-        learnable_sink=c["sinks"], return_softmax_lse=True)
-    check_rows(out.astype(np.float32), lse, golden["out"], golden["lse"], OUT_TOL)
+        learnable_sink=c["sinks"], return_softmax_lse=True, **fp8_kwargs(c))
+    check_rows(out.astype(np.float32), lse, golden["out"], golden["lse"], tol)
     end = int(c["cu"][-1])
     assert not out[end:].astype(np.float32).any()            # packed padding
     assert np.isneginf(lse[:, end:]).all()
-    want_pool = oracle.append_to_pool(pool, c["k"], c["v"], c["cu"], c["lengths"], c["table"])
-    np.testing.assert_array_equal(
-        _arrays.to_host_numpy(new_pool).view(np.uint16), want_pool.view(np.uint16))
+    want_pool = oracle.append_to_pool(pool, c["k"], c["v"], c["cu"], c["lengths"], c["table"],
+                                      nheads_k=c["kv_heads"])
+    np.testing.assert_array_equal(bits(_arrays.to_host_numpy(new_pool)), bits(want_pool))
 
 
 @pytest.mark.parametrize("name", sorted(cases.CASES))
@@ -75,10 +90,12 @@ def test_varlen_func_reads_pool_matches_golden(name):
     from flywheel_tpu import flash_attn_varlen_func
     c = cases.build(name)
     golden = np.load(GOLDEN_DIR / f"{name}.npz")
+    tol = OUT_TOL if c["kv_dtype"] == oracle.BF16 else FP8_TOL
     pool = oracle.merge_kv_heads(c["k_pages"], c["v_pages"])
     seqused = c["lengths"].copy()
     if c["k"] is not None:
-        pool = oracle.append_to_pool(pool, c["k"], c["v"], c["cu"], c["lengths"], c["table"])
+        pool = oracle.append_to_pool(pool, c["k"], c["v"], c["cu"], c["lengths"], c["table"],
+                                     nheads_k=c["kv_heads"])
         seqused = c["lengths"] + np.diff(c["cu"]).astype(np.int32)
     before = pool.copy()
     pool_t = to_cuda(pool)
@@ -88,10 +105,10 @@ def test_varlen_func_reads_pool_matches_golden(name):
         max(1, int(seqused.max(initial=0))), causal=c["causal"], softcap=c["softcap"],
         window_size=(-1 if c["window_left"] is None else c["window_left"], -1),
         learnable_sink=c["sinks"], return_softmax_lse=True, block_table=c["table"],
-        seqused_k=seqused)
-    check_rows(out.astype(np.float32).transpose(1, 0, 2), lse, golden["out"], golden["lse"], OUT_TOL)
+        seqused_k=seqused, **fp8_kwargs(c))
+    check_rows(out.astype(np.float32).transpose(1, 0, 2), lse, golden["out"], golden["lse"], tol)
     from flywheel_tpu.softmax_attention import _arrays
-    np.testing.assert_array_equal(_arrays.to_host_numpy(pool_t).view(np.uint16), before.view(np.uint16))
+    np.testing.assert_array_equal(bits(_arrays.to_host_numpy(pool_t)), bits(before))
 
 
 def random_prefill_case(seed, prefixes, chunks, hq, hk, page_size, dtype=oracle.BF16, padding=5):
@@ -158,6 +175,68 @@ def test_varlen_func_fp8(dtype):
         c["q"], c["pool"], c["cu"], c["seqused"], c["table"], nheads_k=3, causal=True,
         k_descale=c["kd"], v_descale=c["vd"])
     check_rows(out.astype(np.float32).transpose(1, 0, 2), lse, want, want_lse, FP8_TOL)
+
+
+@pytest.mark.parametrize("window_left", [None, 700])
+def test_needle_probes_at_tile_and_page_edges(window_left):
+    """The needle-probe construction of the reference's paged tests
+    (tests/softmax_attention/test_paged.py:698-848 of the reference project) on
+    the prefill kernels: unit-norm key codes, every (row, head) query aimed with
+    a 20-nat logit at one visible position - the row's own, the one before it, a
+    position next to a 16 / 64 / 128 / 256 / 512 / 1024-token tile or page edge,
+    or a random one - and, on every third row, ALSO at the first hidden key.
+    The output is the target's value row unless a key is mis-masked, skipped with
+    its tile, or a neighbour is read in its place.  Stale slots past the length
+    hold live codes.  With a left window the edge targets move to the first
+    visible key, and the extra aim goes to the last key the window hides."""
+    from flywheel_tpu import flash_attn_varlen_func
+    rng = np.random.default_rng(7)
+    prefix, chunk, heads, kv_heads, d, page = 1100, 320, 4, 2, 128, 64
+    total, group = prefix + chunk, heads // kv_heads
+    slots = -(-total // page) * page + page                      # a stale page past the end holds codes too
+    codes = rng.standard_normal((slots, kv_heads, d)).astype(np.float32)
+    codes /= np.linalg.norm(codes, axis=-1, keepdims=True)
+    values = rng.standard_normal((slots, kv_heads, d)).astype(np.float32)
+    edges = [0, 1, 15, 16, 63, 64, 65, 127, 128, 129, 255, 256, 511, 512, 1023, 1024, 1087, 1088, 1099, 1100]
+    q = np.zeros((chunk, heads, d), np.float32)
+    want = np.zeros((chunk, heads, d), np.float32)
+    aim = 20.0 * np.sqrt(d)
+    for r in range(chunk):
+        diag = prefix + r
+        first_visible = 0 if window_left is None else max(0, diag - window_left)
+        for h in range(heads):
+            kind = (r * heads + h) % 4
+            if kind == 0:
+                target = diag
+            elif kind == 1:
+                target = diag - 1
+            elif kind == 2:
+                target = edges[(r + h) % len(edges)] if window_left is None else first_visible
+            else:
+                target = int(rng.integers(first_visible, diag + 1))
+            q[r, h] = codes[target, h // group] * aim
+            want[r, h] = values[target, h // group]
+            if r % 3 == 0:
+                hidden = diag + 1 if window_left is None or h % 2 else first_visible - 1
+                if 0 <= hidden < slots:
+                    q[r, h] += codes[hidden, h // group] * aim
+    pool = oracle.merge_kv_heads(codes.astype(oracle.BF16), values.astype(oracle.BF16)).reshape(-1, page, 2 * kv_heads, d)
+    perm = rng.permutation(pool.shape[0]).astype(np.int32)
+    shuffled = np.empty_like(pool)
+    shuffled[perm] = pool
+    q_bf16 = q.astype(oracle.BF16)
+    cu, seqused = np.array([0, chunk], np.int32), np.array([total], np.int32)
+    out = flash_attn_varlen_func(
+        np.ascontiguousarray(q_bf16.transpose(1, 0, 2)), to_cuda(shuffled), None, cu, None, chunk, total,
+        causal=True, window_size=(-1 if window_left is None else window_left, -1),
+        block_table=perm[None], seqused_k=seqused)
+    got = out.astype(np.float32).transpose(1, 0, 2)
+    want_bf16 = want.astype(oracle.BF16).astype(np.float32)
+    worst = np.abs(got - want_bf16).max(axis=-1)
+    assert worst.max() < 4e-2, np.argwhere(worst >= 4e-2)[:8].tolist()
+    ref, _ = oracle.ragged_paged_attention(q_bf16, shuffled, cu, seqused, perm[None], nheads_k=kv_heads,
+                                           causal=True, window_left=window_left)
+    np.testing.assert_allclose(got, ref, **OUT_TOL)
 
 
 def test_multi_token_batch_call_takes_prefill_route():

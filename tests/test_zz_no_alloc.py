@@ -4,11 +4,13 @@ ordinary one.
 A host that cannot allocate device memory (its HBM is fully committed to the KV
 pool, or it runs where the allocator must not be called) uses the variant whose
 scratch is a fixed array inside the library.  Both entry points launch the same
-kernels, so on the same inputs they must agree; the check runs twice in a row
-because the built-in array is shared by every call and still holds the first
-call's partial states when the second one starts (here with other lengths, so
-stale states would show).  Collected last on purpose: a failure here cannot
-hide one elsewhere under `pytest -x`.
+deterministic kernels, so on the same inputs they must agree bit for bit, and
+both must sit within the decode parity bar of the CPU oracle; the check runs
+twice in a row because the built-in array is shared by every call and still
+holds the first call's partial states when the second one starts (here with
+other lengths, so stale states would show).  The status word of the built-in
+array is read through fw_read_status_static.  Collected last on purpose: a
+failure here cannot hide one elsewhere under `pytest -x`.
 """
 
 import ctypes
@@ -16,9 +18,18 @@ import ctypes
 import numpy as np
 import pytest
 
+from oracle import paged_attention as oracle
+
 pytestmark = pytest.mark.gpu
 
 TOL = dict(rtol=1e-2, atol=2e-2)   # the bf16 bar of the decode parity tests
+
+
+def static_status(lib):
+    from flywheel_tpu.softmax_attention import _native
+    word = ctypes.c_int32(-1)
+    _native.check(lib.fw_read_status_static(0, ctypes.byref(word)))
+    return word.value
 
 
 def decode_args(case, tensors, out, lse):
@@ -60,12 +71,45 @@ def test_static_scratch_entry_matches_workspace_entry_twice():
                 args.workspace, args.workspace_bytes = scratch.data_ptr(), nbytes
             _native.check(getattr(lib, entry)(ctypes.byref(args), 0))
             torch.cuda.synchronize()
+            if entry == "fw_decode_kvcache_static":
+                assert static_status(lib) == 0
             results.append((out.float().cpu().numpy(), lse.cpu().numpy(),
                             tensors["pool"].cpu().view(torch.int16).numpy()))
         (out_a, lse_a, pool_a), (out_b, lse_b, pool_b) = results
-        np.testing.assert_allclose(out_b, out_a, **TOL)
-        np.testing.assert_allclose(lse_b, lse_a, rtol=2e-3, atol=4e-3)
+        np.testing.assert_array_equal(out_b, out_a)       # the same kernels on the same inputs
+        np.testing.assert_array_equal(lse_b, lse_a)
         np.testing.assert_array_equal(pool_b, pool_a)     # appended pages bit-exact
+        want, want_lse, want_pool = oracle.kvcache_paged(
+            case.q, case.pool, case.k_new, case.v_new, case.cache_seqlens, case.block_table,
+            nheads_k=case.nheads_k, causal=True)
+        np.testing.assert_allclose(out_b, want, **TOL)
+        np.testing.assert_allclose(lse_b, want_lse, rtol=2e-3, atol=4e-3)
+        np.testing.assert_array_equal(pool_b.view(np.uint16), want_pool.view(np.uint16))
+
+
+def test_static_scratch_entry_reports_a_bad_page_through_its_own_status_reader():
+    """A block-table entry outside the pool on the static entry point: status 2
+    (FW_STATUS_BAD_PAGE) comes back through fw_read_status_static, once, and a
+    clean call afterwards reads 0."""
+    import torch
+    from flywheel_tpu.softmax_attention import _native
+    import paged_cases as workloads
+    lib = _native.library()
+    dev = torch.device("cuda", torch.cuda.current_device())
+    case = workloads.host_case(23, lens=(200, 70), hq=32, hk=4, page_size=64)
+    bf16 = lambda a: torch.from_numpy(a.view(np.int16)).to(dev).view(torch.bfloat16)
+    for bad in (True, False):
+        table = case.block_table.copy()
+        if bad:
+            table[0, 1] = 10 ** 6
+        tensors = {"q": bf16(case.q), "pool": bf16(case.pool), "k": bf16(case.k_new), "v": bf16(case.v_new),
+                   "lens": torch.from_numpy(case.cache_seqlens).to(dev), "table": torch.from_numpy(table).to(dev)}
+        out = torch.empty_like(tensors["q"])
+        lse = torch.empty((2, 32, 1), dtype=torch.float32, device=dev)
+        _native.check(lib.fw_decode_kvcache_static(ctypes.byref(decode_args(case, tensors, out, lse)), 0))
+        torch.cuda.synchronize()
+        assert static_status(lib) == (2 if bad else 0)
+        assert static_status(lib) == 0                    # cleared once reported
 
 
 def test_static_scratch_entry_refuses_oversized_calls():
