@@ -169,11 +169,10 @@ __device__ __forceinline__ int v_seg(const DecodeParams& p, int hl) {
 
 // D = head_dim.  At 256 a thread carries 128 output and 64 query registers, so
 // the block is sized for four consumer warps instead of eight.
-// The register cap is what the block size allows with one CTA per SM (65536 /
-// 288 threads, 65536 / 160 threads capped at 255); given outright because the
-// compiler's own choice under __launch_bounds__ stopped at 168 and spilled.
+// Nine warps put three on one SM sub-partition (16384 registers each), which
+// caps a thread at 168 registers; the launch bound tells the compiler so.
 template <int KVT, int TILE, int D = 128>
-__global__ void __maxnreg__(D > 128 ? 255 : 224)
+__global__ void __launch_bounds__(((D > 128 ? kMaxConsumerWarps / 2 : kMaxConsumerWarps) + 1) * 32, 1)
 decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
               const DecodeParams p) {
   constexpr bool kFp8 = KVT != FW_DTYPE_BF16;

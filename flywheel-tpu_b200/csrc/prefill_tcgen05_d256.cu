@@ -292,13 +292,19 @@ prefill_tcgen05_d256_kernel(const __grid_constant__ CUtensorMap map_q, const __g
           for (int c = 0; c < 2; ++c)
 #pragma unroll
             for (int i = 0; i < 32; i += 2) {
-              float y0, y1;
-              unpack2(fma2(pack2(__uint_as_float(sr[c][i]), __uint_as_float(sr[c][i + 1])), mul2, base2), y0, y1);
+              const uint64_t y2 = fma2(pack2(__uint_as_float(sr[c][i]), __uint_as_float(sr[c][i + 1])), mul2, base2);
               if constexpr (kTrueMax) {
+                float y0, y1;
+                unpack2(y2, y0, y1);
                 top0 = fmaxf(top0, y0);
                 top1 = fmaxf(top1, y1);
               }
-              const float p0 = fast_exp2(y0), p1 = fast_exp2(y1);
+              float p0, p1;
+              // the loop is fully unrolled, so this choice is made at compile time
+              if (FW_EXP2_POLY_EVERY > 0 && ((i >> 1) % (FW_EXP2_POLY_EVERY > 0 ? FW_EXP2_POLY_EVERY : 1)) == 0)
+                exp2_pair<true>(y2, p0, p1);
+              else
+                exp2_pair<false>(y2, p0, p1);
               sum2 = add2(sum2, pack2(p0, p1));
               const uint32_t pk = pack_bf16(p0, p1);
               if constexpr (!kTrueMax) pmax = max_bf16x2(pmax, pk);

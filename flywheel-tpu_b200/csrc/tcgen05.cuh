@@ -131,6 +131,44 @@ __host__ __device__ constexpr uint32_t instr_desc(int n, bool b_mn_major) {
          (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(kBM >> 4) << 24);
 }
 
+// 2^y for two scores, on the special-function unit (two ex2.approx) or, with
+// kPoly, on the FMA pipe: y is split into its nearest integer n (adding
+// 1.5 * 2^23 leaves n in the low mantissa bits) and f = y - n in [-0.5, 0.5],
+// 2^f is a cubic (maximum relative error 7.5e-5, far below the bf16 rounding P
+// gets next), and n goes into the exponent field by an integer add.  y is
+// clamped to [-126, 126]: the low end gives a subnormal that rounds to nothing,
+// 126 still trips the rescale check.
+// FW_EXP2_POLY_EVERY = n sends every n-th pair of scores down the FMA-pipe form.
+// It is off: measured on B200 on the chunked-prefill benchmark workload (rounds
+// of 0.5 s, power-capped clocks) the kernel ran 877 TFLOP/s with none, 795 with
+// every 4th pair, 775 with every 3rd, 723 with every 2nd - the softmax warps are
+// short of issue slots, not of special-function throughput.
+#ifndef FW_EXP2_POLY_EVERY
+#define FW_EXP2_POLY_EVERY 0
+#endif
+template <bool kPoly>
+__device__ __forceinline__ void exp2_pair(uint64_t y2, float& p0, float& p1) {
+  float y0, y1;
+  unpack2(y2, y0, y1);
+  if constexpr (!kPoly) {
+    p0 = fast_exp2(y0);
+    p1 = fast_exp2(y1);
+  } else {
+    const uint64_t yc = pack2(fminf(fmaxf(y0, -126.f), 126.f), fminf(fmaxf(y1, -126.f), 126.f));
+    const uint64_t t = add2(yc, pack2(12582912.f, 12582912.f));
+    const uint64_t nf = add2(t, pack2(-12582912.f, -12582912.f));
+    const uint64_t f = fma2(nf, pack2(-1.f, -1.f), yc);
+    uint64_t poly = fma2(pack2(0.0551716685f, 0.0551716685f), f, pack2(0.2426111251f, 0.2426111251f));
+    poly = fma2(poly, f, pack2(0.6932609677f, 0.6932609677f));
+    poly = fma2(poly, f, pack2(0.9999280572f, 0.9999280572f));
+    float t0, t1, q0, q1;
+    unpack2(t, t0, t1);
+    unpack2(poly, q0, q1);
+    p0 = __uint_as_float(__float_as_uint(q0) + (__float_as_uint(t0) << 23));
+    p1 = __uint_as_float(__float_as_uint(q1) + (__float_as_uint(t1) << 23));
+  }
+}
+
 // Pass 1 of the softmax over one 64-key row: optional softcap (scores become
 // log2-unit logits in place), optional mask (-inf in place), returns the row
 // max of what is left in `sr` (raw scores without a softcap).
