@@ -34,7 +34,7 @@ constexpr int kTile = 16;          // smallest stage: tokens per MMA k-step; pag
 #endif
 constexpr int kMaxStages = 8;
 constexpr int kMaxConsumerWarps = 8;
-constexpr int kMaxHeadDim = 256;   // head_dim 128 and 256 are built
+constexpr int kMaxHeadDim = 256;   // head_dim 64 (bf16), 128 and 256 are built
 constexpr int kMaxInlineBatch = 2048;  // requests whose tile counts fit the CTA-local scan
 
 struct DecodeParams {
@@ -62,7 +62,7 @@ struct DecodeParams {
   int spp;          // 128-byte segments per head plane
   int stages, stage_bytes;
   int tile;         // tokens per pipeline stage (16, 32 or 64)
-  int head_dim;     // 128 or 256
+  int head_dim;     // 64, 128 or 256
   int has_new, causal, window_left;
   int zero_pad_head;  // fp8 merged pool with an odd nheads_k: append zeroes the pad head
   float scale, softcap;
@@ -670,7 +670,9 @@ __global__ void __launch_bounds__((WPR > kCombineWarps ? WPR : kCombineWarps) * 
 combine_kernel(const CombineParams cp) {
   constexpr int kWarps = WPR > kCombineWarps ? WPR : kCombineWarps;  // warps per block
   constexpr int kRowsPerBlock = kWarps / WPR;
-  constexpr int NB = D / 128;  // a lane owns four columns of every 128-column block
+  // a lane owns four columns of every 128-column block; at head_dim 64 two columns of the one block
+  constexpr int NB = D >= 128 ? D / 128 : 1;
+  constexpr bool kNarrow = D < 128;
   const DecodeParams& p = cp.d;
   __shared__ float4 red_acc[kWarps][NB][32];
   __shared__ float red_den[kWarps], red_max[kWarps];
@@ -744,8 +746,14 @@ combine_kernel(const CombineParams cp) {
       const float2 ml = *reinterpret_cast<const float2*>(p.part_ml + prow * 2);
       float4 o[NB];
 #pragma unroll
-      for (int nb = 0; nb < NB; ++nb)
-        o[nb] = *reinterpret_cast<const float4*>(p.part_o + prow * D + nb * 128 + lane * 4);
+      for (int nb = 0; nb < NB; ++nb) {
+        if constexpr (kNarrow) {
+          const float2 two = *reinterpret_cast<const float2*>(p.part_o + prow * D + lane * 2);
+          o[nb] = make_float4(two.x, two.y, 0.f, 0.f);
+        } else {
+          o[nb] = *reinterpret_cast<const float4*>(p.part_o + prow * D + nb * 128 + lane * 4);
+        }
+      }
       const float x = has_tiles ? ml.x : -INFINITY;  // a segment that saw no key carries -inf
       const float m_new = fmaxf(m_max, x);
       const float base = m_new == -INFINITY ? 0.f : m_new;
@@ -807,9 +815,14 @@ combine_kernel(const CombineParams cp) {
       const long long orow = static_cast<long long>(b) * rq + row;
       const float inv = den > 0.f ? 1.f / den : 0.f;
 #pragma unroll
-      for (int nb = 0; nb < NB; ++nb)
-        *reinterpret_cast<float4*>(cp.partial_out + orow * D + nb * 128 + lane * 4) = make_float4(
-            acc[nb].x * inv * vd, acc[nb].y * inv * vd, acc[nb].z * inv * vd, acc[nb].w * inv * vd);
+      for (int nb = 0; nb < NB; ++nb) {
+        if constexpr (kNarrow)
+          *reinterpret_cast<float2*>(cp.partial_out + orow * D + lane * 2) =
+              make_float2(acc[nb].x * inv * vd, acc[nb].y * inv * vd);
+        else
+          *reinterpret_cast<float4*>(cp.partial_out + orow * D + nb * 128 + lane * 4) = make_float4(
+              acc[nb].x * inv * vd, acc[nb].y * inv * vd, acc[nb].z * inv * vd, acc[nb].w * inv * vd);
+      }
       if (lane == 0) cp.partial_lse[orow] = den > 0.f ? (m_max + log2f(den)) * kLn2 : -INFINITY;
       continue;
     }
@@ -835,7 +848,8 @@ combine_kernel(const CombineParams cp) {
       uint2 packed;
       packed.x = pack_bf16(acc[nb].x * out_scale, acc[nb].y * out_scale);
       packed.y = pack_bf16(acc[nb].z * out_scale, acc[nb].w * out_scale);
-      *reinterpret_cast<uint2*>(cp.out + ooff + nb * 128 + lane * 4) = packed;
+      if constexpr (kNarrow) *reinterpret_cast<uint32_t*>(cp.out + ooff + lane * 2) = packed.x;
+      else *reinterpret_cast<uint2*>(cp.out + ooff + nb * 128 + lane * 4) = packed;
     }
     if (cp.lse != nullptr && lane == 0) {
       if (p.items != nullptr)
@@ -874,8 +888,13 @@ static int plan_decode(const FwDecodeArgs* a, DecodePlan* plan, int max_batch = 
     set_error("nheads=%d must be a multiple of nheads_k=%d.", a->nheads, a->nheads_k);
     return FW_ERR_BAD_SHAPE;
   }
-  if (a->head_dim != 128 && a->head_dim != kMaxHeadDim) {
-    set_error("head_dim %d is not built; this library serves head_dim 128 and 256.", a->head_dim);
+  if (a->head_dim != 64 && a->head_dim != 128 && a->head_dim != kMaxHeadDim) {
+    set_error("head_dim %d is not built; this library serves head_dim 64, 128 and 256.", a->head_dim);
+    return FW_ERR_UNSUPPORTED;
+  }
+  if (a->head_dim == 64 && a->kv_dtype != FW_DTYPE_BF16) {
+    // a 64-element fp8 plane is 64 bytes: K and V of a head would share one 128-byte segment
+    set_error("head_dim 64 is built for bfloat16 caches; fp8 caches take head_dim 128 or 256.");
     return FW_ERR_UNSUPPORTED;
   }
   if (paged) {
@@ -1068,6 +1087,8 @@ static int launch_decode(DecodePlan& plan, void* workspace, cudaStream_t stream,
     } else {
       kernel = decode_kernel<FW_DTYPE_E5M2, 16, 256>;
     }
+  } else if (p.head_dim == 64) {
+    kernel = decode_kernel<FW_DTYPE_BF16, 16, 64>;
   } else if (kv_dtype == FW_DTYPE_BF16) {
     kernel = decode_kernel<FW_DTYPE_BF16, 16>;
   } else if (kv_dtype == FW_DTYPE_E4M3) {
@@ -1104,7 +1125,7 @@ static int launch_decode(DecodePlan& plan, void* workspace, cudaStream_t stream,
   // Few rows with many segments each (a long request cut over every SM): 16
   // warps share a row, so its ~150 segments are read in a few rounds.
   const bool wide = static_cast<long long>(p.batch) * plan.rows_q <= 2048;
-  const bool d256 = p.head_dim == kMaxHeadDim;
+  const bool d256 = p.head_dim == kMaxHeadDim, d64 = p.head_dim == 64;
   // The combine is launched as a programmatic dependent of the decode kernel:
   // its grid is set up while the decode kernel still runs and its blocks wait
   // (griddepcontrol.wait) for the decode grid to complete and flush, which
@@ -1121,6 +1142,8 @@ static int launch_decode(DecodePlan& plan, void* workspace, cudaStream_t stream,
     cfg.blockDim = dim3(16 * 32);
     if (d256)
       cudaLaunchKernelEx(&cfg, combine_kernel<16, 256>, cp);
+    else if (d64)
+      cudaLaunchKernelEx(&cfg, combine_kernel<16, 64>, cp);
     else
       cudaLaunchKernelEx(&cfg, combine_kernel<16, 128>, cp);
   } else {
@@ -1132,6 +1155,8 @@ static int launch_decode(DecodePlan& plan, void* workspace, cudaStream_t stream,
     cfg.blockDim = dim3(kCombineWarps * 32);
     if (d256)
       cudaLaunchKernelEx(&cfg, combine_kernel<1, 256>, cp);
+    else if (d64)
+      cudaLaunchKernelEx(&cfg, combine_kernel<1, 64>, cp);
     else
       cudaLaunchKernelEx(&cfg, combine_kernel<1, 128>, cp);
   }

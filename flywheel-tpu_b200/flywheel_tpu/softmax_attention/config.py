@@ -17,5 +17,9 @@ def max_folded_query_rows(head_dim: int) -> int:
     registers hold twice the output columns."""
     return MAX_FOLDED_QUERY_ROWS if head_dim <= 128 else MAX_FOLDED_QUERY_ROWS // 2
 SUPPORTED_HEAD_DIMS = (128, 256)
+# The decode kernel (single token, folded verify window) also takes head_dim 64
+# with a bf16 cache, like the reference's (traits.py:50, 473-477 there); the
+# paged prefill kernels need head_dim % 128 == 0, as the reference's do.
+DECODE_HEAD_DIMS = (64, 128, 256)
 # Rows one decode launch takes; the host entry slices larger batches.
 MAX_DECODE_BATCH = 2048

@@ -18,6 +18,7 @@ import torch
 
 from flywheel_tpu.softmax_attention import _arrays, _native
 from flywheel_tpu.softmax_attention.config import (
+    DECODE_HEAD_DIMS,
     MAX_DECODE_BATCH,
     max_folded_query_rows,
     PAGE_SIZE_MULTIPLE,
@@ -241,10 +242,14 @@ def flash_attn_with_kvcache(
         raise ValueError(
             f"k and v must be {expected_new_shape} (matching q's token layout);"
             f" got {tuple(k.shape)=}, {tuple(v.shape)=}.")
-    if head_dim not in SUPPORTED_HEAD_DIMS:
+    if head_dim not in DECODE_HEAD_DIMS:
         raise NotImplementedError(
             f"head_dim {head_dim} is not built; this library serves"
-            f" {SUPPORTED_HEAD_DIMS}.")
+            f" {DECODE_HEAD_DIMS}.")
+    if head_dim not in SUPPORTED_HEAD_DIMS and cache_dtype != "bfloat16":
+        raise NotImplementedError(
+            f"head_dim {head_dim} is built for bfloat16 caches; fp8 caches take"
+            f" head_dim {SUPPORTED_HEAD_DIMS}.")
 
     device = _arrays.pick_device(k_cache, q)
     lengths = _arrays.to_device(cache_seqlens, device, dtype="int32")
@@ -351,6 +356,12 @@ def flash_attn_with_kvcache(
             _native.check(lib.fw_decode_kvcache(ctypes.byref(part), stream))
             _native.raise_on_status(scratch, device)
     else:
+        if head_dim not in SUPPORTED_HEAD_DIMS:
+            raise NotImplementedError(
+                f"head_dim {head_dim} is served by the decode kernel only (one"
+                " query token, or a (batch, seqlen_q, ...) window of up to"
+                f" {max_folded_query_rows(head_dim)} query rows per KV head);"
+                f" packed and longer calls need head_dim {SUPPORTED_HEAD_DIMS}.")
         from flywheel_tpu.softmax_attention.prefill import paged_prefill_device
         if is_ragged:
             cu = _arrays.to_device(cu_seqlens_q, device, dtype="int32").contiguous()

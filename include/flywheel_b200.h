@@ -66,8 +66,8 @@ extern "C" {
  * Attention of q against a KV cache with the new tokens' K/V appended in the
  * same launch (flash_attn_with_kvcache, decode.py:189-625).
  *
- * head_dim is 128 or 256 (at 256: at most 64 query rows, seqlen_q * nheads /
- * nheads_k, per KV head).
+ * head_dim is 64 (bf16 caches only), 128 or 256 (at 256: at most 64 query
+ * rows, seqlen_q * nheads / nheads_k, per KV head).
  *
  * Layouts
  *   paged merged (block_table != NULL): kv_cache is one pool

@@ -295,3 +295,45 @@ def test_batch_larger_than_one_launch_is_sliced():
                      hq=4, hk=1, page_size=16, extra_pages=1)
     out = run_case(case, num_active=2300)
     assert not out[2300:].any()
+
+
+@pytest.mark.parametrize("hq,hk", [(64, 8), (8, 8), (6, 3), (16, 1)])
+def test_decode_head_dim_64_with_sinks(hq, hk):
+    """head_dim 64 on the paged decode kernel, the gpt-oss shape of the
+    reference's tests (tests/softmax_attention/test_paged.py:1157-1182 there: 64
+    query heads over 8 KV heads, head_dim 64, sinks): single token, a folded
+    verify window, window + softcap, and without the append."""
+    rng = np.random.default_rng(64)
+    sinks = rng.uniform(-2, 8, hq).astype(np.float32)
+    case = host_case(64, lens=(0, 1, 63, 64, 65, 300, 1027), hq=hq, hk=hk, d=64, page_size=64)
+    run_case(case, sinks=sinks)
+    run_case(case, sinks=sinks, append=False, window_left=127, softcap=30.0)
+    if hq // hk <= 8:
+        run_case(host_case(65, lens=(5, 60, 200), q_len=4, hq=hq, hk=hk, d=64, page_size=128), sinks=sinks,
+                 num_active=2)
+
+
+def test_decode_head_dim_64_contiguous_and_rejections():
+    import torch
+    from flywheel_tpu import flash_attn_with_kvcache
+    rng = np.random.default_rng(66)
+    b, cap, hk, hq, d = 3, 128, 4, 16, 64
+    draw = lambda shape: rng.standard_normal(shape, dtype=np.float32).astype(oracle.BF16)
+    kc, vc = draw((b, cap, hk, d)), draw((b, cap, hk, d))
+    q, k, v = draw((b, 1, hq, d)), draw((b, 1, hk, d)), draw((b, 1, hk, d))
+    lengths = np.array([0, 17, 127], np.int32)
+    to_t = lambda a: torch.from_numpy(a.view(np.int16)).cuda().view(torch.bfloat16)
+    want, want_lse, kc2, vc2 = oracle.kvcache_contiguous(q, kc, vc, k, v, lengths, None, causal=True)
+    out, lse, ko, vo = flash_attn_with_kvcache(q, to_t(kc), to_t(vc), k, v, cache_seqlens=lengths, causal=True,
+                                               return_softmax_lse=True)
+    np.testing.assert_allclose(out.astype(np.float32), want, **BF16_TOL)
+    np.testing.assert_allclose(lse, want_lse, **LSE_TOL)
+    np.testing.assert_array_equal(ko.cpu().view(torch.int16).numpy(), kc2.view(np.int16))
+    # fp8 at head_dim 64 and the packed route are not built: say so, do not fall back
+    pool8 = torch.zeros((4, 64, 2 * hk, d), dtype=torch.uint8).cuda().view(torch.float8_e4m3fn)
+    table = np.zeros((b, 1), np.int32)
+    with pytest.raises(NotImplementedError, match="bfloat16 caches"):
+        flash_attn_with_kvcache(q, pool8, None, cache_seqlens=lengths, block_table=table, nheads_k=hk)
+    pool = torch.zeros((4, 64, 2 * hk, d), dtype=torch.bfloat16).cuda()
+    with pytest.raises(NotImplementedError, match="decode kernel only"):
+        flash_attn_with_kvcache(draw((b, 40, hq, d)), pool, None, cache_seqlens=lengths, block_table=table)
