@@ -22,10 +22,11 @@ median over rounds, with the spread beside it.
   resident on the device, as it does in serving.
 * roofline: algorithmic KV bytes per launch / this rank's measured time per
   launch, against the measured HBM copy bandwidth in MEASURED_PEAKS.json.
-* prefill, c1, c3, long_context, strong: the other benchmark configurations
-  (chunked prefill; contiguous decode; fp8 verify-window decode; one 128K-token
-  request split over the GPUs with its (o, lse) exchange; one decode batch split
-  over the GPUs by request and by KV head), each with its own roofline.
+* prefill, c1, c3, long_context, strong, mixed: the other benchmark
+  configurations (chunked prefill; contiguous decode; fp8 verify-window decode;
+  one 128K-token request split over the GPUs with its (o, lse) exchange; one
+  decode batch split over the GPUs by request and by KV head; a step mixing
+  decode rows and prefill chunks), each with its own figures.
 * cpu_baseline: the C + OpenMP restatement of the reference's test oracle
   (oracle/paged_decode_ref.c) on the same batch, on all host cores.
 * --impl reference: that CPU restatement as its own arm (the reference itself
@@ -599,6 +600,78 @@ def strong_scaling_key(ns, ranks, full_batch_ms):
     return result
 
 
+# ---------------------------------------------------------------- a mixed step (decode rows + prefill chunks)
+def bench_mixed(ns, ranks):
+    """One serving step that mixes 96 one-token decode requests (cached lengths
+    U[1024,32768]) with 8 prefill chunks (prefix U[0,16384], chunk U[512,2048])
+    over one paged bf16 pool, 32 q heads, 8 kv heads, page 64: the page write of
+    all scheduled tokens plus attention.  Timed twice on device-resident inputs:
+    through paged_extend (decode kernel for the one-token rows, tensor-core
+    prefill for the chunks, one launch sequence) and through the packed
+    flash_attn_with_kvcache call, where every request, one-token ones included,
+    takes tensor-core query tiles."""
+    import torch
+    from flywheel_tpu import flash_attn_with_kvcache
+    from flywheel_tpu.softmax_attention.extend import paged_extend
+    device = ranks.device
+    rng = np.random.default_rng(3000)
+    n_decode, n_prefill, hq, hk = 96, 8, 32, 8
+    before = np.concatenate([rng.integers(LEN_LO, LEN_HI + 1, n_decode), rng.integers(0, 16384 + 1, n_prefill)])
+    new = np.concatenate([np.ones(n_decode, np.int64), rng.integers(512, 2048 + 1, n_prefill)])
+    before, new = before.astype(np.int32), new.astype(np.int32)
+    after = before + new
+    cu = np.concatenate(([0], np.cumsum(new))).astype(np.int32)
+    total = int(cu[-1])
+    table, pool_pages = workloads.paged_table(rng, after, 0, PAGE, slack=0.10)
+    columns = []
+    for r in range(len(before)):
+        pos, row = int(before[r]), int(cu[r])
+        while pos < after[r]:
+            run = min(int(after[r]) - pos, PAGE - pos % PAGE)
+            columns.append((int(table[r, pos // PAGE]) * PAGE + pos % PAGE, row, run))
+            pos, row = pos + run, row + run
+    slices = torch.from_numpy(np.ascontiguousarray(np.array(columns, np.int32).T)).to(device)
+    gen = torch.Generator(device=device)
+    gen.manual_seed(3000)
+    pool = torch.empty((pool_pages, PAGE, 2 * hk, D), dtype=torch.bfloat16, device=device)
+    fill_normal(pool, gen)
+    q = torch.randn((total, hq, D), device=device).to(torch.bfloat16)
+    k = torch.randn((total, hk, D), device=device).to(torch.bfloat16)
+    v = torch.randn((total, hk, D), device=device).to(torch.bfloat16)
+    dev = lambda a: torch.from_numpy(a).to(device)
+    after_t, before_t, cu_t, table_t = dev(after), dev(before), dev(cu), dev(table)
+    count = torch.tensor([len(columns)], dtype=torch.int32, device=device)
+    n_dec = torch.tensor([n_decode], dtype=torch.int32, device=device)
+    n_act = torch.tensor([n_decode + n_prefill], dtype=torch.int32, device=device)
+
+    def mixed_pass():
+        for _ in range(5):
+            paged_extend(q, k, v, pool, after_t, table_t, cu_t, slices, count, n_dec, n_act)
+
+    def packed_pass():
+        for _ in range(5):
+            flash_attn_with_kvcache(q, pool, None, k, v, cache_seqlens=before_t, block_table=table_t,
+                                    cu_seqlens_q=cu_t, max_seqlen_q=int(new.max()), causal=True)
+
+    out_mixed, _ = paged_extend(q, k, v, pool, after_t, table_t, cu_t, slices, count, n_dec, n_act)
+    out_packed = flash_attn_with_kvcache(q, pool, None, k, v, cache_seqlens=before_t, block_table=table_t,
+                                         cu_seqlens_q=cu_t, max_seqlen_q=int(new.max()), causal=True)[0]
+    agree = float((out_mixed.float() - out_packed.float()).abs().max())
+    mixed = timed_rounds(mixed_pass, 5, ranks, rounds=3, min_round_s=min(ns.min_round_s, 0.2))
+    packed = timed_rounds(packed_pass, 5, ranks, rounds=3, min_round_s=min(ns.min_round_s, 0.2))
+    kv_bytes = workloads.decode_kv_bytes(before[:n_decode], 1, hk, D, 2)
+    flops = workloads.prefill_flops(before[n_decode:], new[n_decode:], hq, D)
+    return {"metric": "mixed_step_ms", "unit": "ms", "higher_is_better": False,
+            "config": {"workload": f"{n_decode} decode requests U[1024,32768] + {n_prefill} prefill chunks (prefix "
+                                   "U[0,16384], chunk U[512,2048]), 32 q heads, 8 kv heads, head_dim 128, page 64, "
+                                   "bf16; page write of the scheduled tokens included", "tokens": total},
+            "value": mixed["ms_per_step"], "ms_per_step": mixed["ms_per_step"],
+            "decode_kv_bytes": kv_bytes, "prefill_flops": flops,
+            "packed_route_ms_per_step": packed["ms_per_step"],
+            "speedup_over_packed_route": packed["ms_per_step"] / mixed["ms_per_step"],
+            "max_abs_diff_between_routes": agree, "rounds": round_summary(mixed)}
+
+
 # ---------------------------------------------------------------- secondary decode configurations
 # The reference's own serving and perf-gate decode shapes (page 128), beside
 # which its TPU tables sit: docs/v7x.md:129-150 and scripts/perf_gate.py:80-107
@@ -1042,6 +1115,7 @@ def headline(ns, ranks):
         if world == 1:
             extra["c1"] = bench_config(ns, "c1", ranks)
             extra["c3"] = bench_config(ns, "c3", ranks)
+            extra["mixed"] = bench_mixed(ns, ranks)
         else:
             # every rank has just timed the full batch by itself: that is the one-GPU time
             extra["strong"] = strong_scaling_key(ns, ranks, full_batch_ms)

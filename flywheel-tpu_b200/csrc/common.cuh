@@ -264,6 +264,9 @@ bool tcgen05_d256_supported(const FwPrefillArgs* args);
 uint64_t tcgen05_d256_workspace_bytes(const FwPrefillArgs* args);
 int tcgen05_d256_prefill(const FwPrefillArgs* args, cudaStream_t stream);
 
+// fw_decode_kvcache reporting to `status` instead of the head of its workspace (decode.cu).
+int decode_with_status(const FwDecodeArgs* args, int* status, cudaStream_t stream);
+
 // Chunked prefill through the split-KV decode kernel (decode.cu).
 uint64_t splitkv_prefill_workspace_bytes(const FwPrefillArgs* args);
 int splitkv_prefill(const FwPrefillArgs* args, cudaStream_t stream);

@@ -1054,11 +1054,11 @@ namespace fw {
 // Enqueues decode_kernel + combine_kernel for a finished plan.
 static int launch_decode(DecodePlan& plan, void* workspace, cudaStream_t stream, int kv_dtype, void* out,
                          float* lse, float* partial_out, float* partial_lse, const float* v_descale,
-                         const float* sinks) {
+                         const float* sinks, int* status = nullptr) {
   int rc;
   DecodeParams& p = plan.p;
   uint8_t* ws = static_cast<uint8_t*>(workspace);
-  p.status = reinterpret_cast<int*>(ws);
+  p.status = status != nullptr ? status : reinterpret_cast<int*>(ws);  // by default the head of the workspace
   p.tile_prefix = reinterpret_cast<int*>(ws + plan.off_prefix);
   p.part_ml = reinterpret_cast<float*>(ws + plan.off_ml);
   p.part_o = reinterpret_cast<float*>(ws + plan.off_o);
@@ -1179,6 +1179,13 @@ extern "C" uint64_t fw_decode_workspace_bytes(const FwDecodeArgs* args) {
 }
 
 extern "C" int fw_decode_kvcache(const FwDecodeArgs* a, void* stream_ptr) {
+  return fw::decode_with_status(a, nullptr, static_cast<cudaStream_t>(stream_ptr));
+}
+
+// fw_decode_kvcache; `status` (or NULL = the head of the workspace) is where the
+// kernels report.  A caller that runs several kernels on one workspace gives
+// them one status word.
+int fw::decode_with_status(const FwDecodeArgs* a, int* status, cudaStream_t stream) {
   DecodePlan plan;
   int rc = plan_decode(a, &plan);
   if (rc != FW_OK) return rc;
@@ -1199,8 +1206,8 @@ extern "C" int fw_decode_kvcache(const FwDecodeArgs* a, void* stream_ptr) {
     set_error("q, out, caches and new k/v must be 16-byte aligned.");
     return FW_ERR_BAD_SHAPE;
   }
-  return launch_decode(plan, a->workspace, static_cast<cudaStream_t>(stream_ptr), a->kv_dtype, a->out, a->lse,
-                       a->partial_out, a->partial_lse, a->v_descale, a->sinks);
+  return launch_decode(plan, a->workspace, stream, a->kv_dtype, a->out, a->lse, a->partial_out, a->partial_lse,
+                       a->v_descale, a->sinks, status);
 }
 
 // ---------------------------------------------------------------- split-KV prefill
@@ -1220,6 +1227,7 @@ struct PrefillPlanParams {
   int kv_stride;       // packed K/V in fixed slots: request r's keys start at row r * kv_stride
   const int* seqused;  // paged: request r's key count
   const int* num_active;
+  const int* first_request;  // NULL, or requests below this one get no query blocks
   int* items;
   int* status;  // status block of the launch that follows, or NULL
   __nv_bfloat16* out;
@@ -1242,8 +1250,9 @@ __global__ void __launch_bounds__(256) prefill_plan_kernel(const PrefillPlanPara
   if (blockIdx.x == 0) {
     // nothing an earlier launch reported may switch the coming one off
     if (threadIdx.x == 0 && pp.status != nullptr) pp.status[kStatusLaunchVoidWord] = 0;
+    const int first = pp.first_request ? min(n_active, max(0, *pp.first_request)) : 0;
     for (int r = threadIdx.x; r < pp.batch; r += blockDim.x) {
-      const int c = r < n_active ? max(0, pp.cu[r + 1] - pp.cu[r]) : 0;
+      const int c = r >= first && r < n_active ? max(0, pp.cu[r + 1] - pp.cu[r]) : 0;
       off[r + 1] = (c + pp.qb - 1) / pp.qb;
     }
     __syncthreads();
@@ -1330,6 +1339,7 @@ int launch_prefill_plan(const FwPrefillArgs* a, int qb, int max_items, int* item
   pp.kv_stride = a->block_table == nullptr && a->cu_seqlens_k == nullptr ? a->kv_request_stride : 0;
   pp.seqused = a->seqused_k;
   pp.num_active = a->num_active;
+  pp.first_request = a->first_request;
   pp.items = items;
   pp.status = status;
   pp.out = static_cast<__nv_bfloat16*>(a->out);

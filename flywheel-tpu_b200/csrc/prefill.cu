@@ -39,11 +39,14 @@ static int check_prefill_args(const FwPrefillArgs* a) {
   return FW_OK;
 }
 
-// ---------------------------------------------------------------- Q-only RoPE
-// Rotates packed q into a scratch copy before attention: token t of request r
-// sits at position seqused_k[r] - len_q(r) + t (its own K/V position), the
-// rotation runs in f32 and rounds once to bf16.  Rows outside every request
-// and positions past the table are copied unrotated.
+// ---------------------------------------------------------------- RoPE pre-pass
+// The tensor-core kernels rotate Q themselves, in shared memory, right after the
+// TMA copy of the Q tile (tcgen05.cuh).  This kernel remains for what they do not
+// cover: Q on the split-KV route (short chunks) and K of packed K/V.  It rotates
+// packed rows into a scratch copy: token t of request r sits at position
+// seqused_k[r] - len_q(r) + t (its own K/V position), the rotation runs in f32
+// and rounds once to bf16.  Rows outside every request and positions past the
+// table are copied unrotated.
 struct RopeParams {
   const __nv_bfloat16* q;
   __nv_bfloat16* q_out;
@@ -127,7 +130,8 @@ __global__ void __launch_bounds__(256) rope_q_kernel(const RopeParams p) {
   }
 }
 
-static uint64_t rope_bytes(const FwPrefillArgs* a) {
+// Scratch for a rotated copy of q: only the split-KV route needs one.
+static uint64_t rope_copy_bytes(const FwPrefillArgs* a) {
   if (a->rotary_cos == nullptr) return 0;
   return (static_cast<uint64_t>(a->total_q) * a->nheads * a->head_dim * 2 + 255) & ~255ull;
 }
@@ -249,6 +253,10 @@ static uint64_t attention_workspace_bytes(const FwPrefillArgs* a) {
   return n == 0 ? 0 : (n + 255) & ~255ull;
 }
 
+static uint64_t rope_bytes(const FwPrefillArgs* a) {
+  return pick_route(a) == PrefillRoute::kSplitKv ? rope_copy_bytes(a) : 0;
+}
+
 extern "C" uint64_t fw_prefill_workspace_bytes(const FwPrefillArgs* a) {
   if (check_prefill_args(a) != FW_OK) return 0;
   const uint64_t n = attention_workspace_bytes(a);
@@ -263,8 +271,10 @@ extern "C" int fw_prefill_paged(const FwPrefillArgs* a, void* stream_ptr) {
   if (a->total_q == 0) return FW_OK;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
   FwPrefillArgs local = *a;
-  if (a->rotary_cos != nullptr) {
-    // The rotated copy of q lives behind the attention kernels' own scratch.
+  const PrefillRoute route = pick_route(a);
+  if (a->rotary_cos != nullptr && route == PrefillRoute::kSplitKv) {
+    // The split-KV kernel reads q from global memory: rotate a copy first.  It
+    // lives behind the attention kernel's own scratch.
     const uint64_t head = attention_workspace_bytes(a);
     if (head == 0) return FW_ERR_UNSUPPORTED;
     if (a->workspace == nullptr || a->workspace_bytes < head + rope_bytes(a) ||
@@ -304,9 +314,10 @@ extern "C" int fw_prefill_paged(const FwPrefillArgs* a, void* stream_ptr) {
       return FW_ERR_LAUNCH;
     }
     local.q = rp.q_out;
+    local.rotary_cos = local.rotary_sin = nullptr;  // done
     local.workspace_bytes = head;
   }
-  switch (pick_route(a)) {
+  switch (route) {
     case PrefillRoute::kTensorCore: return tcgen05_prefill(&local, stream);
     case PrefillRoute::kSplitKv: return splitkv_prefill(&local, stream);
     case PrefillRoute::kGatherTensorCore: break;
@@ -398,7 +409,7 @@ static uint64_t packed_rope_k_bytes(const FwPrefillArgs* a) {
 
 extern "C" uint64_t fw_attention_packed_workspace_bytes(const FwPrefillArgs* a) {
   if (check_packed_args(a) != FW_OK) return 0;
-  return ((tcgen05_prefill_workspace_bytes(a) + 255) & ~255ull) + rope_bytes(a) + packed_rope_k_bytes(a);
+  return ((tcgen05_prefill_workspace_bytes(a) + 255) & ~255ull) + packed_rope_k_bytes(a);
 }
 
 static int launch_rope(const RopeParams& rp, long long rows, cudaStream_t stream) {
@@ -420,53 +431,41 @@ extern "C" int fw_attention_packed(const FwPrefillArgs* a, void* stream_ptr) {
   cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
   FwPrefillArgs local = *a;
   const uint64_t head = (tcgen05_prefill_workspace_bytes(a) + 255) & ~255ull;
-  if (a->rotary_cos != nullptr) {
-    const uint64_t need = head + rope_bytes(a) + packed_rope_k_bytes(a);
+  if (a->rotary_cos != nullptr && a->rotary_k) {
+    // Q is rotated inside the attention kernel.  K's token t of a request sits at
+    // position t: rotate it into a scratch copy as a tensor whose rows are its own
+    // keys (length = key count).
+    const uint64_t need = head + packed_rope_k_bytes(a);
     if (a->workspace == nullptr || a->workspace_bytes < need || (reinterpret_cast<uintptr_t>(a->workspace) & 255)) {
       set_error("workspace must be 256-byte aligned and hold %llu bytes; got %llu.",
                 static_cast<unsigned long long>(need), static_cast<unsigned long long>(a->workspace_bytes));
       return FW_ERR_WORKSPACE;
     }
-    if (a->q == nullptr || a->kv_cache == nullptr || a->cu_seqlens_q == nullptr) {
-      set_error("q, k and cu_seqlens_q must not be NULL.");
+    if (a->kv_cache == nullptr) {
+      set_error("k must not be NULL.");
       return FW_ERR_BAD_SHAPE;
     }
     uint8_t* ws = static_cast<uint8_t*>(a->workspace);
-    RopeParams rp;
-    rp.q = static_cast<const __nv_bfloat16*>(a->q);
-    rp.q_out = reinterpret_cast<__nv_bfloat16*>(ws + head);
-    rp.cos = a->rotary_cos;
-    rp.sin = a->rotary_sin;
-    rp.cu = a->cu_seqlens_q;
-    rp.seqused = nullptr;
-    rp.cu_k = a->cu_seqlens_k;
-    rp.tok_stride = a->token_major ? static_cast<long long>(a->nheads) * a->head_dim : a->head_dim;
-    rp.head_stride = a->token_major ? a->head_dim : static_cast<long long>(a->total_q) * a->head_dim;
-    rp.batch = a->batch;
-    rp.total_q = a->total_q;
-    rp.nheads = a->nheads;
-    rp.rotary_len = a->rotary_len;
-    rp.interleaved = a->rotary_interleaved;
-    rp.table_bf16 = a->rotary_bf16;
-    rp.head_dim = a->head_dim;
-    rc = launch_rope(rp, a->total_q, stream);
+    RopeParams rk;
+    rk.q = static_cast<const __nv_bfloat16*>(a->kv_cache);
+    rk.q_out = reinterpret_cast<__nv_bfloat16*>(ws + head);
+    rk.cos = a->rotary_cos;
+    rk.sin = a->rotary_sin;
+    rk.cu = a->cu_seqlens_k;
+    rk.seqused = nullptr;
+    rk.cu_k = a->cu_seqlens_k;
+    rk.tok_stride = a->kv_token_major ? static_cast<long long>(a->nheads_k) * a->head_dim : a->head_dim;
+    rk.head_stride = a->kv_token_major ? a->head_dim : static_cast<long long>(a->total_k) * a->head_dim;
+    rk.batch = a->batch;
+    rk.total_q = a->total_k;
+    rk.nheads = a->nheads_k;
+    rk.rotary_len = a->rotary_len;
+    rk.interleaved = a->rotary_interleaved;
+    rk.table_bf16 = a->rotary_bf16;
+    rk.head_dim = a->head_dim;
+    rc = launch_rope(rk, a->total_k, stream);
     if (rc != FW_OK) return rc;
-    local.q = rp.q_out;
-    if (a->rotary_k) {
-      // K's token t of a request sits at position t: rotate it as a tensor whose
-      // rows are its own keys (length = key count).
-      RopeParams rk = rp;
-      rk.q = static_cast<const __nv_bfloat16*>(a->kv_cache);
-      rk.q_out = reinterpret_cast<__nv_bfloat16*>(ws + head + rope_bytes(a));
-      rk.cu = a->cu_seqlens_k;
-      rk.tok_stride = a->kv_token_major ? static_cast<long long>(a->nheads_k) * a->head_dim : a->head_dim;
-      rk.head_stride = a->kv_token_major ? a->head_dim : static_cast<long long>(a->total_k) * a->head_dim;
-      rk.total_q = a->total_k;
-      rk.nheads = a->nheads_k;
-      rc = launch_rope(rk, a->total_k, stream);
-      if (rc != FW_OK) return rc;
-      local.kv_cache = rk.q_out;
-    }
+    local.kv_cache = rk.q_out;
     local.workspace_bytes = head;
   }
   return tcgen05_prefill(&local, stream);

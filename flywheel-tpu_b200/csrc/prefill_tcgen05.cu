@@ -39,6 +39,7 @@ struct Bars {
   uint64_t k_full[kKvStages], v_full[kKvStages], k_empty[kKvStages], v_empty[kKvStages];
   uint64_t s_full[kStreams], p_full[kStreams], pv_done[kStreams];
   uint64_t drain;  // abort path: completion of the MMAs issued so far
+  uint64_t q_rotated;  // rotary embedding: every softmax warp has rotated its rows of Q
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -95,6 +96,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       mbar_init(&bars->pv_done[t], 1);
     }
     mbar_init(&bars->drain, 1);
+    mbar_init(&bars->q_rotated, 4 * n_streams);
     bars->abort_flag = 0;
     fence_barrier_init();
   }
@@ -210,7 +212,8 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         }
         tc_commit(&bars->s_full[t]);
       };
-      bool ok = FW_WAIT(2, 0, &bars->q_full, 0);
+      // with a rotary embedding the softmax warps rotate their rows of Q first
+      bool ok = p.rotary_cos != nullptr ? FW_WAIT(19, 0, &bars->q_rotated, 0) : FW_WAIT(2, 0, &bars->q_full, 0);
       if (ok) ok = FW_WAIT(3, 0, &bars->k_full[0], 0);
       if (ok) {
         tc_fence_after();
@@ -267,6 +270,20 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     const float mul = p.softcap > 0.f ? 1.0f : c1;
     float m_used = -INFINITY, l_run = 0.f;
     bool ok = true;
+
+    if (p.rotary_cos != nullptr && n_tiles > 0) {
+      // Rotary embedding, fused: this thread's softmax row is also its row of the
+      // Q tile the TMA copy left in shared memory; rotate it in place at the
+      // row's own key position (its diagonal) before the first QK MMA reads it.
+      ok = FW_WAIT(20 + t, 0, &bars->q_full, 0);
+      if (ok) {
+        if (row_ok && diag >= 0 && diag < p.rotary_len)
+          rotate_q_row_in_smem<D>(smem + kSmemQ + t * 32768, 16384, row, diag, p);
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bars->q_rotated);
+      }
+    }
 
     for (int j = 0; j < n_tiles && ok; ++j) {
       const int s = j % kKvStages;
@@ -552,6 +569,11 @@ int tcgen05_prefill(const FwPrefillArgs* a, cudaStream_t stream) {
   p.softcap = a->softcap;
   p.packed = packed;
   p.sink_period = a->sink_period;
+  p.rotary_cos = a->rotary_cos;
+  p.rotary_sin = a->rotary_sin;
+  p.rotary_len = a->rotary_len;
+  p.rotary_interleaved = a->rotary_interleaved;
+  p.rotary_bf16 = a->rotary_bf16;
 
   int rc = launch_prefill_plan(a, kStreams * tpb, max_items, const_cast<int*>(p.items), p.tok_stride,
                                p.head_stride, p.status, stream);

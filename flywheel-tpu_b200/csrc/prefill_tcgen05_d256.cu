@@ -44,6 +44,7 @@ struct Bars {
   uint64_t k_full[kStages], k_empty[kStages], v_full[kStages], v_empty[kStages];
   uint64_t s_full[2], p_full[2], pv_done;
   uint64_t drain;  // abort path: completion of the MMAs issued so far
+  uint64_t q_rotated;  // rotary embedding: every softmax warp has rotated its rows of Q
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -93,6 +94,7 @@ prefill_tcgen05_d256_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     }
     mbar_init(&bars->pv_done, 1);
     mbar_init(&bars->drain, 1);
+    mbar_init(&bars->q_rotated, 4);
     bars->abort_flag = 0;
     fence_barrier_init();
   }
@@ -202,7 +204,8 @@ prefill_tcgen05_d256_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         tc_commit(&bars->s_full[j & 1]);
         tc_commit(&bars->k_empty[j % kStages]);
       };
-      bool ok = FW_WAIT(2, 0, &bars->q_full, 0);
+      // with a rotary embedding the softmax warps rotate their rows of Q first
+      bool ok = p.rotary_cos != nullptr ? FW_WAIT(19, 0, &bars->q_rotated, 0) : FW_WAIT(2, 0, &bars->q_full, 0);
       if (ok) ok = FW_WAIT(3, 0, &bars->k_full[0], 0);
       if (ok) {
         tc_fence_after();
@@ -253,6 +256,18 @@ prefill_tcgen05_d256_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     const float mul = p.softcap > 0.f ? 1.0f : c1;
     float m_used = -INFINITY, l_run = 0.f;
     bool ok = true;
+
+    if (p.rotary_cos != nullptr && n_tiles > 0) {
+      // Rotary embedding, fused: rotate this thread's row of the Q tile in shared
+      // memory at the row's own key position before the first QK MMA reads it.
+      ok = FW_WAIT(20, 0, &bars->q_full, 0);
+      if (ok) {
+        if (row_ok && diag >= 0 && diag < p.rotary_len) rotate_q_row_in_smem<kD>(smem + kSmemQ, 16384, row, diag, p);
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bars->q_rotated);
+      }
+    }
 
     for (int j = 0; j < n_tiles && ok; ++j) {
       const int s = j % kStages;
@@ -522,6 +537,11 @@ static int launch_single_tile(const FwPrefillArgs* a, cudaStream_t stream) {
   p.softcap = a->softcap;
   p.packed = packed;
   p.sink_period = a->sink_period;
+  p.rotary_cos = a->rotary_cos;
+  p.rotary_sin = a->rotary_sin;
+  p.rotary_len = a->rotary_len;
+  p.rotary_interleaved = a->rotary_interleaved;
+  p.rotary_bf16 = a->rotary_bf16;
 
   int rc = launch_prefill_plan(a, tpb, max_items, const_cast<int*>(p.items), p.tok_stride, p.head_stride, p.status,
                                stream);

@@ -29,7 +29,74 @@ struct Tc05Params {
   float scale, softcap;
   int packed;       // K and V are packed tensors addressed by token (no block table)
   int sink_period;  // head h uses sinks[h % sink_period]; 0 = one sink per head
+  // Rotary embedding of Q inside the kernel (rotary.py:27-215 of the reference
+  // rotates Q in its attention kernel too): NULL, or (rotary_len, head_dim / 2)
+  // cos / sin tables, f32 or bf16.  A query row on diagonal `pos` is rotated at
+  // position pos in f32 and rounded once to bf16; positions past the table stay
+  // as they are.
+  const void* rotary_cos;
+  const void* rotary_sin;
+  int rotary_len, rotary_interleaved, rotary_bf16;
 };
+
+__device__ __forceinline__ float rotary_entry(const void* table, long long index, int is_bf16) {
+  return is_bf16 ? __bfloat162float(static_cast<const __nv_bfloat16*>(table)[index])
+                 : static_cast<const float*>(table)[index];
+}
+
+// Rotates one query row that a TMA copy left in shared memory as D / 64 blocks
+// of [rows][128 B] with the 128-byte swizzle (16-byte chunk c of row r sits at
+// r * 128 + ((c ^ (r & 7)) << 4) inside its block; `block_bytes` apart).  The
+// caller owns the row; it must fence the generic-proxy writes before the tensor
+// core reads them.
+template <int D>
+__device__ __forceinline__ void rotate_q_row_in_smem(uint8_t* q_tile, int block_bytes, int row, int pos,
+                                                     const Tc05Params& p) {
+  constexpr int kHalf = D / 2;
+  auto chunk_ptr = [&](int element) {  // the 16-byte chunk holding `element` (a multiple of 8) of this row
+    const int block = element >> 6, c = (element & 63) >> 3;
+    return reinterpret_cast<uint4*>(q_tile + block * block_bytes + row * 128 + ((c ^ (row & 7)) << 4));
+  };
+  const long long base = static_cast<long long>(pos) * kHalf;
+  if (!p.rotary_interleaved) {
+    // element i pairs with element i + D / 2
+#pragma unroll
+    for (int i0 = 0; i0 < kHalf; i0 += 8) {
+      uint4* pa = chunk_ptr(i0);
+      uint4* pb = chunk_ptr(i0 + kHalf);
+      uint4 a = *pa, b = *pb;
+      __nv_bfloat16* x1 = reinterpret_cast<__nv_bfloat16*>(&a);
+      __nv_bfloat16* x2 = reinterpret_cast<__nv_bfloat16*>(&b);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float c = rotary_entry(p.rotary_cos, base + i0 + i, p.rotary_bf16);
+        const float sn = rotary_entry(p.rotary_sin, base + i0 + i, p.rotary_bf16);
+        const float u = __bfloat162float(x1[i]), w = __bfloat162float(x2[i]);
+        x1[i] = __float2bfloat16_rn(u * c - w * sn);
+        x2[i] = __float2bfloat16_rn(u * sn + w * c);
+      }
+      *pa = a;
+      *pb = b;
+    }
+  } else {
+    // elements (2 i, 2 i + 1) form pair i
+#pragma unroll
+    for (int e0 = 0; e0 < D; e0 += 8) {
+      uint4* pa = chunk_ptr(e0);
+      uint4 a = *pa;
+      __nv_bfloat16* x = reinterpret_cast<__nv_bfloat16*>(&a);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float c = rotary_entry(p.rotary_cos, base + (e0 >> 1) + i, p.rotary_bf16);
+        const float sn = rotary_entry(p.rotary_sin, base + (e0 >> 1) + i, p.rotary_bf16);
+        const float u = __bfloat162float(x[2 * i]), w = __bfloat162float(x[2 * i + 1]);
+        x[2 * i] = __float2bfloat16_rn(u * c - w * sn);
+        x[2 * i + 1] = __float2bfloat16_rn(u * sn + w * c);
+      }
+      *pa = a;
+    }
+  }
+}
 
 // ---------------------------------------------------------------- tcgen05 wrappers
 __device__ __forceinline__ void tmem_alloc(uint32_t* smem_slot, uint32_t cols) {

@@ -84,6 +84,15 @@ class FwPrefillArgs(ctypes.Structure):
         ("v_packed", c_ptr), ("cu_seqlens_k", c_ptr), ("total_k", i32),
         ("kv_token_major", i32), ("rotary_k", i32), ("sink_period", i32),
         ("window_right", i32), ("kv_request_stride", i32), ("route", i32),
+        ("first_request", c_ptr),
+    ]
+
+
+class FwExtendArgs(ctypes.Structure):
+    _fields_ = [
+        ("attn", FwPrefillArgs), ("num_decode", c_ptr), ("k_new", c_ptr),
+        ("v_new", c_ptr), ("slices", c_ptr), ("num_slices", c_ptr),
+        ("num_columns", i32), ("total_tokens", i32),
     ]
 
 
@@ -121,6 +130,8 @@ EXPORTS = {
     "fw_write_kv_pages": (ctypes.c_int, [ctypes.POINTER(FwWritePagesArgs), c_ptr]),
     "fw_prefill_workspace_bytes": (u64, [ctypes.POINTER(FwPrefillArgs)]),
     "fw_prefill_paged": (ctypes.c_int, [ctypes.POINTER(FwPrefillArgs), c_ptr]),
+    "fw_extend_workspace_bytes": (u64, [ctypes.POINTER(FwExtendArgs)]),
+    "fw_extend_mixed": (ctypes.c_int, [ctypes.POINTER(FwExtendArgs), c_ptr]),
     "fw_attention_packed_workspace_bytes": (u64, [ctypes.POINTER(FwPrefillArgs)]),
     "fw_attention_packed": (ctypes.c_int, [ctypes.POINTER(FwPrefillArgs), c_ptr]),
     "fw_lse_combine": (ctypes.c_int, [ctypes.POINTER(FwCombineArgs), c_ptr]),

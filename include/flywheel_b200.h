@@ -291,6 +291,11 @@ typedef struct FwPrefillArgs {
    * split-KV kernel below that); the other two pin it for this call where the
    * pinned kernel can take the shapes.  Per call, no process-wide switch. */
   int32_t route;
+  /* NULL, or one device int: requests below *first_request are left out (no
+   * query blocks are made for them and their packed rows are not written), as if
+   * the request window started there.  What a mixed step needs: its leading
+   * one-token requests go to the decode kernel (see fw_extend_mixed). */
+  const int32_t* first_request;
 } FwPrefillArgs;
 
 #define FW_ROUTE_AUTO 0
@@ -299,6 +304,44 @@ typedef struct FwPrefillArgs {
 
 uint64_t fw_prefill_workspace_bytes(const FwPrefillArgs* args);
 int fw_prefill_paged(const FwPrefillArgs* args, void* stream);
+
+/*
+ * One mixed serving step over the paged pool: the leading *num_decode requests
+ * are one-token decode rows, the requests after them (up to *num_active) are
+ * prefill chunks; what flywheel_tpu_extend of the reference's serving backend
+ * does with a page write, a decode call and a varlen call over a request window
+ * slid past the decode rows (patches/tpu-inference.patch:8219-8320).  Here it is
+ * one entry point and one launch sequence on `stream`, with every count read on
+ * the device: (1) when k_new is given, the slice-table page write of all
+ * scheduled tokens (fw_write_kv_pages); (2) the split-KV decode kernel over
+ * requests [0, *num_decode), reading the pool (nothing appended: the rows were
+ * just written), so a one-token row never occupies a 256-row tensor-core tile;
+ * (3) the paged prefill over requests [*num_decode, *num_active), whose query
+ * blocks start at the first prefill request without the host sliding any array.
+ *
+ * attn describes the step like a fw_prefill_paged call with token_major = 1:
+ * q / out (total_q, nheads, head_dim) bf16, request r owns rows
+ * [cu_seqlens_q[r], cu_seqlens_q[r + 1]) (one row each for the decode requests),
+ * seqused_k[r] = its KV length with this step's tokens included.  attn.lse and
+ * the rotary fields must be NULL; attn.first_request is ignored.  Rows at or past
+ * cu_seqlens_q[*num_active] return 0.  The workspace (fw_extend_workspace_bytes)
+ * holds both kernels' scratch; one status word at its head serves both.
+ */
+typedef struct FwExtendArgs {
+  FwPrefillArgs attn;
+  const int32_t* num_decode;   /* device int, 0 <= *num_decode <= *num_active */
+  /* Optional page write before attention (NULL k_new = the pool is already
+   * written); fields as in FwWritePagesArgs. */
+  const void* k_new;
+  const void* v_new;
+  const int32_t* slices;
+  const int32_t* num_slices;
+  int32_t num_columns;
+  int32_t total_tokens;
+} FwExtendArgs;
+
+uint64_t fw_extend_workspace_bytes(const FwExtendArgs* args);
+int fw_extend_mixed(const FwExtendArgs* args, void* stream);
 
 /*
  * Forward attention of packed q over packed K/V without a block table: the

@@ -32,7 +32,7 @@ def test_struct_layouts_match_the_header(tmp_path):
     import subprocess
     from flywheel_tpu.softmax_attention import _native
     structs = ["FwDecodeArgs", "FwAppendArgs", "FwWritePagesArgs", "FwPrefillArgs", "FwCombineArgs",
-               "FwExchangeArgs", "FwShardStepArgs"]
+               "FwExchangeArgs", "FwShardStepArgs", "FwExtendArgs"]
     lines = ['#include <stddef.h>', '#include <stdio.h>', '#include "flywheel_b200.h"', 'int main(void) {']
     for name in structs:
         lines.append(f'  printf("{name} %zu\\n", sizeof({name}));')
