@@ -137,9 +137,10 @@ static uint64_t rope_copy_bytes(const FwPrefillArgs* a) {
 }
 
 // ---------------------------------------------------------------- gather for the tensor-core kernel
-// The tensor-core kernel reads bf16 K/V through 64-token TMA boxes.  Pools it
-// cannot read in place (fp8, or pages that are not a multiple of 64 tokens) are
-// first copied, request by request, into bf16 K and V scratch tensors of
+// The tensor-core kernels read K/V through 64-token TMA boxes; the head_dim 128
+// kernel reads bf16 and fp8 pools in place (it widens fp8 tiles itself).  Pools
+// they cannot read in place (pages that are not a multiple of 64 tokens; fp8 at
+// head_dim 256) are first copied, request by request, into bf16 K and V scratch tensors of
 // (batch * capacity, nheads_k, head_dim), capacity = pages_per_seq * page_size:
 // request r's key t lands in row r * capacity + t.  fp8 widens exactly to bf16;
 // the descales stay where they were (score scale and output scale).  One block

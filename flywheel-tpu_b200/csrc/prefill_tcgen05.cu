@@ -33,6 +33,14 @@ constexpr int kSmemK = kStreams * 32768;       // stages x 2 halves x [128 keys]
 constexpr int kSmemV = kSmemK + kKvStages * 32768;
 constexpr int kSmemBar = kSmemV + kKvStages * 32768;
 constexpr int kSmemBytes = kSmemBar + 256;
+// fp8 pools: one more region behind the barriers, where TMA lands the fp8 K and V
+// tiles ([128 keys][128 B] each) that the converter warps widen into the bf16
+// operand buffers above.
+constexpr int kSmemF8K = (kSmemBytes + 1023) & ~1023;  // swizzled TMA destinations sit on 1024-byte boundaries
+constexpr int kSmemF8V = kSmemF8K + 16384;
+constexpr int kSmemBytesFp8 = kSmemF8V + 16384;
+static_assert(kSmemBytesFp8 <= 227 * 1024, "shared memory budget of the fp8 variant");
+constexpr int kConverterWarps = 2;
 
 struct Bars {
   uint64_t q_full;
@@ -40,6 +48,7 @@ struct Bars {
   uint64_t s_full[kStreams], p_full[kStreams], pv_done[kStreams];
   uint64_t drain;  // abort path: completion of the MMAs issued so far
   uint64_t q_rotated;  // rotary embedding: every softmax warp has rotated its rows of Q
+  uint64_t f8k_full, f8k_empty, f8v_full, f8v_empty;  // fp8 pools: the staging tiles
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -52,10 +61,20 @@ __device__ __forceinline__ uint32_t tmem_s(uint32_t base, int t) { return base +
 // D = head_dim, 128 or 64 (64 for packed K/V only).  Shared memory keeps the
 // 128-wide layout either way: operands are stored as 64-element (128-byte) halves,
 // and at 64 the second half of every tile simply stays unused.
-template <int D>
-__global__ void __launch_bounds__(64 + kStreams * 128, 1)
+//
+// KVT = pool element type.  A bf16 pool is copied by TMA straight into the
+// operand buffers.  An fp8 pool (e4m3 / e5m2, head_dim 128, paged) is read in
+// place too: TMA lands each fp8 K and V tile in a staging buffer and two
+// converter warps (10, 11) widen it - exactly: every fp8 value is a bf16 value -
+// into the swizzled bf16 operand buffer the MMAs read, tile by tile, inside the
+// kernel (the reference widens per block inside its kernel as well,
+// kernels/fwd_paged.py:260-328).  The descales stay in the score scale and the
+// output scale.
+template <int D, int KVT = FW_DTYPE_BF16>
+__global__ void __launch_bounds__(64 + kStreams * 128 + (KVT == FW_DTYPE_BF16 ? 0 : kConverterWarps * 32), 1)
 prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv,
                        const __grid_constant__ CUtensorMap map_v, const Tc05Params p) {
+  constexpr bool kFp8 = KVT != FW_DTYPE_BF16;
   extern __shared__ __align__(1024) uint8_t smem[];
   Bars* bars = reinterpret_cast<Bars*>(smem + kSmemBar);
   volatile int* abort_flag = &bars->abort_flag;
@@ -85,11 +104,16 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   if (threadIdx.x == 0) {
     mbar_init(&bars->q_full, 1);
     for (int s = 0; s < kKvStages; ++s) {
-      mbar_init(&bars->k_full[s], 1);
-      mbar_init(&bars->v_full[s], 1);
+      // filled by TMA (one arrival with a byte count), or by the converter warps
+      mbar_init(&bars->k_full[s], kFp8 ? kConverterWarps : 1);
+      mbar_init(&bars->v_full[s], kFp8 ? kConverterWarps : 1);
       mbar_init(&bars->k_empty[s], 1);
       mbar_init(&bars->v_empty[s], 1);
     }
+    mbar_init(&bars->f8k_full, 1);
+    mbar_init(&bars->f8v_full, 1);
+    mbar_init(&bars->f8k_empty, kConverterWarps);
+    mbar_init(&bars->f8v_empty, kConverterWarps);
     for (int t = 0; t < kStreams; ++t) {
       mbar_init(&bars->s_full[t], 1);
       mbar_init(&bars->p_full[t], 4);
@@ -127,8 +151,9 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         const int s = j % kKvStages;
         const uint32_t round = j / kKvStages;
         // K of a stage is free once the QK MMAs of its tile are done, V once
-        // the PV MMAs are: K therefore runs further ahead than V.
-        if (!FW_WAIT(1, j, &bars->k_empty[s], (round & 1) ^ 1)) {
+        // the PV MMAs are: K therefore runs further ahead than V.  (fp8: the
+        // staging tile is free once the converters have widened it.)
+        if (!(kFp8 ? FW_WAIT(1, j, &bars->f8k_empty, (j & 1) ^ 1) : FW_WAIT(1, j, &bars->k_empty[s], (round & 1) ^ 1))) {
           ok = false;
           break;
         }
@@ -155,6 +180,22 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             page[sub] = 0;
           }
           tok[sub] = pos - page_idx * p.page_size;
+        }
+        if constexpr (kFp8) {
+          // one 64-token box of a head plane is [64][128 B] of fp8
+          mbar_arrive_expect_tx(&bars->f8k_full, subs * 64 * 128);
+          for (int sub = 0; sub < subs; ++sub)
+            tma_load_4d(smem + kSmemF8K + sub * 8192, &map_kv, &bars->f8k_full, 0, 2 * h, tok[sub], page[sub]);
+          k_armed = j + 1;
+          if (!FW_WAIT(18, j, &bars->f8v_empty, (j & 1) ^ 1)) {
+            ok = false;
+            break;
+          }
+          mbar_arrive_expect_tx(&bars->f8v_full, subs * 64 * 128);
+          for (int sub = 0; sub < subs; ++sub)
+            tma_load_4d(smem + kSmemF8V + sub * 8192, &map_kv, &bars->f8v_full, 0, 2 * h + 1, tok[sub], page[sub]);
+          v_armed = j + 1;
+          continue;
         }
         mbar_arrive_expect_tx(&bars->k_full[s], subs * 64 * D * 2);
         for (int sub = 0; sub < subs; ++sub)
@@ -183,10 +224,15 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         *abort_flag = 1;
         report_timeout(p.status);
         drain_wait(&bars->q_full, 0);
-        for (int j = max(0, k_armed - kKvStages); j < k_armed; ++j)
-          drain_wait(&bars->k_full[j % kKvStages], (j / kKvStages) & 1);
-        for (int j = max(0, v_armed - kKvStages); j < v_armed; ++j)
-          drain_wait(&bars->v_full[j % kKvStages], (j / kKvStages) & 1);
+        if constexpr (kFp8) {
+          if (k_armed > 0) drain_wait(&bars->f8k_full, (k_armed - 1) & 1);
+          if (v_armed > 0) drain_wait(&bars->f8v_full, (v_armed - 1) & 1);
+        } else {
+          for (int j = max(0, k_armed - kKvStages); j < k_armed; ++j)
+            drain_wait(&bars->k_full[j % kKvStages], (j / kKvStages) & 1);
+          for (int j = max(0, v_armed - kKvStages); j < v_armed; ++j)
+            drain_wait(&bars->v_full[j % kKvStages], (j / kKvStages) & 1);
+        }
       }
     }
   } else if (n_tiles > 0 && warp == 1) {
@@ -251,6 +297,76 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         report_timeout(p.status);
         tc_commit(&bars->drain);
         drain_wait(&bars->drain, 0);
+      }
+    }
+  } else if (kFp8 && warp >= 2 + kStreams * 4) {
+    // ------------------------------------------------------------ fp8 -> bf16 converters
+    // Each 16-byte chunk of a staged fp8 row (16 head_dim elements of one key)
+    // becomes two 16-byte chunks of the bf16 operand tile: half d / 64, row =
+    // key, chunk (d % 64) / 8 under the 128-byte swizzle, the layout a TMA copy
+    // of a bf16 pool would have produced.
+    if (n_tiles > 0) {
+      const int ct = (warp - (2 + kStreams * 4)) * 32 + lane;  // 0 .. 63
+      bool ok = true;
+      // Thread ct always takes 16-byte chunk ct % 8 of keys ct / 8, ct / 8 + 8, ...:
+      // the swizzle term (key & 7) is then a per-thread constant and a step is
+      // 1024 bytes in both buffers.  Eight chunks are loaded before any is widened
+      // so the conversions of different keys overlap.
+      const int c8 = ct & 7, r0 = ct >> 3;
+      const int src_off = r0 * 128 + ((c8 ^ r0) << 4);
+      const int c = (c8 & 3) * 2;
+      const int dst_off = (c8 >> 2) * 16384 + r0 * 128;
+      const int dst_a = dst_off + ((c ^ r0) << 4), dst_b = dst_off + (((c + 1) ^ r0) << 4);
+      auto widen_tile = [&](const uint8_t* staged, uint8_t* tile) {
+#pragma unroll 1
+        for (int n0 = 0; n0 < kBN / 8; n0 += 8) {
+          uint4 raw[8];
+#pragma unroll
+          for (int n = 0; n < 8; ++n) raw[n] = *reinterpret_cast<const uint4*>(staged + src_off + (n0 + n) * 1024);
+#pragma unroll
+          for (int n = 0; n < 8; ++n) {
+            const uint32_t w[4] = {raw[n].x, raw[n].y, raw[n].z, raw[n].w};
+            uint32_t wide[8];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const uint32_t lo = fp8_half_to_f16x2<KVT, false>(w[i]), hi = fp8_half_to_f16x2<KVT, true>(w[i]);
+              const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&lo));
+              const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&hi));
+              wide[2 * i] = pack_bf16(a.x, a.y);
+              wide[2 * i + 1] = pack_bf16(b.x, b.y);
+            }
+            *reinterpret_cast<uint4*>(tile + dst_a + (n0 + n) * 1024) = make_uint4(wide[0], wide[1], wide[2], wide[3]);
+            *reinterpret_cast<uint4*>(tile + dst_b + (n0 + n) * 1024) = make_uint4(wide[4], wide[5], wide[6], wide[7]);
+          }
+        }
+      };
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        const int s = j % kKvStages;
+        const uint32_t round = j / kKvStages;
+        ok = FW_WAIT(24, j, &bars->f8k_full, j & 1);
+        if (ok) ok = FW_WAIT(25, j, &bars->k_empty[s], (round & 1) ^ 1);
+        if (!ok) break;
+        widen_tile(smem + kSmemF8K, smem + kSmemK + s * 32768);
+        fence_proxy_async_smem();  // the tensor core reads what these threads wrote
+        __syncwarp();
+        if (lane == 0) {
+          mbar_arrive(&bars->k_full[s]);
+          mbar_arrive(&bars->f8k_empty);
+        }
+        ok = FW_WAIT(26, j, &bars->f8v_full, j & 1);
+        if (ok) ok = FW_WAIT(27, j, &bars->v_empty[s], (round & 1) ^ 1);
+        if (!ok) break;
+        widen_tile(smem + kSmemF8V, smem + kSmemV + s * 32768);
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          mbar_arrive(&bars->v_full[s]);
+          mbar_arrive(&bars->f8v_empty);
+        }
+      }
+      if (!ok && lane == 0) {
+        *abort_flag = 1;
+        report_timeout(p.status);
       }
     }
   } else if (warp >= 2 && (warp - 2) / 4 < n_streams) {
@@ -337,14 +453,26 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 top1 = fmaxf(top1, y1);
               }
               float p0, p1;
-              // the loop is fully unrolled, so this choice is made at compile time
-              if (FW_EXP2_POLY_EVERY > 0 && ((i >> 1) % (FW_EXP2_POLY_EVERY > 0 ? FW_EXP2_POLY_EVERY : 1)) == 0)
-                exp2_pair<true>(y2, p0, p1);
-              else
-                exp2_pair<false>(y2, p0, p1);
+              uint32_t pk;
+              if constexpr (FW_EXP2_BF16X2 != 0) {
+                // both exponentials in one special-function op, on bf16 operands: P is
+                // rounded to bf16 for the PV MMA anyway, and the row sum below adds the
+                // rounded values, so l matches the P the MMA sees
+                float y0, y1;
+                unpack2(y2, y0, y1);
+                pk = exp2_bf16x2(pack_bf16(y0, y1));
+                p0 = __uint_as_float(pk << 16);
+                p1 = __uint_as_float(pk & 0xffff0000u);
+              } else {
+                // the loop is fully unrolled, so this choice is made at compile time
+                if (FW_EXP2_POLY_EVERY > 0 && ((i >> 1) % (FW_EXP2_POLY_EVERY > 0 ? FW_EXP2_POLY_EVERY : 1)) == 0)
+                  exp2_pair<true>(y2, p0, p1);
+                else
+                  exp2_pair<false>(y2, p0, p1);
+                pk = pack_bf16(p0, p1);
+              }
               sum2 = add2(sum2, pack2(p0, p1));
-              const uint32_t pk = pack_bf16(p0, p1);
-              if constexpr (!kTrueMax) pmax = max_bf16x2(pmax, pk);
+              if constexpr (!kTrueMax && FW_OVER_BY_SUM == 0) pmax = max_bf16x2(pmax, pk);
               packed[half][c * 16 + (i >> 1)] = pk;
             }
         }
@@ -353,7 +481,8 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         sum = s0 + s1;
         top = fmaxf(top0, top1);  // row max minus the base (the row max itself when the base is 0)
         // bf16 bit patterns of non-negative values order like integers
-        over = max(pmax & 0xffffu, pmax >> 16) > 0x4380u;  // bf16(256.0) = 2^kRescaleThreshold
+        if constexpr (FW_OVER_BY_SUM != 0) over = sum > 256.0f;  // no P can be above 2^8 unless their sum is
+        else over = max(pmax & 0xffffu, pmax >> 16) > 0x4380u;  // bf16(256.0) = 2^kRescaleThreshold
       };
       static_assert(kRescaleThreshold == 8.0f, "the bf16 constant above is 2^8");
       float alpha = 1.f;
@@ -482,7 +611,8 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 bool tcgen05_prefill_supported(const FwPrefillArgs* a) {
   if (a->head_dim == 256) return tcgen05_d256_supported(a);
   const bool packed_kv = a->block_table == nullptr && a->v_packed != nullptr;
-  if (a->kv_dtype != FW_DTYPE_BF16) return false;
+  // fp8 pools are widened inside the kernel: paged, head_dim 128 (a head plane is one 128-byte row)
+  if (a->kv_dtype != FW_DTYPE_BF16 && (packed_kv || a->head_dim != 128)) return false;
   if (a->head_dim != 128 && !(a->head_dim == 64 && packed_kv)) return false;
   if (a->nheads_k <= 0 || a->nheads % a->nheads_k) return false;
   const int group = a->nheads / a->nheads_k;
@@ -604,19 +734,37 @@ int tcgen05_prefill(const FwPrefillArgs* a, cudaStream_t stream) {
     if (rc != FW_OK) return rc;
   } else {
     // pool viewed as (head_dim, head planes [k0,v0,k1,v1,...], tokens in page, pages)
-    const uint64_t planes = 2ull * a->nheads_k;
-    const uint64_t row_bytes = planes * 256;
-    const uint64_t dims[4] = {128, planes, static_cast<uint64_t>(a->page_size), static_cast<uint64_t>(a->num_pages)};
-    const uint64_t strides[3] = {256, row_bytes, row_bytes * a->page_size};
-    const uint32_t box[4] = {64, 1, 64, 1};
-    rc = encode_tensor_map_bf16(&map_kv, 4, a->kv_cache, dims, strides, box);
+    if (a->kv_dtype == FW_DTYPE_BF16) {
+      const uint64_t planes = 2ull * a->nheads_k;
+      const uint64_t row_bytes = planes * 256;
+      const uint64_t dims[4] = {128, planes, static_cast<uint64_t>(a->page_size), static_cast<uint64_t>(a->num_pages)};
+      const uint64_t strides[3] = {256, row_bytes, row_bytes * a->page_size};
+      const uint32_t box[4] = {64, 1, 64, 1};
+      rc = encode_tensor_map_bf16(&map_kv, 4, a->kv_cache, dims, strides, box);
+    } else {
+      // fp8: bytes; a head plane of a token is one 128-byte row, an odd head count carries a pad head
+      const uint64_t planes = 2ull * ((a->nheads_k + 1) / 2 * 2);
+      const uint64_t row_bytes = planes * 128;
+      const uint64_t dims[4] = {128, planes, static_cast<uint64_t>(a->page_size), static_cast<uint64_t>(a->num_pages)};
+      const uint64_t strides[3] = {128, row_bytes, row_bytes * a->page_size};
+      const uint32_t box[4] = {128, 1, 64, 1};
+      rc = encode_tensor_map_u8_4d(&map_kv, a->kv_cache, dims, strides, box);
+    }
     if (rc != FW_OK) return rc;
     map_v = map_kv;
   }
-  auto kernel = d == 64 ? prefill_tcgen05_kernel<64> : prefill_tcgen05_kernel<128>;
-  cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+  using Kernel = void (*)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const Tc05Params);
+  Kernel kernel = d == 64 ? prefill_tcgen05_kernel<64> : prefill_tcgen05_kernel<128>;
+  int smem_bytes = kSmemBytes, threads = 64 + kStreams * 128;
+  if (a->kv_dtype != FW_DTYPE_BF16) {
+    kernel = a->kv_dtype == FW_DTYPE_E4M3 ? prefill_tcgen05_kernel<128, FW_DTYPE_E4M3>
+                                          : prefill_tcgen05_kernel<128, FW_DTYPE_E5M2>;
+    smem_bytes = kSmemBytesFp8;
+    threads += kConverterWarps * 32;
+  }
+  cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
   if (err != cudaSuccess) {
-    set_error("cudaFuncSetAttribute(%d bytes): %s", kSmemBytes, cudaGetErrorString(err));
+    set_error("cudaFuncSetAttribute(%d bytes): %s", smem_bytes, cudaGetErrorString(err));
     return FW_ERR_LAUNCH;
   }
   dim3 grid(a->nheads_k, max_items);
@@ -625,8 +773,8 @@ int tcgen05_prefill(const FwPrefillArgs* a, cudaStream_t stream) {
   pdl.val.programmaticStreamSerializationAllowed = 1;
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = grid;
-  cfg.blockDim = dim3(64 + kStreams * 128);
-  cfg.dynamicSmemBytes = kSmemBytes;
+  cfg.blockDim = dim3(threads);
+  cfg.dynamicSmemBytes = smem_bytes;
   cfg.stream = stream;
   cfg.attrs = &pdl;
   cfg.numAttrs = 1;

@@ -315,14 +315,26 @@ prefill_tcgen05_d256_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 top1 = fmaxf(top1, y1);
               }
               float p0, p1;
-              // the loop is fully unrolled, so this choice is made at compile time
-              if (FW_EXP2_POLY_EVERY > 0 && ((i >> 1) % (FW_EXP2_POLY_EVERY > 0 ? FW_EXP2_POLY_EVERY : 1)) == 0)
-                exp2_pair<true>(y2, p0, p1);
-              else
-                exp2_pair<false>(y2, p0, p1);
+              uint32_t pk;
+              if constexpr (FW_EXP2_BF16X2 != 0) {
+                // both exponentials in one special-function op, on bf16 operands: P is
+                // rounded to bf16 for the PV MMA anyway, and the row sum below adds the
+                // rounded values, so l matches the P the MMA sees
+                float y0, y1;
+                unpack2(y2, y0, y1);
+                pk = exp2_bf16x2(pack_bf16(y0, y1));
+                p0 = __uint_as_float(pk << 16);
+                p1 = __uint_as_float(pk & 0xffff0000u);
+              } else {
+                // the loop is fully unrolled, so this choice is made at compile time
+                if (FW_EXP2_POLY_EVERY > 0 && ((i >> 1) % (FW_EXP2_POLY_EVERY > 0 ? FW_EXP2_POLY_EVERY : 1)) == 0)
+                  exp2_pair<true>(y2, p0, p1);
+                else
+                  exp2_pair<false>(y2, p0, p1);
+                pk = pack_bf16(p0, p1);
+              }
               sum2 = add2(sum2, pack2(p0, p1));
-              const uint32_t pk = pack_bf16(p0, p1);
-              if constexpr (!kTrueMax) pmax = max_bf16x2(pmax, pk);
+              if constexpr (!kTrueMax && FW_OVER_BY_SUM == 0) pmax = max_bf16x2(pmax, pk);
               packed[half][c * 16 + (i >> 1)] = pk;
             }
         }
@@ -330,7 +342,8 @@ prefill_tcgen05_d256_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         unpack2(sum2, s0, s1);
         sum = s0 + s1;
         top = fmaxf(top0, top1);
-        over = max(pmax & 0xffffu, pmax >> 16) > 0x4380u;  // bf16(256.0) = 2^kRescaleThreshold
+        if constexpr (FW_OVER_BY_SUM != 0) over = sum > 256.0f;  // no P can be above 2^8 unless their sum is
+        else over = max(pmax & 0xffffu, pmax >> 16) > 0x4380u;  // bf16(256.0) = 2^kRescaleThreshold
       };
       static_assert(kRescaleThreshold == 8.0f, "the bf16 constant above is 2^8");
       float alpha = 1.f;

@@ -213,6 +213,22 @@ __host__ __device__ constexpr uint32_t instr_desc(int n, bool b_mn_major) {
 #ifndef FW_EXP2_POLY_EVERY
 #define FW_EXP2_POLY_EVERY 0
 #endif
+// Experiment switches of the softmax inner loop (see the measurements beside the
+// defaults): FW_EXP2_BF16X2 computes both exponentials of a pair with one
+// ex2.approx.ftz.bf16x2; FW_OVER_BY_SUM detects a score that outran the exponent
+// base from the row sum instead of a running bf16 max of P.
+#ifndef FW_EXP2_BF16X2
+#define FW_EXP2_BF16X2 0
+#endif
+#ifndef FW_OVER_BY_SUM
+#define FW_OVER_BY_SUM 0
+#endif
+__device__ __forceinline__ uint32_t exp2_bf16x2(uint32_t y) {
+  uint32_t r;
+  asm("ex2.approx.ftz.bf16x2 %0, %1;" : "=r"(r) : "r"(y));
+  return r;
+}
+
 template <bool kPoly>
 __device__ __forceinline__ void exp2_pair(uint64_t y2, float& p0, float& p1) {
   float y0, y1;
