@@ -10,7 +10,7 @@ import ctypes
 import os
 import pathlib
 
-import torch
+from flywheel_tpu.softmax_attention import _cuda
 
 PACKAGE_ROOT = pathlib.Path(__file__).resolve().parents[2]
 LIBRARY_PATH = PACKAGE_ROOT / "lib" / "libflywheel_b200.so"
@@ -180,24 +180,49 @@ def check(code: int) -> None:
 
 
 def current_stream(device) -> int:
-    return torch.cuda.current_stream(device).cuda_stream
+    from flywheel_tpu.softmax_attention import _arrays
+    return _arrays.current_stream(device)
+
+
+class Workspace:
+    """Scratch memory for the kernels: cudaMalloc'ed through libcudart, zeroed
+    once, 256-byte aligned (cudaMalloc aligns to at least that).  It looks
+    enough like a tensor (data_ptr / numel) for the callers that pass one."""
+
+    def __init__(self, nbytes, device_index, stream):
+        _cuda.set_device(device_index)
+        self.nbytes, self.device_index = int(nbytes), device_index
+        self.ptr = _cuda.malloc(self.nbytes)
+        _cuda.memset(self.ptr, 0, self.nbytes, stream)
+
+    def data_ptr(self):
+        return self.ptr
+
+    def numel(self):
+        return self.nbytes
+
+    def __del__(self):
+        _cuda.free(self.ptr)
 
 
 _WORKSPACES: dict = {}
 
 
-def workspace(device, nbytes: int) -> torch.Tensor:
-    """A zero-initialised, 256-byte aligned scratch buffer on `device`, grown
-    on demand and reused by later calls on the same device and stream."""
-    key = (device.index, torch.cuda.current_stream(device).cuda_stream)
+def workspace(device, nbytes: int) -> Workspace:
+    """A zero-initialised scratch buffer on `device`, grown on demand and reused
+    by later calls on the same device and stream."""
+    stream = current_stream(device)
+    key = (device.index, stream)
     buf = _WORKSPACES.get(key)
     if buf is None or buf.numel() < nbytes:
-        buf = torch.zeros(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        if buf is not None:
+            _cuda.synchronize(stream)   # the old buffer may still be in use on this stream
+        buf = Workspace(max(nbytes, 1 << 20), device.index, stream)
         _WORKSPACES[key] = buf
     return buf
 
 
-def read_status(buf: torch.Tensor, device) -> int:
+def read_status(buf, device) -> int:
     """The device status word at the head of workspace `buf` (the OR of the
     FW_STATUS_* bits reported since the last read), cleared once read.
     Synchronises the current stream."""
@@ -224,7 +249,7 @@ def status_check_enabled() -> bool:
     return os.environ.get("FLYWHEEL_CHECK_STATUS", "0") not in ("", "0")
 
 
-def raise_on_status(buf: torch.Tensor, device) -> None:
+def raise_on_status(buf, device) -> None:
     """Reads the status word of `buf` when the check is enabled and raises
     TimeoutError (a wait gave up) or RuntimeError (bad page) if it is set."""
     if not status_check_enabled():

@@ -6,15 +6,13 @@ project: same name, arguments, layouts, return tuples and error behaviour.
 Differences, all widening: page_size may be any multiple of 16 (the reference
 needs 128), a (batch, seqlen_q, ...) verify window runs on the decode kernel
 also with a left window, and the arrays are torch / NumPy / DLPack arrays
-instead of JAX arrays (see _arrays).
+instead of JAX arrays (see _arrays; torch is not needed for NumPy callers).
 """
 
 from __future__ import annotations
 
 import ctypes
 import math
-
-import torch
 
 from flywheel_tpu.softmax_attention import _arrays, _native
 from flywheel_tpu.softmax_attention.config import (
@@ -254,7 +252,7 @@ def flash_attn_with_kvcache(
     device = _arrays.pick_device(k_cache, q)
     lengths = _arrays.to_device(cache_seqlens, device, dtype="int32")
     if lengths.ndim == 0:
-        lengths = lengths.reshape(1).expand(batch)
+        lengths = _arrays.broadcast_scalar(lengths, batch, device)
     if tuple(lengths.shape) != (batch,):
         raise ValueError(
             f"cache_seqlens must be a scalar or ({batch},) int array; got"
@@ -298,10 +296,9 @@ def flash_attn_with_kvcache(
     stream = _native.current_stream(device)
     lse = None
     if not is_extend or is_folded:
-        out = torch.empty_like(q_dev)
+        out = _arrays.empty_like(q_dev)
         if return_softmax_lse:
-            lse = torch.empty((batch, nheads, seqlen_q), dtype=torch.float32,
-                              device=device)
+            lse = _arrays.empty((batch, nheads, seqlen_q), "float32", device)
         kernel_has_new = has_new
         args = _native.FwDecodeArgs(
             q=q_dev.data_ptr(), out=out.data_ptr(), lse=_arrays.data_ptr(lse),
@@ -342,10 +339,10 @@ def flash_attn_with_kvcache(
                 part.cache_batch_idx = cache_batch_idx[first:].data_ptr()
             elif first:
                 # identity mapping of a later slice: spell the cache rows out
-                rows_idx = torch.arange(first, first + rows, dtype=torch.int32, device=device)
+                rows_idx = _arrays.arange_scaled(rows, 1, device, first=first)
                 part.cache_batch_idx = rows_idx.data_ptr()
             if active is not None and first:
-                rebased = (active - first).clamp_(0, rows)
+                rebased = _arrays.rebase_count(active, first, rows)
                 part.num_active = rebased.data_ptr()
             nbytes = lib.fw_decode_workspace_bytes(ctypes.byref(part))
             if nbytes == 0:
@@ -368,7 +365,7 @@ def flash_attn_with_kvcache(
             packed_q, packed_k, packed_v = q_dev, k_dev, v_dev
             packed_max = max_seqlen_q
         else:
-            cu = torch.arange(batch + 1, dtype=torch.int32, device=device) * seqlen_q
+            cu = _arrays.arange_scaled(batch + 1, seqlen_q, device)
             packed_q = q_dev.reshape(-1, nheads, head_dim)
             packed_k = k_dev.reshape(-1, nheads_k, head_dim) if has_new else None
             packed_v = v_dev.reshape(-1, nheads_k, head_dim) if has_new else None
@@ -378,7 +375,7 @@ def flash_attn_with_kvcache(
                           active, nheads_k=nheads_k)
             # seqused_k = cache_seqlens + this request's new tokens.  (Index
             # arithmetic on metadata; the attention itself is the CUDA kernel.)
-            seqused = lengths + (cu[1:] - cu[:-1])
+            seqused = _arrays.add_token_counts(lengths, cu)
         else:
             seqused = lengths
         out, lse = paged_prefill_device(
@@ -391,11 +388,10 @@ def flash_attn_with_kvcache(
         if not is_ragged:
             out = out.reshape(q_dev.shape)
             if lse is not None:
-                lse = lse.reshape(nheads, batch, seqlen_q).permute(1, 0, 2).contiguous()
+                lse = _arrays.heads_first_to_batch_first(lse, nheads, batch, seqlen_q)
 
     caches_out = tuple(
-        original if (isinstance(original, torch.Tensor) and original.is_cuda)
-        else _arrays.like(updated, original)
+        original if _arrays.is_device_resident(original) else _arrays.like(updated, original)
         for original, updated in zip(cache_operands, cache_dev))
     out = _arrays.like(out, q)
     if return_softmax_lse:

@@ -18,8 +18,6 @@ from __future__ import annotations
 import ctypes
 import math
 
-import torch
-
 from flywheel_tpu.softmax_attention import _arrays, _native
 from flywheel_tpu.softmax_attention.config import SUPPORTED_HEAD_DIMS
 from flywheel_tpu.softmax_attention.inputs import descale_operand, sinks_operand
@@ -95,7 +93,7 @@ def paged_extend(q, k, v, kv_cache, kv_lens, page_indices, cu_q_lens,
         raise ValueError("the KV cache must be contiguous.")
     table = _arrays.to_device(page_indices, device, dtype="int32").contiguous().reshape(batch, -1)
     q_dev = _arrays.to_device(q, device).contiguous()
-    out = torch.empty_like(q_dev)
+    out = _arrays.empty_like(q_dev)
     lens = _arrays.to_device(kv_lens, device, dtype="int32").contiguous()
     cu = _arrays.to_device(cu_q_lens, device, dtype="int32").contiguous()
     decode_count = _count_operand(num_decode, "num_decode", device)
@@ -139,5 +137,5 @@ def paged_extend(q, k, v, kv_cache, kv_lens, page_indices, cu_q_lens,
     args.attn.workspace, args.attn.workspace_bytes = scratch.data_ptr(), scratch.numel()
     _native.check(lib.fw_extend_mixed(ctypes.byref(args), stream))
     _native.raise_on_status(scratch, device)
-    cache_out = kv_cache if (isinstance(kv_cache, torch.Tensor) and kv_cache.is_cuda) else _arrays.like(pool, kv_cache)
+    cache_out = kv_cache if _arrays.is_device_resident(kv_cache) else _arrays.like(pool, kv_cache)
     return _arrays.like(out, q), cache_out

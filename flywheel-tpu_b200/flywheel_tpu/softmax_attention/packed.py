@@ -14,7 +14,6 @@ from __future__ import annotations
 import ctypes
 import math
 
-import torch
 
 from flywheel_tpu.softmax_attention import _arrays, _native
 from flywheel_tpu.softmax_attention.inputs import (
@@ -140,8 +139,8 @@ def packed_attention_device(q, k, v, cu_seqlens_q, cu_seqlens_k, *, nheads, nhea
     nheads_k and total_k.  Returns (out shaped like q, lse (nheads, total_q) or
     None)."""
     device = q.device
-    out = torch.empty_like(q)
-    lse = (torch.empty((nheads, total_q), dtype=torch.float32, device=device) if return_lse else None)
+    out = _arrays.empty_like(q)
+    lse = _arrays.empty((nheads, total_q), "float32", device) if return_lse else None
     if total_q == 0:
         return out, lse
     if total_k == 0:
@@ -164,7 +163,7 @@ def packed_attention_device(q, k, v, cu_seqlens_q, cu_seqlens_k, *, nheads, nhea
         args.rotary_cos, args.rotary_sin = cos.data_ptr(), sin.data_ptr()
         args.rotary_len = cos.shape[0]
         args.rotary_interleaved = int(bool(interleaved))
-        args.rotary_bf16 = int(cos.dtype == torch.bfloat16)
+        args.rotary_bf16 = int(_arrays.dtype_name(cos.dtype) == "bfloat16")
         args.rotary_k = int(bool(rotate_k))
     lib = _native.library()
     stream = _native.current_stream(device)
@@ -253,11 +252,10 @@ def flash_attn_func(
     sinks = sinks_operand(learnable_sink, nheads, device)
     scale = 1.0 / math.sqrt(head_dim_qk) if softmax_scale is None else float(softmax_scale)
     q_dev, k_dev, v_dev = (_arrays.to_device(x, device).contiguous() for x in (q, k, v))
-    int32 = dict(dtype=torch.int32, device=device)
     if token_major:
         # packed tokens (batch * seqlen, nheads, d): one sequence per batch row
-        cu_q = torch.arange(batch + 1, **int32) * seqlen_q
-        cu_k = torch.arange(batch + 1, **int32) * seqlen_k
+        cu_q = _arrays.arange_scaled(batch + 1, seqlen_q, device)
+        cu_k = _arrays.arange_scaled(batch + 1, seqlen_k, device)
         out, lse = packed_attention_device(
             q_dev.view(batch * seqlen_q, nheads, head_dim_qk), k_dev.view(batch * seqlen_k, nheads_k, head_dim_qk),
             v_dev.view(batch * seqlen_k, nheads_k, head_dim_qk), cu_q, cu_k, nheads=nheads, nheads_k=nheads_k,
@@ -266,11 +264,11 @@ def flash_attn_func(
             return_lse=return_softmax_lse, sinks=sinks, rotary=rotary, window_right=right)
         out = out.view(q_dev.shape)
         if lse is not None:
-            lse = lse.view(nheads, batch, seqlen_q).transpose(0, 1).contiguous()
+            lse = _arrays.heads_first_to_batch_first(lse, nheads, batch, seqlen_q)
     else:
         # the batch folds into the head axis: batch * nheads heads over one sequence
-        cu_q = torch.tensor([0, seqlen_q], **int32)
-        cu_k = torch.tensor([0, seqlen_k], **int32)
+        cu_q = _arrays.int32_array([0, seqlen_q], device)
+        cu_k = _arrays.int32_array([0, seqlen_k], device)
         out, lse = packed_attention_device(
             q_dev.view(batch * nheads, seqlen_q, head_dim_qk), k_dev.view(batch * nheads_k, seqlen_k, head_dim_qk),
             v_dev.view(batch * nheads_k, seqlen_k, head_dim_qk), cu_q, cu_k, nheads=batch * nheads,

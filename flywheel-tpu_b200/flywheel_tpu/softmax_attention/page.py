@@ -7,8 +7,6 @@ from __future__ import annotations
 
 import ctypes
 
-import torch
-
 from flywheel_tpu.softmax_attention import _arrays, _native
 from flywheel_tpu.softmax_attention.kv_layout import (
     check_merged_kv_dtype,
@@ -61,6 +59,6 @@ def write_kv_cache_pages(k, v, kv_cache, slices, num_slices, *, interpret=False)
         kv_dtype=_native.DTYPE_CODE[names[2]])
     _native.check(_native.library().fw_write_kv_pages(
         ctypes.byref(args), _native.current_stream(device)))
-    if isinstance(kv_cache, torch.Tensor) and kv_cache.is_cuda:
+    if _arrays.is_device_resident(kv_cache):
         return kv_cache
     return _arrays.like(cache, kv_cache)

@@ -11,8 +11,6 @@ from __future__ import annotations
 import ctypes
 import math
 
-import torch
-
 from flywheel_tpu.softmax_attention import _arrays, _native
 from flywheel_tpu.softmax_attention.config import (
     PAGE_SIZE_MULTIPLE,
@@ -48,9 +46,8 @@ def paged_prefill_device(q, kv_cache, cu_seqlens_q, seqused_k, block_table,
         total_q, nheads, head_dim = q.shape
     else:
         nheads, total_q, head_dim = q.shape
-    out = torch.empty_like(q)
-    lse = (torch.empty((nheads, total_q), dtype=torch.float32, device=device)
-           if return_lse else None)
+    out = _arrays.empty_like(q)
+    lse = _arrays.empty((nheads, total_q), "float32", device) if return_lse else None
     if total_q == 0:
         return out, lse
     args = _native.FwPrefillArgs(
@@ -75,7 +72,7 @@ def paged_prefill_device(q, kv_cache, cu_seqlens_q, seqused_k, block_table,
         args.rotary_cos, args.rotary_sin = cos.data_ptr(), sin.data_ptr()
         args.rotary_len = cos.shape[0]
         args.rotary_interleaved = int(bool(interleaved))
-        args.rotary_bf16 = int(cos.dtype == torch.bfloat16)
+        args.rotary_bf16 = int(_arrays.dtype_name(cos.dtype) == "bfloat16")
     lib = _native.library()
     stream = _native.current_stream(device)
     nbytes = lib.fw_prefill_workspace_bytes(ctypes.byref(args))

@@ -130,8 +130,11 @@ def test_a_reported_status_does_not_switch_later_prefills_off():
     pool = oracle.merge_kv_heads(draw((sum(pages_b), page, hk, d)), draw((sum(pages_b), page, hk, d)))
     q = draw((int(cu[-1]), hq, d))
     # leave a BAD_PAGE report in the workspace the public entry points share on this stream
+    from flywheel_tpu.softmax_attention import _cuda
     scratch = _native.workspace(dev, 1 << 20)
-    scratch[:4] = torch.tensor([2, 0, 0, 0], dtype=torch.uint8, device=dev)
+    word = torch.tensor([2], dtype=torch.int32, device=dev)
+    _cuda.memcpy(scratch.data_ptr(), word.data_ptr(), 4, _cuda.MEMCPY_D2D)
+    torch.cuda.synchronize()
     old = prefill.FORCED_ROUTE
     prefill.FORCED_ROUTE = "tcgen05"
     try:
