@@ -702,6 +702,7 @@ def bench_config(ns, name, ranks):
     from flywheel_tpu.softmax_attention import _native
     device = ranks.device
     rng = np.random.default_rng(0)
+    e2e = None
     if name == "c1":
         batch, hq, hk, cap = 8, 32, 8, 2048
         lens = rng.integers(128, 2048, batch).astype(np.int32)
@@ -720,6 +721,22 @@ def bench_config(ns, name, ranks):
         kv_bytes = workloads.decode_kv_bytes(lens, 1, hk, D, 2)
         keep = (kc, vc, q, k, v, lens_t, out)
         kernel = "fw::decode_kernel<bf16> (+ combine_kernel)"
+        # the same step end to end: q, new k / v and the lengths in pinned host memory, the caches
+        # resident, the output read back; at this size the host side is most of the step
+        from flywheel_tpu import flash_attn_with_kvcache
+        pinned = [t.cpu().pin_memory() for t in (q, k, v, lens_t)]
+
+        def e2e_pass():
+            for _ in range(20):
+                flash_attn_with_kvcache(pinned[0], kc, vc, pinned[1], pinned[2], cache_seqlens=pinned[3],
+                                        causal=True)
+
+        e2e_pass()
+        e2e_ms = timed_rounds(e2e_pass, 20, ranks, rounds=3, min_round_s=0.05)["own_ms_per_step"]
+        e2e = {"value": kv_bytes / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": e2e_ms,
+               "h2d_bytes_per_step": sum(t.numel() * t.element_size() for t in pinned),
+               "d2h_bytes_per_step": q.numel() * 2,
+               "note": "through flywheel_tpu.flash_attn_with_kvcache; L2 not flushed between these steps"}
     elif name in SECONDARY_SHAPES:
         spec = SECONDARY_SHAPES[name]
         batch, hq, hk, d, page, q_len = (spec[key] for key in ("batch", "hq", "hk", "d", "page", "q_len"))
@@ -800,10 +817,13 @@ def bench_config(ns, name, ranks):
         raise RuntimeError("decode kernel reported a device status")
     del keep
     torch.cuda.empty_cache()
-    return {"metric": "decode_kv_read_bandwidth",
-            "config": {"workload": CONFIG_TEXT.get(name, name), "name": name, "l2": l2},
-            "value": kv_bytes / (ms * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": ms, "rounds": rounds,
-            "gpu_launches_per_step": 2, "roofline": hbm_roofline(kv_bytes, ms, kernel)}
+    result = {"metric": "decode_kv_read_bandwidth",
+              "config": {"workload": CONFIG_TEXT.get(name, name), "name": name, "l2": l2},
+              "value": kv_bytes / (ms * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": ms, "rounds": rounds,
+              "gpu_launches_per_step": 2, "roofline": hbm_roofline(kv_bytes, ms, kernel)}
+    if e2e is not None:
+        result["e2e"] = e2e
+    return result
 
 
 # Dense causal prefill shapes for flash_attn_func (the reference's dense-prefill
