@@ -684,6 +684,8 @@ SECONDARY_SHAPES = {
     "serve-d256-mha-b128": dict(batch=128, hq=32, hk=32, d=256, page=128, q_len=1, lens=(15360, 15360)),
     "gate-decode": dict(batch=64, hq=32, hk=8, d=128, page=128, q_len=1, lens=(6144, 10239)),
     "gate-verify": dict(batch=32, hq=32, hk=8, d=128, page=128, q_len=4, lens=(6144, 10239)),
+    # the verify window of configuration 3 (32 query rows per KV head) on a bf16 pool, no softcap or window
+    "verify-bf16-gqa8": dict(batch=128, hq=64, hk=8, d=128, page=64, q_len=4, lens=(1024, 32768)),
 }
 CONFIG_TEXT = {
     "c1": "contiguous bf16 GQA decode, batch 8, 32 q heads, 8 kv heads, head_dim 128, caches (8, 2048, 8, 128), "

@@ -435,37 +435,60 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
       for (int u = 0; u < NU; ++u)
 #pragma unroll
         for (int nt = 0; nt < 2; ++nt) s[u][nt][0] = s[u][nt][1] = s[u][nt][2] = s[u][nt][3] = 0.f;
-#pragma unroll
-      for (int u = 0; u < NU; ++u) {
+      // The k-steps run outermost and the sub-tiles innermost, so consecutive
+      // MMAs go to different accumulators (2 * NU chains in flight instead of two).
       if constexpr (!kFp8) {
         const int mi = lane >> 3;
-        const int key = u * 16 + ((mi >> 1) << 3) + (lane & 7);
+        // A one-sub-tile stage would leave two chains of KS dependent MMAs: the
+        // odd k-steps go to a second pair of accumulators, summed at the end.
+        float s_odd[2][4];
+        if constexpr (NU == 1) {
+#pragma unroll
+          for (int nt = 0; nt < 2; ++nt) s_odd[nt][0] = s_odd[nt][1] = s_odd[nt][2] = s_odd[nt][3] = 0.f;
+        }
 #pragma unroll
         for (int ks = 0; ks < KS; ++ks) {
-          const int chunk = ks * 2 + (mi & 1);
-          const uint32_t addr = st + (kseg + (chunk >> 3)) * seg_bytes + key * 128 +
-                                (((chunk & 7) ^ (key & 7)) << 4);
-          uint32_t r0, r1, r2, r3;
-          ldmatrix_x4(addr, r0, r1, r2, r3);
-          mma_bf16(s[u][0], qa[ks], r0, r1);
-          mma_bf16(s[u][1], qa[ks], r2, r3);
+#pragma unroll
+          for (int u = 0; u < NU; ++u) {
+            const int key = u * 16 + ((mi >> 1) << 3) + (lane & 7);
+            const int chunk = ks * 2 + (mi & 1);
+            const uint32_t addr = st + (kseg + (chunk >> 3)) * seg_bytes + key * 128 +
+                                  (((chunk & 7) ^ (key & 7)) << 4);
+            uint32_t r0, r1, r2, r3;
+            ldmatrix_x4(addr, r0, r1, r2, r3);
+            if (NU == 1 && (ks & 1)) {
+              mma_bf16(s_odd[0], qa[ks], r0, r1);
+              mma_bf16(s_odd[1], qa[ks], r2, r3);
+            } else {
+              mma_bf16(s[u][0], qa[ks], r0, r1);
+              mma_bf16(s[u][1], qa[ks], r2, r3);
+            }
+          }
+        }
+        if constexpr (NU == 1) {
+#pragma unroll
+          for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) s[0][nt][i] += s_odd[nt][i];
         }
       } else {
         const int mi = lane >> 3;
-        const int key = u * 16 + ((mi & 1) << 3) + (lane & 7);
 #pragma unroll
         for (int kp = 0; kp < KS / 2; ++kp) {
-          const int chunk = kp * 2 + (mi >> 1);
-          const uint32_t addr = st + (kseg + (chunk >> 3)) * seg_bytes + key * 128 +
-                                (((chunk & 7) ^ (key & 7)) << 4);
-          uint32_t r0, r1, r2, r3;  // (keys 0-7, c), (keys 8-15, c), (keys 0-7, c+1), (keys 8-15, c+1)
-          ldmatrix_x4(addr, r0, r1, r2, r3);
-          mma_f16(s[u][0], qa[2 * kp], fp8_half_to_f16x2<KVT, false>(r0), fp8_half_to_f16x2<KVT, true>(r0));
-          mma_f16(s[u][1], qa[2 * kp], fp8_half_to_f16x2<KVT, false>(r1), fp8_half_to_f16x2<KVT, true>(r1));
-          mma_f16(s[u][0], qa[2 * kp + 1], fp8_half_to_f16x2<KVT, false>(r2), fp8_half_to_f16x2<KVT, true>(r2));
-          mma_f16(s[u][1], qa[2 * kp + 1], fp8_half_to_f16x2<KVT, false>(r3), fp8_half_to_f16x2<KVT, true>(r3));
+#pragma unroll
+          for (int u = 0; u < NU; ++u) {
+            const int key = u * 16 + ((mi & 1) << 3) + (lane & 7);
+            const int chunk = kp * 2 + (mi >> 1);
+            const uint32_t addr = st + (kseg + (chunk >> 3)) * seg_bytes + key * 128 +
+                                  (((chunk & 7) ^ (key & 7)) << 4);
+            uint32_t r0, r1, r2, r3;  // (keys 0-7, c), (keys 8-15, c), (keys 0-7, c+1), (keys 8-15, c+1)
+            ldmatrix_x4(addr, r0, r1, r2, r3);
+            mma_f16(s[u][0], qa[2 * kp], fp8_half_to_f16x2<KVT, false>(r0), fp8_half_to_f16x2<KVT, true>(r0));
+            mma_f16(s[u][1], qa[2 * kp], fp8_half_to_f16x2<KVT, false>(r1), fp8_half_to_f16x2<KVT, true>(r1));
+            mma_f16(s[u][0], qa[2 * kp + 1], fp8_half_to_f16x2<KVT, false>(r2), fp8_half_to_f16x2<KVT, true>(r2));
+            mma_f16(s[u][1], qa[2 * kp + 1], fp8_half_to_f16x2<KVT, false>(r3), fp8_half_to_f16x2<KVT, true>(r3));
+          }
         }
-      }
       }
 
       // ---- scale (+ softcap), mask.  With a softcap the logit is
