@@ -1131,17 +1131,25 @@ def headline(ns, ranks):
     del work, call, out
     torch.cuda.empty_cache()
 
-    prefill = None if ns.skip_prefill else bench_prefill(ns, ranks)
+    def guarded(measure):
+        """A secondary measurement that fails must not take the headline line with it."""
+        try:
+            return measure()
+        except Exception as exc:  # pylint: disable=broad-except
+            torch.cuda.empty_cache()
+            return {"error": f"{type(exc).__name__}: {exc}"[:300]}
+
+    prefill = None if ns.skip_prefill else guarded(lambda: bench_prefill(ns, ranks))
     extra = {}
     if not ns.skip_extra:
         if world == 1:
-            extra["c1"] = bench_config(ns, "c1", ranks)
-            extra["c3"] = bench_config(ns, "c3", ranks)
-            extra["mixed"] = bench_mixed(ns, ranks)
+            extra["c1"] = guarded(lambda: bench_config(ns, "c1", ranks))
+            extra["c3"] = guarded(lambda: bench_config(ns, "c3", ranks))
+            extra["mixed"] = guarded(lambda: bench_mixed(ns, ranks))
         else:
             # every rank has just timed the full batch by itself: that is the one-GPU time
-            extra["strong"] = strong_scaling_key(ns, ranks, full_batch_ms)
-        extra["long_context"] = long_context_key(ns, ranks)
+            extra["strong"] = guarded(lambda: strong_scaling_key(ns, ranks, full_batch_ms))
+        extra["long_context"] = guarded(lambda: long_context_key(ns, ranks))
     if rank == 0:
         if prefill is not None:
             line["prefill"] = prefill
