@@ -105,7 +105,7 @@ int encode_tensor_map_bf16(CUtensorMap* map, int rank, const void* base, const u
 
 extern "C" const char* fw_last_error(void) { return fw::g_error; }
 
-extern "C" int fw_version(void) { return 7; }
+extern "C" int fw_version(void) { return 8; }
 
 namespace fw {
 // A CTA that waits on a barrier nobody will ever arrive on: the wait must give

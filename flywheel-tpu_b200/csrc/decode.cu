@@ -25,6 +25,7 @@
 #include <mutex>
 
 #include "common.cuh"
+#include "exchange.cuh"
 
 namespace fw {
 
@@ -679,6 +680,10 @@ struct CombineParams {
   float* partial_lse;
   const float* v_descale;
   const float* sinks;
+  // xchg.world > 0: the sink-free normalised state of every row goes straight
+  // into every rank's exchange buffer (peer stores over NVLink) as {value,
+  // epoch} pairs instead of partial_out / partial_lse.
+  PeerSlots xchg;
 };
 
 constexpr int kCombineWarps = 4;
@@ -742,10 +747,29 @@ combine_kernel(const CombineParams cp) {
     live = __ballot_sync(0xffffffffu, has_tiles);
   }
   const float vd = cp.v_descale ? *cp.v_descale : 1.0f;
+  const bool scatter = cp.xchg.world > 0;
+  const uint32_t epoch = scatter ? step_epoch(cp.xchg.peers[cp.xchg.rank]) : 0u;
 
   for (int row = blockIdx.y * kRowsPerBlock + warp; row < rq; row += gridDim.y * kRowsPerBlock) {
     const int t = row / p.nheads, hq = row - t * p.nheads;
-    if (t >= sp.q_valid) break;  // rows are token-major: the rest are not real query rows either
+    if (t >= sp.q_valid) {
+      if (!scatter) break;  // rows are token-major: the rest are not real query rows either
+      // the peers wait for every row of the step: a row that is no query row travels as the empty state
+      if (sub == 0) {
+        const long long orow = static_cast<long long>(b) * rq + row;
+        for (int r = 0; r < cp.xchg.world; ++r) {
+          uint2* slot = slot_of(cp.xchg.peers[r], epoch, cp.xchg.world, cp.xchg.rank, cp.xchg.slot_pairs);
+#pragma unroll
+          for (int nb = 0; nb < NB; ++nb) {
+            uint2* dst = slot + orow * D + nb * 128 + lane * 4;
+            store_pairs2(dst, 0.f, 0.f, epoch);
+            store_pairs2(dst + 2, 0.f, 0.f, epoch);
+          }
+          if (lane == 0) store_pair(slot + static_cast<long long>(p.total_q) * p.nheads * D + orow, -INFINITY, epoch);
+        }
+      }
+      continue;
+    }
 
     // One pass: every segment is folded into a running (max, sum, acc) state,
     // so a row costs one round of loads, not a max pass and then a sum pass.
@@ -833,6 +857,25 @@ combine_kernel(const CombineParams cp) {
       m_max = top;
     }
 
+    if (scatter) {
+      // Sink-free normalised state, delivered to every rank (this one included).
+      if constexpr (!kNarrow) {
+        const long long orow = static_cast<long long>(b) * rq + row;
+        const float inv = den > 0.f ? vd / den : 0.f;
+        const float row_lse = den > 0.f ? (m_max + log2f(den)) * kLn2 : -INFINITY;
+        for (int r = 0; r < cp.xchg.world; ++r) {
+          uint2* slot = slot_of(cp.xchg.peers[r], epoch, cp.xchg.world, cp.xchg.rank, cp.xchg.slot_pairs);
+#pragma unroll
+          for (int nb = 0; nb < NB; ++nb) {
+            uint2* dst = slot + orow * D + nb * 128 + lane * 4;
+            store_pairs2(dst, acc[nb].x * inv, acc[nb].y * inv, epoch);
+            store_pairs2(dst + 2, acc[nb].z * inv, acc[nb].w * inv, epoch);
+          }
+          if (lane == 0) store_pair(slot + static_cast<long long>(p.total_q) * p.nheads * D + orow, row_lse, epoch);
+        }
+      }
+      continue;
+    }
     if (cp.partial_out != nullptr) {
       // Sink-free normalised state for a cross-GPU merge.
       const long long orow = static_cast<long long>(b) * rq + row;
@@ -1077,7 +1120,7 @@ namespace fw {
 // Enqueues decode_kernel + combine_kernel for a finished plan.
 static int launch_decode(DecodePlan& plan, void* workspace, cudaStream_t stream, int kv_dtype, void* out,
                          float* lse, float* partial_out, float* partial_lse, const float* v_descale,
-                         const float* sinks, int* status = nullptr) {
+                         const float* sinks, int* status = nullptr, const PeerSlots* xchg = nullptr) {
   int rc;
   DecodeParams& p = plan.p;
   uint8_t* ws = static_cast<uint8_t*>(workspace);
@@ -1145,6 +1188,7 @@ static int launch_decode(DecodePlan& plan, void* workspace, cudaStream_t stream,
   cp.partial_lse = partial_lse;
   cp.v_descale = v_descale;
   cp.sinks = sinks;
+  cp.xchg = xchg != nullptr ? *xchg : PeerSlots{};
   // Few rows with many segments each (a long request cut over every SM): 16
   // warps share a row, so its ~150 segments are read in a few rounds.
   const bool wide = static_cast<long long>(p.batch) * plan.rows_q <= 2048;
@@ -1231,6 +1275,93 @@ int fw::decode_with_status(const FwDecodeArgs* a, int* status, cudaStream_t stre
   }
   return launch_decode(plan, a->workspace, stream, a->kv_dtype, a->out, a->lse, a->partial_out, a->partial_lse,
                        a->v_descale, a->sinks, status);
+}
+
+// One request whose pages are split over the GPUs of a node, the whole step:
+// decode kernel over this rank's pages, combine kernel that delivers the rank's
+// sink-free state to every rank's exchange buffer, merge kernel that waits for
+// all ranks' states and writes the final rows.  Three launches, no flag, fence
+// or collective call.
+extern "C" int fw_sharded_decode_step(const FwShardedDecodeArgs* s, void* stream_ptr) {
+  if (s == nullptr || s->peer_buffers == nullptr) {
+    set_error("args and peer_buffers must not be NULL.");
+    return FW_ERR_BAD_SHAPE;
+  }
+  const FwDecodeArgs* a = &s->decode;
+  if (s->world <= 0 || s->world > kMaxRanks || s->rank < 0 || s->rank >= s->world) {
+    set_error("world must be in [1, %d] and rank inside it; got world %d rank %d.", kMaxRanks, s->world, s->rank);
+    return FW_ERR_BAD_SHAPE;
+  }
+  if (a->head_dim != 128 && a->head_dim != 256) {
+    set_error("the state exchange serves head_dim 128 and 256; got %d.", a->head_dim);
+    return FW_ERR_UNSUPPORTED;
+  }
+  if (a->batch != 1 && a->seqlen_q != 1) {
+    set_error("the sharded step takes one request (any seqlen_q) or one-token requests; got batch %d, seqlen_q %d.",
+              a->batch, a->seqlen_q);
+    return FW_ERR_UNSUPPORTED;
+  }
+  if (a->partial_out != nullptr || a->partial_lse != nullptr) {
+    set_error("partial_out / partial_lse must be NULL: the state goes to the exchange buffers.");
+    return FW_ERR_BAD_SHAPE;
+  }
+  if (s->global_len != nullptr && (s->local_len == nullptr || s->append_enable == nullptr || s->advance < 0)) {
+    set_error("global_len needs local_len and append_enable, and advance >= 0.");
+    return FW_ERR_BAD_SHAPE;
+  }
+  DecodePlan plan;
+  int rc = plan_decode(a, &plan);
+  if (rc != FW_OK) return rc;
+  if (a->q == nullptr || a->kv_cache == nullptr || a->cache_seqlens == nullptr ||
+      (a->out == nullptr && !s->deliver_only)) {
+    set_error("q, kv_cache, cache_seqlens and out must be device pointers, not NULL.");
+    return FW_ERR_BAD_SHAPE;
+  }
+  if (a->workspace == nullptr || a->workspace_bytes < plan.bytes ||
+      (reinterpret_cast<uintptr_t>(a->workspace) & 255)) {
+    set_error("workspace must be 256-byte aligned and hold %llu bytes; got %llu.",
+              static_cast<unsigned long long>(plan.bytes), static_cast<unsigned long long>(a->workspace_bytes));
+    return FW_ERR_WORKSPACE;
+  }
+  if ((reinterpret_cast<uintptr_t>(a->kv_cache) & 15) || (reinterpret_cast<uintptr_t>(a->q) & 15) ||
+      (reinterpret_cast<uintptr_t>(a->k_new) & 15) || (reinterpret_cast<uintptr_t>(a->v_new) & 15) ||
+      (reinterpret_cast<uintptr_t>(a->out) & 15)) {
+    set_error("q, out, the cache and new k/v must be 16-byte aligned.");
+    return FW_ERR_BAD_SHAPE;
+  }
+  const int rows = a->batch * a->seqlen_q * a->nheads;
+  MergeParams m{};
+  for (int r = 0; r < s->world; ++r) {
+    if (s->peer_buffers[r] == nullptr) {
+      set_error("peer_buffers[%d] is NULL.", r);
+      return FW_ERR_BAD_SHAPE;
+    }
+    m.slots.peers[r] = static_cast<uint8_t*>(s->peer_buffers[r]);
+  }
+  m.slots.world = s->world;
+  m.slots.rank = s->rank;
+  m.slots.slot_pairs = slot_pairs_of(rows, a->head_dim);
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
+  // the sink joins once, at the merge; v_descale scales this rank's state
+  rc = launch_decode(plan, a->workspace, stream, a->kv_dtype, nullptr, nullptr, nullptr, nullptr, a->v_descale,
+                     nullptr, nullptr, &m.slots);
+  if (rc != FW_OK || s->deliver_only) return rc;
+  m.sinks = a->sinks;
+  m.out = static_cast<__nv_bfloat16*>(a->out);
+  m.lse = a->lse;
+  m.status = static_cast<int*>(a->workspace);
+  m.rows = rows;
+  m.nheads = a->nheads;
+  m.head_dim = a->head_dim;
+  // lse is (batch, nheads, seqlen_q); a merge row is (token, head) with token = b * seqlen_q + t
+  m.lse_head_stride = a->batch == 1 ? a->seqlen_q : 1;
+  m.lse_token_stride = a->batch == 1 ? 1 : a->nheads;
+  m.global_len = s->global_len;
+  m.local_len = s->local_len;
+  m.append_enable = s->append_enable;
+  m.page_size = a->page_size;
+  m.advance = s->advance;
+  return launch_gather_merge(m, stream);
 }
 
 // ---------------------------------------------------------------- split-KV prefill

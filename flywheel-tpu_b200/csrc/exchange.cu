@@ -1,153 +1,125 @@
 // Cross-GPU exchange of per-rank attention states for one long request whose KV
-// pages are split over the GPUs of a node, fused with the merge: every rank
-// stores its sink-free (o, lse) state straight into each peer's memory over
-// NVLink (plain peer stores, no multicast), raises a per-rank epoch flag there,
-// and the merge kernel waits - with an iteration limit - for the flags of all
-// ranks before it reads the gathered states from its own memory.  It replaces
-// an NCCL all-gather of 33 KB plus a merge launch.
+// pages are split over the GPUs of a node, fused with the merge.  The sending
+// side stores its sink-free (o, lse) state straight into each peer's memory
+// over NVLink (plain peer stores, no multicast) as {value, epoch} pairs
+// (exchange.cuh); the merge kernel polls - with an iteration limit - the pairs
+// it needs in its own memory until they carry the step's epoch, so a step has
+// no flag, no system-scope fence and no collective-library call.  The sender is
+// normally the decode launch's own combine kernel (fw_sharded_decode_step,
+// decode.cu); scatter_state_kernel below serves callers that already hold the
+// state in a buffer.
 //
 // The merge itself is _merge_states of the reference project
 // (patches/tpu-inference.patch:7174-7186); the reference has no multi-device
 // code in its library, the exchange is this build's.
-//
-// Layout of a rank's exchange buffer (same on every rank, cudaMalloc'ed here so
-// its IPC handle can be opened by the peers):
-//   [0, 256)            this rank's own bookkeeping: step counter, merge blocks done,
-//                       scatter blocks done per peer
-//   [256, 256 + 4 W)    flags[r]: last epoch rank r has delivered
-//   [4096, ...)         2 x W slots of rows * (head_dim + 1) floats: [o | lse],
-//                       indexed [epoch parity][source rank]
-// Two parities, because a rank may run one step ahead of a peer that is still
-// merging the previous one; it cannot run two ahead, since its own merge of
-// step e + 1 needs that peer's state of step e + 1.
 #include <cstring>
 
-#include "common.cuh"
+#include "exchange.cuh"
 
 namespace fw {
 
-constexpr int kMaxRanks = 16;
-constexpr uint64_t kExchangeHeader = 4096;
-constexpr uint32_t kExchangePollLimit = 1u << 21;  // polls of a peer's flag before giving up (about a second)
-
-struct ExchangeParams {
-  uint8_t* peers[kMaxRanks];  // every rank's exchange buffer as mapped in this process (own included)
-  const float* state_out;     // (rows, head_dim) this rank's normalised partial output
-  const float* state_lse;     // (rows,)
-  const float* sinks;
-  __nv_bfloat16* out;
-  float* lse;
-  int* status;
-  int world, rank, rows, nheads, head_dim;
-  int lse_head_stride, lse_token_stride;
-  uint64_t slot_floats;  // rows * (head_dim + 1), rounded up to a multiple of 4
+struct ScatterParams {
+  PeerSlots slots;
+  const float* state_out;  // (rows, head_dim) this rank's normalised partial output
+  const float* state_lse;  // (rows,)
+  int rows, head_dim;
 };
-
-__device__ __forceinline__ void store_release_sys(uint32_t* addr, uint32_t value) {
-  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(addr), "r"(value) : "memory");
-}
-__device__ __forceinline__ uint32_t load_acquire_sys(const uint32_t* addr) {
-  uint32_t value;
-  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(value) : "l"(addr) : "memory");
-  return value;
-}
-
-__device__ __forceinline__ float* slot_of(uint8_t* buffer, uint32_t epoch, int world, int source,
-                                          uint64_t slot_floats) {
-  return reinterpret_cast<float*>(buffer + kExchangeHeader) +
-         (static_cast<uint64_t>(epoch & 1) * world + source) * slot_floats;
-}
 
 constexpr int kScatterBlocks = 8;  // blocks that share the copy to one peer
 
-// Blocks (p, 0 .. kScatterBlocks) deliver this rank's state to rank p; the last
-// of them to finish raises this rank's flag there.
-__global__ void __launch_bounds__(128) scatter_state_kernel(const ExchangeParams p) {
+// Blocks (p, 0 .. kScatterBlocks) deliver this rank's state to rank p.
+__global__ void __launch_bounds__(128) scatter_state_kernel(const ScatterParams p) {
   const int peer = blockIdx.x;
-  uint32_t* header = reinterpret_cast<uint32_t*>(p.peers[p.rank]);
   // Launched as a programmatic dependent of the kernel that writes the state
   // (and, through it, of the previous step's merge, which advances the epoch).
   asm volatile("griddepcontrol.wait;" ::: "memory");
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-  const uint32_t epoch = header[0] + 1;
-  float* dst = slot_of(p.peers[peer], epoch, p.world, p.rank, p.slot_floats);
+  const uint32_t epoch = step_epoch(p.slots.peers[p.slots.rank]);
+  uint2* dst = slot_of(p.slots.peers[peer], epoch, p.slots.world, p.slots.rank, p.slots.slot_pairs);
   const int n_out = p.rows * p.head_dim;
   const int first = (blockIdx.y * blockDim.x + threadIdx.x) * 4, stride = gridDim.y * blockDim.x * 4;
-  for (int i = first; i < n_out; i += stride)
-    *reinterpret_cast<float4*>(dst + i) = *reinterpret_cast<const float4*>(p.state_out + i);
-  if (blockIdx.y == 0)
-    for (int i = threadIdx.x; i < p.rows; i += blockDim.x) dst[n_out + i] = p.state_lse[i];
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    __threadfence_system();  // this block's stores are out before it is counted
-    uint32_t* arrived = header + 2 + peer;
-    if (atomicAdd(arrived, 1u) == gridDim.y - 1) {
-      *arrived = 0;
-      __threadfence_system();
-      store_release_sys(reinterpret_cast<uint32_t*>(p.peers[peer] + 256) + p.rank, epoch);
-    }
+  for (int i = first; i < n_out; i += stride) {
+    const float4 v = *reinterpret_cast<const float4*>(p.state_out + i);
+    store_pairs2(dst + i, v.x, v.y, epoch);
+    store_pairs2(dst + i + 2, v.z, v.w, epoch);
   }
+  if (blockIdx.y == 0)
+    for (int i = threadIdx.x; i < p.rows; i += blockDim.x) store_pair(dst + n_out + i, p.state_lse[i], epoch);
 }
 
-// One warp per row, after every rank's flag shows this step's epoch.  The last
-// block to finish advances the step counter.
-__global__ void __launch_bounds__(128) gather_merge_kernel(const ExchangeParams p) {
-  __shared__ int failed;
-  uint8_t* mine = p.peers[p.rank];
+// One warp per row: waits until every rank's pairs of that row carry this
+// step's epoch, merges them, and the last block to finish advances the epoch
+// (and the round-robin bookkeeping, when given).
+__global__ void __launch_bounds__(128) gather_merge_kernel(const MergeParams p) {
+  uint8_t* mine = p.slots.peers[p.slots.rank];
   uint32_t* header = reinterpret_cast<uint32_t*>(mine);
-  asm volatile("griddepcontrol.wait;" ::: "memory");  // the scatter kernel of this rank is done
-  const uint32_t epoch = header[0] + 1;
-  if (threadIdx.x == 0) failed = 0;
-  __syncthreads();
-  if (threadIdx.x < p.world) {
-    const uint32_t* flag = reinterpret_cast<const uint32_t*>(mine + 256) + threadIdx.x;
-    bool seen = false;
-    for (uint32_t poll = 0; poll < kExchangePollLimit; ++poll) {
-      // epochs only grow; the signed difference survives a wrap of the counter
-      if (static_cast<int32_t>(load_acquire_sys(flag) - epoch) >= 0) {
-        seen = true;
-        break;
-      }
-      if (poll > 64) __nanosleep(poll > 4096 ? 512 : 64);
-    }
-    if (!seen) {
-      failed = 1;
-      report_status(p.status, FW_STATUS_WAIT_TIMEOUT);
-    }
-  }
-  __syncthreads();
+  asm volatile("griddepcontrol.wait;" ::: "memory");  // this rank's sending kernel is done
+  const uint32_t epoch = step_epoch(mine);
+  const int world = p.slots.world;
   const int row = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
-  if (!failed && row < p.rows) {
+  if (row < p.rows) {
     const int head = row % p.nheads, tok = row / p.nheads;
     const int n_out = p.rows * p.head_dim;
-    const float sink = p.sinks ? p.sinks[head] : -INFINITY;
-    float top = sink;
-    for (int r = 0; r < p.world; ++r)
-      top = fmaxf(top, slot_of(mine, epoch, p.world, r, p.slot_floats)[n_out + row]);
     const int blocks = p.head_dim / 128;
+    const float sink = p.sinks ? p.sinks[head] : -INFINITY;
+    // Running (max, sum, acc) over the ranks, in rank order, so every rank
+    // computes bit-identical results.
+    float top = -INFINITY, den = 0.f;
     float4 acc[2] = {make_float4(0.f, 0.f, 0.f, 0.f), make_float4(0.f, 0.f, 0.f, 0.f)};
-    float den = 0.f;
-    if (top != -INFINITY) {
-      for (int r = 0; r < p.world; ++r) {
-        const float* slot = slot_of(mine, epoch, p.world, r, p.slot_floats);
-        const float l = slot[n_out + row];
-        if (l == -INFINITY) continue;
-        const float w = __expf(l - top);
-        den += w;
+    bool failed = false;
+    for (int r = 0; r < world && !failed; ++r) {
+      const uint2* slot = slot_of(mine, epoch, world, r, p.slots.slot_pairs);
+      const uint2* o_pairs = slot + static_cast<long long>(row) * p.head_dim + lane * 4;
+      float4 o[2];
+      float l = 0.f;
+      bool seen = false;
+      for (uint32_t poll = 0; poll < kExchangePollLimit; ++poll) {
+        bool ok = load_pair(slot + n_out + row, epoch, l);
 #pragma unroll
         for (int nb = 0; nb < 2; ++nb) {
           if (nb >= blocks) break;
-          const float4 o = *reinterpret_cast<const float4*>(slot + static_cast<long long>(row) * p.head_dim +
-                                                            nb * 128 + lane * 4);
-          acc[nb].x += o.x * w;
-          acc[nb].y += o.y * w;
-          acc[nb].z += o.z * w;
-          acc[nb].w += o.w * w;
+          ok &= load_pairs2(o_pairs + nb * 128, epoch, o[nb].x, o[nb].y);
+          ok &= load_pairs2(o_pairs + nb * 128 + 2, epoch, o[nb].z, o[nb].w);
         }
+        if (__all_sync(0xffffffffu, ok)) {
+          seen = true;
+          break;
+        }
+        if (poll > 64) __nanosleep(poll > 4096 ? 512 : 64);
       }
-      if (sink != -INFINITY) den += __expf(sink - top);
+      if (!seen) {
+        failed = true;
+        if (lane == 0) report_status(p.status, FW_STATUS_WAIT_TIMEOUT);
+        break;
+      }
+      if (l == -INFINITY) continue;
+      const float m_new = fmaxf(top, l);
+      const float keep = __expf(top - m_new), w = __expf(l - m_new);  // e^-inf = 0
+      den = den * keep + w;
+#pragma unroll
+      for (int nb = 0; nb < 2; ++nb) {
+        if (nb >= blocks) break;
+        acc[nb].x = acc[nb].x * keep + o[nb].x * w;
+        acc[nb].y = acc[nb].y * keep + o[nb].y * w;
+        acc[nb].z = acc[nb].z * keep + o[nb].z * w;
+        acc[nb].w = acc[nb].w * keep + o[nb].w * w;
+      }
+      top = m_new;
     }
-    const float inv = den > 0.f ? 1.f / den : 0.f;
+    if (sink != -INFINITY && !failed) {
+      const float m_new = fmaxf(top, sink);
+      const float keep = __expf(top - m_new);
+      den = den * keep + __expf(sink - m_new);
+#pragma unroll
+      for (int nb = 0; nb < 2; ++nb) {
+        acc[nb].x *= keep;
+        acc[nb].y *= keep;
+        acc[nb].z *= keep;
+        acc[nb].w *= keep;
+      }
+      top = m_new;
+    }
+    const float inv = den > 0.f && !failed ? 1.f / den : 0.f;
 #pragma unroll
     for (int nb = 0; nb < 2; ++nb) {
       if (nb >= blocks) break;
@@ -158,7 +130,7 @@ __global__ void __launch_bounds__(128) gather_merge_kernel(const ExchangeParams 
     }
     if (p.lse != nullptr && lane == 0)
       p.lse[static_cast<long long>(head) * p.lse_head_stride + static_cast<long long>(tok) * p.lse_token_stride] =
-          den > 0.f ? top + logf(den) : -INFINITY;
+          den > 0.f && !failed ? top + logf(den) : -INFINITY;
   }
   // the step is over once every block has read the epoch
   __syncthreads();
@@ -166,15 +138,36 @@ __global__ void __launch_bounds__(128) gather_merge_kernel(const ExchangeParams 
     __threadfence();
     if (atomicAdd(&header[1], 1u) == gridDim.x - 1) {
       header[1] = 0;
+      if (p.global_len != nullptr) {
+        // what fw_shard_step does ahead of a step, done for the next one
+        const int len = max(*p.global_len, 0) + p.advance;
+        *p.global_len = len;
+        *p.local_len = round_robin_local_length(len, p.page_size, world, p.slots.rank);
+        *p.append_enable = (len / p.page_size) % world == p.slots.rank ? 1 : 0;
+      }
       __threadfence();
       header[0] = epoch;
     }
   }
 }
 
-// Floats of one (o, lse) slot, padded so every slot starts on a 16-byte boundary.
-static uint64_t slot_floats_of(int rows, int head_dim) {
-  return (static_cast<uint64_t>(rows) * (head_dim + 1) + 3) & ~3ull;
+int launch_gather_merge(const MergeParams& p, cudaStream_t stream) {
+  cudaLaunchAttribute pdl{};
+  pdl.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  pdl.val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchConfig_t cfg{};
+  cfg.stream = stream;
+  cfg.attrs = &pdl;
+  cfg.numAttrs = 1;
+  cfg.gridDim = dim3((p.rows + 3) / 4);
+  cfg.blockDim = dim3(128);
+  cudaError_t err = cudaLaunchKernelEx(&cfg, gather_merge_kernel, p);
+  if (err == cudaSuccess) err = cudaGetLastError();
+  if (err != cudaSuccess) {
+    set_error("merge kernel launch: %s", cudaGetErrorString(err));
+    return FW_ERR_LAUNCH;
+  }
+  return FW_OK;
 }
 
 }  // namespace fw
@@ -186,7 +179,7 @@ extern "C" uint64_t fw_exchange_buffer_bytes(int32_t world, int32_t rows, int32_
     set_error("exchange buffer: world must be in [1, %d], rows positive, head_dim 128 or 256.", kMaxRanks);
     return 0;
   }
-  return kExchangeHeader + 2ull * world * slot_floats_of(rows, head_dim) * sizeof(float);
+  return kExchangeHeader + 2ull * world * slot_pairs_of(rows, head_dim) * sizeof(uint2);
 }
 
 extern "C" int fw_peer_alloc(uint64_t bytes, void** ptr, void* handle64) {
@@ -239,9 +232,12 @@ extern "C" int fw_peer_free(void* ptr) {
 }
 
 extern "C" int fw_state_exchange_merge(const FwExchangeArgs* a, void* stream_ptr) {
-  if (a == nullptr || a->peer_buffers == nullptr || a->state_out == nullptr || a->state_lse == nullptr ||
-      a->out == nullptr) {
-    set_error("peer_buffers, state_out, state_lse and out must not be NULL.");
+  if (a == nullptr || a->peer_buffers == nullptr || a->out == nullptr) {
+    set_error("peer_buffers and out must not be NULL.");
+    return FW_ERR_BAD_SHAPE;
+  }
+  if ((a->state_out == nullptr) != (a->state_lse == nullptr)) {
+    set_error("state_out and state_lse must be passed together (or both NULL: merge only).");
     return FW_ERR_BAD_SHAPE;
   }
   if (a->world <= 0 || a->world > kMaxRanks || a->rank < 0 || a->rank >= a->world) {
@@ -256,64 +252,67 @@ extern "C" int fw_state_exchange_merge(const FwExchangeArgs* a, void* stream_ptr
     set_error("rows and nheads must be positive.");
     return FW_ERR_BAD_SHAPE;
   }
-  ExchangeParams p{};
+  if (a->global_len != nullptr &&
+      (a->local_len == nullptr || a->append_enable == nullptr || a->page_size <= 0 || a->advance < 0)) {
+    set_error("global_len needs local_len, append_enable, a positive page_size and advance >= 0.");
+    return FW_ERR_BAD_SHAPE;
+  }
+  MergeParams m{};
   for (int r = 0; r < a->world; ++r) {
     if (a->peer_buffers[r] == nullptr) {
       set_error("peer_buffers[%d] is NULL.", r);
       return FW_ERR_BAD_SHAPE;
     }
-    p.peers[r] = static_cast<uint8_t*>(a->peer_buffers[r]);
+    m.slots.peers[r] = static_cast<uint8_t*>(a->peer_buffers[r]);
   }
-  p.state_out = a->state_out;
-  p.state_lse = a->state_lse;
-  p.sinks = a->sinks;
-  p.out = static_cast<__nv_bfloat16*>(a->out);
-  p.lse = a->lse;
-  p.status = a->status;
-  p.world = a->world;
-  p.rank = a->rank;
-  p.rows = a->rows;
-  p.nheads = a->nheads;
-  p.head_dim = a->head_dim;
-  p.lse_head_stride = a->lse_head_stride;
-  p.lse_token_stride = a->lse_token_stride;
-  p.slot_floats = slot_floats_of(a->rows, a->head_dim);
+  m.slots.world = a->world;
+  m.slots.rank = a->rank;
+  m.slots.slot_pairs = slot_pairs_of(a->rows, a->head_dim);
+  m.sinks = a->sinks;
+  m.out = static_cast<__nv_bfloat16*>(a->out);
+  m.lse = a->lse;
+  m.status = a->status;
+  m.rows = a->rows;
+  m.nheads = a->nheads;
+  m.head_dim = a->head_dim;
+  m.lse_head_stride = a->lse_head_stride;
+  m.lse_token_stride = a->lse_token_stride;
+  m.global_len = a->global_len;
+  m.local_len = a->local_len;
+  m.append_enable = a->append_enable;
+  m.page_size = a->page_size;
+  m.advance = a->advance;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
-  // Both kernels are programmatic dependents of the kernel before them in the
-  // stream: their launch latency hides under it, and each starts with
-  // griddepcontrol.wait before it reads anything.
-  cudaLaunchAttribute pdl{};
-  pdl.id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  pdl.val.programmaticStreamSerializationAllowed = 1;
-  cudaLaunchConfig_t cfg{};
-  cfg.stream = stream;
-  cfg.attrs = &pdl;
-  cfg.numAttrs = 1;
-  cfg.gridDim = dim3(a->world, kScatterBlocks);
-  cfg.blockDim = dim3(128);
-  cudaError_t err = cudaLaunchKernelEx(&cfg, scatter_state_kernel, p);
-  if (err == cudaSuccess) {
-    cfg.gridDim = dim3((a->rows + 3) / 4);
-    err = cudaLaunchKernelEx(&cfg, gather_merge_kernel, p);
+  if (a->state_out != nullptr) {
+    // A programmatic dependent of the kernel before it in the stream: its launch
+    // latency hides under that kernel, and it starts with griddepcontrol.wait.
+    ScatterParams s{};
+    s.slots = m.slots;
+    s.state_out = a->state_out;
+    s.state_lse = a->state_lse;
+    s.rows = a->rows;
+    s.head_dim = a->head_dim;
+    cudaLaunchAttribute pdl{};
+    pdl.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    pdl.val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchConfig_t cfg{};
+    cfg.stream = stream;
+    cfg.attrs = &pdl;
+    cfg.numAttrs = 1;
+    cfg.gridDim = dim3(a->world, kScatterBlocks);
+    cfg.blockDim = dim3(128);
+    cudaError_t err = cudaLaunchKernelEx(&cfg, scatter_state_kernel, s);
+    if (err == cudaSuccess) err = cudaGetLastError();
+    if (err != cudaSuccess) {
+      set_error("scatter kernel launch: %s", cudaGetErrorString(err));
+      return FW_ERR_LAUNCH;
+    }
   }
-  if (err == cudaSuccess) err = cudaGetLastError();
-  if (err != cudaSuccess) {
-    set_error("exchange kernels launch: %s", cudaGetErrorString(err));
-    return FW_ERR_LAUNCH;
-  }
-  return FW_OK;
+  return launch_gather_merge(m, stream);
 }
 
 // ---------------------------------------------------------------- round-robin page ownership
 namespace fw {
-
-// Tokens of the first `len` positions that fall in pages p with p % world == rank.
-__host__ __device__ inline int round_robin_local_length(int len, int page_size, int world, int rank) {
-  const int full_pages = len / page_size, tail = len - full_pages * page_size;
-  // full pages owned: those p < full_pages with p % world == rank
-  const int owned_full = full_pages > rank ? (full_pages - rank + world - 1) / world : 0;
-  return owned_full * page_size + (full_pages % world == rank ? tail : 0);
-}
 
 __global__ void shard_step_kernel(const FwShardStepArgs a) {
   if (threadIdx.x != 0 || blockIdx.x != 0) return;

@@ -112,6 +112,8 @@ class FwExchangeArgs(ctypes.Structure):
         ("sinks", c_ptr), ("out", c_ptr), ("lse", c_ptr), ("status", c_ptr),
         ("world", i32), ("rank", i32), ("rows", i32), ("nheads", i32),
         ("head_dim", i32), ("lse_head_stride", i32), ("lse_token_stride", i32),
+        ("global_len", c_ptr), ("local_len", c_ptr), ("append_enable", c_ptr),
+        ("page_size", i32), ("advance", i32),
     ]
 
 
@@ -119,6 +121,14 @@ class FwShardStepArgs(ctypes.Structure):
     _fields_ = [
         ("global_len", c_ptr), ("local_len", c_ptr), ("append_enable", c_ptr),
         ("page_size", i32), ("world", i32), ("rank", i32), ("advance", i32),
+    ]
+
+
+class FwShardedDecodeArgs(ctypes.Structure):
+    _fields_ = [
+        ("decode", FwDecodeArgs), ("peer_buffers", c_ptr), ("world", i32), ("rank", i32),
+        ("global_len", c_ptr), ("local_len", c_ptr), ("append_enable", c_ptr),
+        ("advance", i32), ("deliver_only", i32),
     ]
 
 
@@ -142,6 +152,7 @@ EXPORTS = {
     "fw_peer_free": (ctypes.c_int, [c_ptr]),
     "fw_state_exchange_merge": (ctypes.c_int, [ctypes.POINTER(FwExchangeArgs), c_ptr]),
     "fw_shard_step": (ctypes.c_int, [ctypes.POINTER(FwShardStepArgs), c_ptr]),
+    "fw_sharded_decode_step": (ctypes.c_int, [ctypes.POINTER(FwShardedDecodeArgs), c_ptr]),
     "fw_selftest_wait_timeout": (ctypes.c_int, [c_ptr, ctypes.c_uint32, c_ptr]),
     "fw_read_status": (ctypes.c_int, [c_ptr, c_ptr, ctypes.POINTER(i32)]),
     "fw_read_status_static": (ctypes.c_int, [c_ptr, ctypes.POINTER(i32)]),

@@ -6,14 +6,16 @@ the reference project).  Here one process per GPU holds every world-th logical
 page of the request (round-robin) in its own pool; every decode step each rank runs
 the split-KV decode kernel over its own pages in partial-state mode; then the
 sink-free `(o, lse)` states (33 KB per rank for 64 heads) are exchanged and
-merged.  Two exchanges are built: "p2p" (default) - every rank stores its
-state into each peer's exchange buffer over NVLink and raises a flag there,
-and the merge kernel waits for all flags (fw_state_exchange_merge: two
-launches, no collective library on the data path); "nccl" - an NCCL
-all-gather followed by `fw_lse_combine`.  The rank that owns the page holding
-position `cache_len` appends the new token; which rank that is, and how many
-tokens each rank holds, is worked out on the device every step (fw_shard_step),
-so one captured CUDA graph serves a whole generation.
+merged.  Two exchanges are built: "p2p" (default) - the decode launch's combine
+kernel stores the rank's state straight into every rank's exchange buffer over
+NVLink as {value, epoch} pairs, and the merge kernel polls its own buffer until
+all ranks' pairs carry the step's epoch (fw_sharded_decode_step: three launches
+per step, no flag, fence or collective library on the data path); "nccl" - an
+NCCL all-gather followed by `fw_lse_combine`.  The rank that owns the page
+holding position `cache_len` appends the new token; which rank that is, and how
+many tokens each rank holds, is worked out on the device every step (by the
+merge kernel for the next step, or by fw_shard_step), so one captured CUDA graph
+serves a whole generation.
 
 Requests and KV heads need none of this: they shard with no communication
 (`request_shard`, `kv_head_shard`).
@@ -135,6 +137,7 @@ class ShardedDecoder:
             raise ValueError(f"exchange must be 'p2p' or 'nccl'; got {self.exchange!r}.")
         if self.exchange == "p2p" and self.world > 1:
             self._open_exchange_buffers()
+            self._shard_step(advance=0)   # bookkeeping of length 0, as the fused step expects to find it
 
     def _open_exchange_buffers(self):
         """Allocates this rank's exchange buffer, passes its IPC handle to the
@@ -179,6 +182,20 @@ class ShardedDecoder:
         """Sets the number of tokens cached so far (over all ranks).  Every step
         that carries a new token advances it on the device."""
         self.counters[0:1].fill_(int(global_len))
+        if self._fused:
+            # the fused step advances the bookkeeping at its end, for the next step: prime it
+            self._shard_step(advance=0)
+
+    @property
+    def _fused(self) -> bool:
+        return self.world > 1 and self.exchange == "p2p"
+
+    def _shard_step(self, advance: int) -> None:
+        base = self.counters.data_ptr()
+        shard = _native.FwShardStepArgs(
+            global_len=base, local_len=base + 4, append_enable=base + 8,
+            page_size=self.page_size, world=self.world, rank=self.rank, advance=advance)
+        _native.check(self.lib.fw_shard_step(ctypes.byref(shard), _native.current_stream(self.device)))
 
     def step(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, global_len: int | None = None):
         """One decode step: q (1, 1, nheads, d), new k / v (1, 1, nheads_k, d).
@@ -218,19 +235,19 @@ class ShardedDecoder:
         alone = self.world == 1   # one rank holds every page: no partial state, no exchange
         stream = _native.current_stream(self.device)
         base = self.counters.data_ptr()
-        shard = _native.FwShardStepArgs(
-            global_len=base, local_len=base + 4, append_enable=base + 8,
-            page_size=self.page_size, world=self.world, rank=self.rank,
-            advance=advance if k is not None else 0)
-        _native.check(self.lib.fw_shard_step(ctypes.byref(shard), stream))
+        advance = advance if k is not None else 0
+        fused = self._fused
+        if not fused:
+            self._shard_step(advance)
+        merged = alone or fused   # out / lse / sinks describe the final result
         args = _native.FwDecodeArgs(
-            q=q.data_ptr(), out=self.out.data_ptr() if alone else 0, lse=self.lse.data_ptr() if alone else 0,
+            q=q.data_ptr(), out=self.out.data_ptr() if merged else 0, lse=self.lse.data_ptr() if merged else 0,
             kv_cache=self.pool.data_ptr(), v_cache=0,
             k_new=_arrays.data_ptr(k), v_new=_arrays.data_ptr(v), append_enable=base + 8,
             cache_seqlens=base + 4, block_table=self.table.data_ptr(),
-            sinks=_arrays.data_ptr(self.sinks) if alone else 0,
-            partial_out=0 if alone else partial_out.data_ptr(),
-            partial_lse=0 if alone else partial_lse.data_ptr(),
+            sinks=_arrays.data_ptr(self.sinks) if merged else 0,
+            partial_out=0 if merged else partial_out.data_ptr(),
+            partial_lse=0 if merged else partial_lse.data_ptr(),
             num_pages=self.pool.shape[0], page_size=self.page_size,
             pages_per_seq=self.table.shape[1], batch=1, seqlen_q=1, nheads=self.nheads,
             nheads_k=self.nheads_k, head_dim=d,
@@ -243,19 +260,16 @@ class ShardedDecoder:
                 raise RuntimeError(_native.last_error())
             self.scratch = torch.zeros(nbytes, dtype=torch.uint8, device=self.device)
         args.workspace, args.workspace_bytes = self.scratch.data_ptr(), self.scratch.numel()
-        _native.check(self.lib.fw_decode_kvcache(ctypes.byref(args), stream))
-        if alone:
-            return self.out, self.lse
-        if self.exchange == "p2p":
+        if fused:
             if self.peers is None:
                 raise RuntimeError("the exchange buffers were closed.")
-            swap = _native.FwExchangeArgs(
-                peer_buffers=ctypes.cast(self.peers, ctypes.c_void_p), state_out=partial_out.data_ptr(),
-                state_lse=partial_lse.data_ptr(), sinks=_arrays.data_ptr(self.sinks),
-                out=self.out.data_ptr(), lse=self.lse.data_ptr(), status=self.scratch.data_ptr(),
-                world=self.world, rank=self.rank, rows=rows, nheads=self.nheads, head_dim=d,
-                lse_head_stride=1, lse_token_stride=self.nheads)
-            _native.check(self.lib.fw_state_exchange_merge(ctypes.byref(swap), stream))
+            whole = _native.FwShardedDecodeArgs(
+                decode=args, peer_buffers=ctypes.cast(self.peers, ctypes.c_void_p), world=self.world,
+                rank=self.rank, global_len=base, local_len=base + 4, append_enable=base + 8, advance=advance)
+            _native.check(self.lib.fw_sharded_decode_step(ctypes.byref(whole), stream))
+            return self.out, self.lse
+        _native.check(self.lib.fw_decode_kvcache(ctypes.byref(args), stream))
+        if alone:
             return self.out, self.lse
         dist.all_gather_into_tensor(self.gathered, self.state, group=self.group)
         outs, lses = unpack_states(self.gathered, self.world, rows, d)

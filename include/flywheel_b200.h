@@ -394,12 +394,17 @@ int fw_lse_combine(const FwCombineArgs* args, void* stream);
  * for one long request whose pages are split over the GPUs of a node, every
  * rank runs fw_decode_kvcache in partial-state mode and then this call, which
  * stores the rank's (o, lse) state into every peer's exchange buffer over
- * NVLink, raises a per-rank epoch flag there, waits (with an iteration limit;
- * FW_STATUS_WAIT_TIMEOUT in *status when a peer does not deliver) for the
- * flags of all ranks and merges the gathered states like fw_lse_combine.  Two
- * launches, capturable in a CUDA graph; every rank must make the same sequence
- * of calls.  (No counterpart in the reference, whose library is single-device;
- * the merge is _merge_states, patches/tpu-inference.patch:7174-7186.)
+ * NVLink as {value, epoch} pairs (each 8-byte store carries its own flag, so
+ * there is no separate flag and no system-scope fence), polls (with an
+ * iteration limit; FW_STATUS_WAIT_TIMEOUT in *status when a peer does not
+ * deliver) its own buffer until every rank's pairs carry the step's epoch and
+ * merges the gathered states like fw_lse_combine.  Two launches, capturable in
+ * a CUDA graph; every rank must make the same sequence of calls.  With
+ * state_out = state_lse = NULL only the merge is enqueued: the states were
+ * delivered by fw_sharded_decode_step(deliver_only = 1).  fw_sharded_decode_step
+ * is the fused form of the whole step and what a serving loop should call.
+ * (No counterpart in the reference, whose library is single-device; the merge
+ * is _merge_states, patches/tpu-inference.patch:7174-7186.)
  *
  * Exchange buffers: fw_peer_alloc allocates and zeroes one of
  * fw_exchange_buffer_bytes on the current device and returns a 64-byte handle;
@@ -423,6 +428,16 @@ typedef struct FwExchangeArgs {
   int32_t head_dim;
   int32_t lse_head_stride;
   int32_t lse_token_stride;
+  /* Optional round-robin bookkeeping (see fw_shard_step), advanced by the merge
+   * once the step is complete so the NEXT step needs no launch for it: when
+   * global_len is not NULL the merge adds `advance` to *global_len and writes
+   * *local_len / *append_enable for the new length.  Prime the three words with
+   * fw_shard_step(advance = 0) before the first step. */
+  int32_t* global_len;
+  int32_t* local_len;
+  int32_t* append_enable;
+  int32_t page_size;
+  int32_t advance;
 } FwExchangeArgs;
 
 uint64_t fw_exchange_buffer_bytes(int32_t world, int32_t rows, int32_t head_dim);
@@ -455,6 +470,39 @@ typedef struct FwShardStepArgs {
 } FwShardStepArgs;
 
 int fw_shard_step(const FwShardStepArgs* args, void* stream);
+
+/*
+ * One decode step of a request whose pages are split over the GPUs of a node,
+ * as three launches: the decode kernel over this rank's pages (with the fused
+ * append where append_enable says so), the combine kernel, which stores the
+ * rank's sink-free (o, lse) state straight into every rank's exchange buffer
+ * over NVLink ({value, epoch} pairs: compute and delivery in one kernel), and
+ * the merge kernel, which waits - bounded - for all ranks' states, folds the
+ * sink in and writes decode.out / decode.lse on every rank.  decode is filled
+ * as for fw_decode_kvcache (workspace of fw_decode_workspace_bytes; out / lse /
+ * sinks describe the MERGED result; partial_out / partial_lse NULL; one request
+ * or one-token requests; head_dim 128 or 256).  When global_len is not NULL the
+ * merge also advances the round-robin bookkeeping for the next step (see
+ * FwExchangeArgs), so a captured graph of this one call serves a whole
+ * generation.  deliver_only = 1 stops after the delivery (the merge is then
+ * enqueued with fw_state_exchange_merge, state_out = NULL): for tests that play
+ * several ranks on one GPU, where no kernel may wait for a later one.
+ * Device-side trouble is reported in the status word at the head of
+ * decode.workspace.
+ */
+typedef struct FwShardedDecodeArgs {
+  FwDecodeArgs decode;
+  void* const* peer_buffers;  /* host array of `world` device pointers, own buffer included */
+  int32_t world;
+  int32_t rank;
+  int32_t* global_len;        /* NULL, or the three bookkeeping words */
+  int32_t* local_len;
+  int32_t* append_enable;
+  int32_t advance;
+  int32_t deliver_only;
+} FwShardedDecodeArgs;
+
+int fw_sharded_decode_step(const FwShardedDecodeArgs* args, void* stream);
 int fw_peer_alloc(uint64_t bytes, void** ptr, void* handle64);
 int fw_peer_open(const void* handle64, void** ptr);
 int fw_peer_close(void* ptr);

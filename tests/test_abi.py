@@ -32,7 +32,7 @@ def test_struct_layouts_match_the_header(tmp_path):
     import subprocess
     from flywheel_tpu.softmax_attention import _native
     structs = ["FwDecodeArgs", "FwAppendArgs", "FwWritePagesArgs", "FwPrefillArgs", "FwCombineArgs",
-               "FwExchangeArgs", "FwShardStepArgs", "FwExtendArgs"]
+               "FwExchangeArgs", "FwShardStepArgs", "FwShardedDecodeArgs", "FwExtendArgs"]
     lines = ['#include <stddef.h>', '#include <stdio.h>', '#include "flywheel_b200.h"', 'int main(void) {']
     for name in structs:
         lines.append(f'  printf("{name} %zu\\n", sizeof({name}));')
@@ -113,9 +113,10 @@ def test_host_api_rejections_follow_the_reference():
 def test_exchange_and_packed_entry_points_validate_without_a_gpu():
     from flywheel_tpu.softmax_attention import _native
     lib = _native.library()
-    # exchange buffer: header + 2 parities x world slots of rows * (d + 1) floats, slots 16-byte aligned
-    assert lib.fw_exchange_buffer_bytes(4, 64, 128) == 4096 + 2 * 4 * 64 * 129 * 4
-    assert lib.fw_exchange_buffer_bytes(2, 6, 128) == 4096 + 2 * 2 * ((6 * 129 + 3) // 4 * 4) * 4
+    # exchange buffer: header + 2 parities x world slots of rows * (d + 1) {value, epoch} pairs,
+    # slots 16-byte aligned
+    assert lib.fw_exchange_buffer_bytes(4, 64, 128) == 4096 + 2 * 4 * 64 * 129 * 8
+    assert lib.fw_exchange_buffer_bytes(2, 5, 128) == 4096 + 2 * 2 * (5 * 129 + 1) * 8
     assert lib.fw_exchange_buffer_bytes(0, 64, 128) == 0 and "world" in _native.last_error()
     assert lib.fw_exchange_buffer_bytes(2, 64, 96) == 0
     swap = _native.FwExchangeArgs(world=2, rank=0, rows=64, nheads=64, head_dim=128)
@@ -129,6 +130,22 @@ def test_exchange_and_packed_entry_points_validate_without_a_gpu():
     swap.rank = 1
     with pytest.raises(ValueError, match=r"peer_buffers\[1\]"):
         _native.check(lib.fw_state_exchange_merge(ctypes.byref(swap), None))
+    swap.state_lse = 0
+    with pytest.raises(ValueError, match="passed together"):
+        _native.check(lib.fw_state_exchange_merge(ctypes.byref(swap), None))
+
+    # the fused sharded step validates the same way
+    step = _native.FwShardedDecodeArgs(world=2, rank=0)
+    with pytest.raises(ValueError, match="peer_buffers must not be NULL"):
+        _native.check(lib.fw_sharded_decode_step(ctypes.byref(step), None))
+    step.peer_buffers = ctypes.cast(peers, ctypes.c_void_p)
+    step.decode = _native.FwDecodeArgs(batch=2, seqlen_q=2, nheads=8, nheads_k=4, head_dim=128, block_table=1,
+                                       page_size=64, pages_per_seq=2, num_pages=4)
+    with pytest.raises(NotImplementedError, match="one request"):
+        _native.check(lib.fw_sharded_decode_step(ctypes.byref(step), None))
+    step.decode.batch, step.decode.partial_out = 1, 1
+    with pytest.raises(ValueError, match="partial_out / partial_lse must be NULL"):
+        _native.check(lib.fw_sharded_decode_step(ctypes.byref(step), None))
 
     packed = _native.FwPrefillArgs(batch=1, total_q=8, total_k=8, nheads=4, nheads_k=4, head_dim=128,
                                    kv_cache=1, v_packed=1, cu_seqlens_q=1, cu_seqlens_k=1, q=1, out=1,
