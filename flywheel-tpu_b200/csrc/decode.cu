@@ -191,7 +191,6 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int cta = blockIdx.x, hg = blockIdx.y;
-  const int n_active = load_num_active(p);
   const int heads_here = min(p.hpc, p.nheads_k - hg * p.hpc);
   const int consumer_warps = heads_here * p.mt;
   const int producer_warp = p.hpc * p.mt;
@@ -204,6 +203,7 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
     *abort_flag = 0;
     fence_barrier_init();
   }
+  const int n_active = load_num_active(p);
   scan_tiles(p, n_active, pre);  // contains __syncthreads
   // the combine grid may be set up from here on; it still waits for this grid to finish
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
