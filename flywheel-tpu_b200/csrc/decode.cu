@@ -1062,7 +1062,11 @@ static int plan_decode(const FwDecodeArgs* a, DecodePlan* plan, int max_batch = 
       p.tile *= 2;
   }
   p.stage_bytes = segs_per_stage * p.tile * 128;
-  p.stages = min(kMaxStages, smem_for_stages / p.stage_bytes);
+  // A block with few consumer warps (few KV heads on this GPU) must not take the
+  // whole SM's shared memory for its ring: as many blocks share an SM as it
+  // takes to put max_warps consumer warps there, each with at least two stages.
+  const int share = max(1, min(max_warps / (p.hpc * mt), smem_for_stages / (2 * p.stage_bytes)));
+  p.stages = min(kMaxStages, smem_for_stages / share / p.stage_bytes);
   if (p.stages < 2) {
     set_error("stage of %d bytes leaves fewer than two pipeline stages.", p.stage_bytes);
     return FW_ERR_UNSUPPORTED;
@@ -1072,6 +1076,7 @@ static int plan_decode(const FwDecodeArgs* a, DecodePlan* plan, int max_batch = 
   // Small CTAs share an SM; size the grid so every SM is covered.
   const int threads = (p.hpc * p.mt + 1) * 32;
   int per_sm = min(static_cast<int>(220 * 1024 / plan->smem), 2048 / threads);
+  per_sm = min(per_sm, 65536 / (threads * (a->head_dim > 128 ? 255 : 168)));  // registers per thread of the kernels
   per_sm = max(1, min(per_sm, 8));
   p.ncta = a->num_ctas > 0 ? a->num_ctas : max(1, sm_count() * per_sm / p.nhg);
   p.q = static_cast<const __nv_bfloat16*>(a->q);
