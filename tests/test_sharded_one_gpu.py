@@ -226,3 +226,78 @@ def test_merge_reports_a_state_that_never_arrives():
     assert float(out.float().abs().max().item()) == 0.0
     assert bool(torch.isinf(lse).all().item())
     assert int((torch.ones(4, device=dev) * 2).sum().item()) == 8   # the context still works
+
+
+def test_fused_sharded_step_with_a_batch_of_one_token_requests():
+    """The sharded step over a batch of one-token requests, two ranks played on
+    one GPU: each rank holds half of every request's keys in its own pool; a
+    request past num_active travels as the empty state and comes out as zero
+    rows with lse = -inf."""
+    import torch
+    from flywheel_tpu.softmax_attention import _native
+    lib = _native.library()
+    dev = torch.device("cuda", torch.cuda.current_device())
+    stream = torch.cuda.current_stream(dev).cuda_stream
+    rng = np.random.default_rng(11)
+    world, batch, active, heads, kv_heads, dim, page = 2, 3, 2, 8, 2, 128, 64
+    lengths = [150, 64, 90]                      # whole-request key counts
+    draw = lambda shape: rng.standard_normal(shape, dtype=np.float32).astype(oracle.BF16)
+    keys = [draw((n, kv_heads, dim)) for n in lengths]
+    values = [draw((n, kv_heads, dim)) for n in lengths]
+    q = draw((batch, 1, heads, dim))
+    to_t = lambda a: torch.from_numpy(np.ascontiguousarray(a).view(np.int16)).to(dev).view(torch.bfloat16)
+    q_t = to_t(q)
+    nbytes = lib.fw_exchange_buffer_bytes(world, batch * heads, dim)
+    buffers = [torch.zeros(nbytes, dtype=torch.uint8, device=dev) for _ in range(world)]
+    peers = (ctypes.c_void_p * world)(*[b.data_ptr() for b in buffers])
+    count = torch.tensor([active], dtype=torch.int32, device=dev)
+    states = []
+    for rank in range(world):
+        pages_per_seq = 2
+        pool = np.zeros((batch * pages_per_seq + 1, page, 2 * kv_heads, dim), oracle.BF16)
+        table = np.arange(batch * pages_per_seq, dtype=np.int32).reshape(batch, pages_per_seq) + 1
+        local = []
+        for b, n in enumerate(lengths):
+            lo, hi = (0, n // 2) if rank == 0 else (n // 2, n)
+            rows = oracle.merge_kv_heads(keys[b][lo:hi], values[b][lo:hi])     # (tokens, 2 * kv_heads, dim)
+            flat = pool[table[b]].reshape(pages_per_seq * page, 2 * kv_heads, dim)
+            flat[:hi - lo] = rows
+            pool[table[b]] = flat.reshape(pages_per_seq, page, 2 * kv_heads, dim)
+            local.append(hi - lo)
+        state = dict(pool=to_t(pool), table=torch.from_numpy(table).to(dev),
+                     lens=torch.tensor(local, dtype=torch.int32, device=dev),
+                     out=torch.full((batch, 1, heads, dim), 7.0, dtype=torch.bfloat16, device=dev),
+                     lse=torch.zeros((batch, heads, 1), dtype=torch.float32, device=dev))
+        args = _native.FwDecodeArgs(
+            q=q_t.data_ptr(), out=state["out"].data_ptr(), lse=state["lse"].data_ptr(),
+            kv_cache=state["pool"].data_ptr(), cache_seqlens=state["lens"].data_ptr(),
+            block_table=state["table"].data_ptr(), num_active=count.data_ptr(),
+            num_pages=pool.shape[0], page_size=page, pages_per_seq=pages_per_seq, batch=batch, seqlen_q=1,
+            nheads=heads, nheads_k=kv_heads, head_dim=dim, kv_dtype=0, causal=0, window_left=-1,
+            softmax_scale=dim ** -0.5, softcap=0.0)
+        size = lib.fw_decode_workspace_bytes(ctypes.byref(args))
+        assert size, _native.last_error()
+        state["scratch"] = torch.zeros(size, dtype=torch.uint8, device=dev)
+        args.workspace, args.workspace_bytes = state["scratch"].data_ptr(), size
+        whole = _native.FwShardedDecodeArgs(decode=args, peer_buffers=ctypes.cast(peers, ctypes.c_void_p),
+                                            world=world, rank=rank, deliver_only=1)
+        _native.check(lib.fw_sharded_decode_step(ctypes.byref(whole), stream))
+        states.append(state)
+    torch.cuda.synchronize()
+    for rank, state in enumerate(states):
+        merge = _native.FwExchangeArgs(
+            peer_buffers=ctypes.cast(peers, ctypes.c_void_p), out=state["out"].data_ptr(),
+            lse=state["lse"].data_ptr(), status=state["scratch"].data_ptr(), world=world, rank=rank,
+            rows=batch * heads, nheads=heads, head_dim=dim, lse_head_stride=1, lse_token_stride=heads)
+        _native.check(lib.fw_state_exchange_merge(ctypes.byref(merge), stream))
+    torch.cuda.synchronize()
+    for state in states:
+        got, got_lse = state["out"].float().cpu().numpy(), state["lse"].cpu().numpy()
+        for b in range(active):
+            want, want_lse = oracle.attend_rows(
+                q[b].astype(np.float32), keys[b].astype(np.float32), values[b].astype(np.float32),
+                total=lengths[b], causal=True, window_left=None, softcap=0.0, scale=dim ** -0.5, sinks=None)
+            np.testing.assert_allclose(got[b], want, rtol=1e-2, atol=2e-2)
+            np.testing.assert_allclose(got_lse[b, :, 0], want_lse[:, 0], rtol=2e-3, atol=4e-3)
+        assert np.all(got[active:] == 0.0) and np.all(np.isneginf(got_lse[active:]))
+        assert _native.read_status(state["scratch"], dev) == 0
