@@ -627,6 +627,12 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
       }
       }
 
+      // Every lane's ldmatrix reads of this stage must be performed before lane 0
+      // tells the producer the stage is free: without the fence the arrive could
+      // overtake a read still in flight, and a stage refilled at once (a block
+      // that waited for its slowest warp) was seen half old, half new - rarely,
+      // by one warp, in one 16-column block of O.
+      __threadfence_block();
       __syncwarp();
       if (lane == 0) mbar_arrive(&empty_bar[stage]);
       if (++stage == p.stages) {

@@ -95,3 +95,26 @@ def test_chunked_prefill_kernels_agree_at_full_size(monkeypatch):
         np.arange(n_pages, dtype=np.int32)[None], nheads_k=bench.PF_HK, causal=True)
     got = results["tcgen05"][:, lo:hi].cpu().numpy().transpose(1, 0, 2)
     np.testing.assert_allclose(got, want, rtol=1e-2, atol=2e-2)
+
+
+def test_split_kv_prefill_is_bit_stable_over_many_runs():
+    """The split-KV route at full size, 100 times on one workspace: every run
+    must reproduce the first bit for bit.  A stage of the K/V ring released
+    before a warp's last ldmatrix of it had been performed showed up as one
+    16-column block of a few rows changing in about one run of a hundred; the
+    item order (a sort with atomics) changes from run to run and must not show
+    either."""
+    import torch
+    import bench
+    from flywheel_tpu.softmax_attention import _native
+    dev = torch.device("cuda", torch.cuda.current_device())
+    work = bench.build_prefill_workload(0, dev)
+    call, out, scratch = bench.make_prefill_call(work, dev, route="splitkv")
+    call()
+    torch.cuda.synchronize()
+    first = out.view(torch.int16).clone()
+    for _ in range(100):
+        call()
+        torch.cuda.synchronize()
+        assert bool((out.view(torch.int16) == first).all())
+    assert _native.read_status(scratch, dev) == 0
