@@ -310,6 +310,7 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
   int stage = 0;
   uint32_t phase = 0;
   bool ok = true;
+  bool next_full = false;  // the stage of the coming tile was seen full (valid across requests: one ring)
 
   int b = find_request(pre, p.batch, f0);
   for (int f = f0; f < f1 && ok;) {
@@ -359,7 +360,8 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
 
     for (; f < seg_end; ++f) {
       const int pos0 = (f - pre[b] + sp.first_tile) * TILE;
-      if (!mbar_wait_bounded(&full_bar[stage], phase, abort_flag)) {
+      // (the previous tile has usually seen this stage full already, under its PV MMAs)
+      if (!next_full && !mbar_wait_bounded(&full_bar[stage], phase, abort_flag)) {
         ok = false;
         break;
       }
@@ -578,6 +580,12 @@ decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__
         }
       }
 
+      // Is the next stage full yet?  Asked here, without blocking, so that the
+      // answer's latency hides under the PV MMAs instead of opening the next tile.
+      {
+        const int ns = stage + 1 == p.stages ? 0 : stage + 1;
+        next_full = mbar_test_wait(&full_bar[ns], ns == 0 ? phase ^ 1 : phase);
+      }
       // ---- O += P V, one 16-key k-step per sub-tile
 #pragma unroll
       for (int u = 0; u < NU; ++u) {
