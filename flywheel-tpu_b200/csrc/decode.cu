@@ -30,6 +30,9 @@
 namespace fw {
 
 constexpr int kTile = 16;          // smallest stage: tokens per MMA k-step; page sizes are multiples of it
+#ifndef FW_BF16_MULTI_SLICE_STAGE_TOKENS
+#define FW_BF16_MULTI_SLICE_STAGE_TOKENS 32  // bf16 stage size when two or more warps share a KV head (16 or 32)
+#endif
 #ifndef FW_VERIFY_STAGE_TOKENS
 #define FW_VERIFY_STAGE_TOKENS 32  // fp8 stage size when two or more warps share a KV head (16, 32 or 64)
 #endif
@@ -1069,9 +1072,13 @@ static int plan_decode(const FwDecodeArgs* a, DecodePlan* plan, int max_batch = 
   // must divide the page.
   p.tile = kTile;
   const int smem_for_stages = 200 * 1024;
-  if (itemsize == 1) {
-    // Verify windows (two or more 16-row slices per head) measured best at 32.
-    const int max_tile = a->head_dim > 128 ? kTile : mt >= 2 ? FW_VERIFY_STAGE_TOKENS : 64;
+  {
+    // fp8: verify windows (two or more 16-row slices per head) measured best at 32.
+    // bf16 with two or more slices per head is bound by its consumers too (every
+    // byte feeds two warps' MMAs): 32-token stages halve the per-stage costs.
+    const int max_tile = a->head_dim != 128 ? kTile
+                         : itemsize == 1    ? (mt >= 2 ? FW_VERIFY_STAGE_TOKENS : 64)
+                                            : (mt >= 2 ? FW_BF16_MULTI_SLICE_STAGE_TOKENS : kTile);
     while (p.tile < max_tile && segs_per_stage * (p.tile * 2) * 128 <= 64 * 1024 && a->page_size % (p.tile * 2) == 0)
       p.tile *= 2;
   }
@@ -1175,7 +1182,7 @@ static int launch_decode(DecodePlan& plan, void* workspace, cudaStream_t stream,
   } else if (p.head_dim == 64) {
     kernel = decode_kernel<FW_DTYPE_BF16, 16, 64>;
   } else if (kv_dtype == FW_DTYPE_BF16) {
-    kernel = decode_kernel<FW_DTYPE_BF16, 16>;
+    kernel = p.tile == 32 ? decode_kernel<FW_DTYPE_BF16, 32> : decode_kernel<FW_DTYPE_BF16, 16>;
   } else if (kv_dtype == FW_DTYPE_E4M3) {
     kernel = p.tile == 64   ? decode_kernel<FW_DTYPE_E4M3, 64>
              : p.tile == 32 ? decode_kernel<FW_DTYPE_E4M3, 32>
