@@ -53,7 +53,12 @@ __global__ void __launch_bounds__(128) scatter_state_kernel(const ScatterParams 
 __global__ void __launch_bounds__(128) gather_merge_kernel(const MergeParams p) {
   uint8_t* mine = p.slots.peers[p.slots.rank];
   uint32_t* header = reinterpret_cast<uint32_t*>(mine);
-  asm volatile("griddepcontrol.wait;" ::: "memory");  // this rank's sending kernel is done
+  // No griddepcontrol.wait: the pairs carry their own validity, so the blocks may
+  // start polling while this rank's sending kernel still runs.  (That kernel
+  // releases its dependents only after the decode grid is complete; the epoch
+  // below was advanced by the previous step's merge, long done; and the last
+  // block's bookkeeping runs only after every row of every rank - this rank's
+  // sender included - has been delivered.)
   const uint32_t epoch = step_epoch(mine);
   const int world = p.slots.world;
   const int row = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
