@@ -404,7 +404,8 @@ def bench_prefill(ns, ranks):
                 flash_attn_varlen_func(       # host q in, host out back (the API copies it)
                     work["q_host"], work["pool"], None, work["cu"], None, int(work["chunk"].max()),
                     int(work["seqused"].max()), causal=True, block_table=work["table"],
-                    seqused_k=work["seqused"], k_descale=work["descale"], v_descale=work["descale"])
+                    seqused_k=work["seqused"], k_descale=work["descale"], v_descale=work["descale"],
+                    nheads_k=PF_HK)
 
         e2e_pass()
         e2e_ms = timed_rounds(e2e_pass, 3, ranks, rounds=3, min_round_s=0.0)["ms_per_step"]

@@ -75,6 +75,7 @@ __global__ void __launch_bounds__(64 + kStreams * 128 + (KVT == FW_DTYPE_BF16 ? 
 prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv,
                        const __grid_constant__ CUtensorMap map_v, const Tc05Params p) {
   constexpr bool kFp8 = KVT != FW_DTYPE_BF16;
+  constexpr bool kF16 = kFp8;  // fp8 pools: Q, K, V and P go to the tensor core as f16 (bf16 pools: bf16)
   extern __shared__ __align__(1024) uint8_t smem[];
   Bars* bars = reinterpret_cast<Bars*>(smem + kSmemBar);
   volatile int* abort_flag = &bars->abort_flag;
@@ -242,8 +243,8 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     // read P.  The two streams alternate, which keeps the tensor pipe busy with
     // one stream's MMAs while the other stream's softmax group works.
     if (lane == 0) {
-      constexpr uint32_t idesc_qk = instr_desc(kBN, false);
-      constexpr uint32_t idesc_pv = instr_desc(D, true);
+      constexpr uint32_t idesc_qk = instr_desc(kBN, false, kF16);
+      constexpr uint32_t idesc_pv = instr_desc(D, true, kF16);
       const uint64_t q_desc0 = smem_desc(smem_u32(smem + kSmemQ), 16, 1024);
       const uint64_t k_desc0 = smem_desc(smem_u32(smem + kSmemK), 16, 1024);
       const uint64_t v_desc0 = smem_desc(smem_u32(smem + kSmemV), 16384, 1024);
@@ -258,8 +259,8 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         }
         tc_commit(&bars->s_full[t]);
       };
-      // with a rotary embedding the softmax warps rotate their rows of Q first
-      bool ok = p.rotary_cos != nullptr ? FW_WAIT(19, 0, &bars->q_rotated, 0) : FW_WAIT(2, 0, &bars->q_full, 0);
+      // with a rotary embedding, or f16 operands, the softmax warps rework their rows of Q first
+      bool ok = p.rotary_cos != nullptr || kF16 ? FW_WAIT(19, 0, &bars->q_rotated, 0) : FW_WAIT(2, 0, &bars->q_full, 0);
       if (ok) ok = FW_WAIT(3, 0, &bars->k_full[0], 0);
       if (ok) {
         tc_fence_after();
@@ -329,11 +330,9 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             uint32_t wide[8];
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
-              const uint32_t lo = fp8_half_to_f16x2<KVT, false>(w[i]), hi = fp8_half_to_f16x2<KVT, true>(w[i]);
-              const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&lo));
-              const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&hi));
-              wide[2 * i] = pack_bf16(a.x, a.y);
-              wide[2 * i + 1] = pack_bf16(b.x, b.y);
+              // every fp8 value is an f16 value: one conversion per pair, no rounding
+              wide[2 * i] = fp8_half_to_f16x2<KVT, false>(w[i]);
+              wide[2 * i + 1] = fp8_half_to_f16x2<KVT, true>(w[i]);
             }
             *reinterpret_cast<uint4*>(tile + dst_a + (n0 + n) * 1024) = make_uint4(wide[0], wide[1], wide[2], wide[3]);
             *reinterpret_cast<uint4*>(tile + dst_b + (n0 + n) * 1024) = make_uint4(wide[4], wide[5], wide[6], wide[7]);
@@ -387,14 +386,17 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     float m_used = -INFINITY, l_run = 0.f;
     bool ok = true;
 
-    if (p.rotary_cos != nullptr && n_tiles > 0) {
+    if ((p.rotary_cos != nullptr || kF16) && n_tiles > 0) {
       // Rotary embedding, fused: this thread's softmax row is also its row of the
       // Q tile the TMA copy left in shared memory; rotate it in place at the
       // row's own key position (its diagonal) before the first QK MMA reads it.
+      // With an fp8 pool the MMAs take f16 operands (the pool's values widen to
+      // f16 exactly, with one conversion per pair), so the row becomes f16 here.
       ok = FW_WAIT(20 + t, 0, &bars->q_full, 0);
       if (ok) {
-        if (row_ok && diag >= 0 && diag < p.rotary_len)
+        if (p.rotary_cos != nullptr && row_ok && diag >= 0 && diag < p.rotary_len)
           rotate_q_row_in_smem<D>(smem + kSmemQ + t * 32768, 16384, row, diag, p);
+        if constexpr (kF16) q_row_bf16_to_f16_in_smem<D>(smem + kSmemQ + t * 32768, 16384, row);
         fence_proxy_async_smem();
         __syncwarp();
         if (lane == 0) mbar_arrive(&bars->q_rotated);
@@ -469,10 +471,10 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                   exp2_pair<true>(y2, p0, p1);
                 else
                   exp2_pair<false>(y2, p0, p1);
-                pk = pack_bf16(p0, p1);
+                pk = kF16 ? pack_f16(p0, p1) : pack_bf16(p0, p1);
               }
               sum2 = add2(sum2, pack2(p0, p1));
-              if constexpr (!kTrueMax && FW_OVER_BY_SUM == 0) pmax = max_bf16x2(pmax, pk);
+              if constexpr (!kTrueMax && FW_OVER_BY_SUM == 0) pmax = kF16 ? max_f16x2(pmax, pk) : max_bf16x2(pmax, pk);
               packed[half][c * 16 + (i >> 1)] = pk;
             }
         }
@@ -482,7 +484,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         top = fmaxf(top0, top1);  // row max minus the base (the row max itself when the base is 0)
         // bf16 bit patterns of non-negative values order like integers
         if constexpr (FW_OVER_BY_SUM != 0) over = sum > 256.0f;  // no P can be above 2^8 unless their sum is
-        else over = max(pmax & 0xffffu, pmax >> 16) > 0x4380u;  // bf16(256.0) = 2^kRescaleThreshold
+        else over = max(pmax & 0xffffu, pmax >> 16) > (kF16 ? 0x5c00u : 0x4380u);  // 256.0 = 2^kRescaleThreshold as f16 / bf16
       };
       static_assert(kRescaleThreshold == 8.0f, "the bf16 constant above is 2^8");
       float alpha = 1.f;

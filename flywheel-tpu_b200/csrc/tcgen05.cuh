@@ -192,10 +192,33 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes,
   return d;
 }
 
-// kind::f16 instruction descriptor: f32 accumulate, bf16 A and B, M = 128.
-__host__ __device__ constexpr uint32_t instr_desc(int n, bool b_mn_major) {
-  return (1u << 4) | (1u << 7) | (1u << 10) | (b_mn_major ? (1u << 16) : 0u) |
+// kind::f16 instruction descriptor: f32 accumulate, A and B both bf16 (format 1)
+// or both f16 (format 0), M = 128.
+__host__ __device__ constexpr uint32_t instr_desc(int n, bool b_mn_major, bool f16_operands = false) {
+  return (1u << 4) | (f16_operands ? 0u : (1u << 7) | (1u << 10)) | (b_mn_major ? (1u << 16) : 0u) |
          (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(kBM >> 4) << 24);
+}
+
+// One row of a Q tile in shared memory (128-byte swizzle, 64-element blocks
+// `block_bytes` apart) converted in place from bf16 to f16, finite values kept
+// finite.  Element positions do not change, so the swizzle does not matter.
+template <int D>
+__device__ __forceinline__ void q_row_bf16_to_f16_in_smem(uint8_t* q_tile, int block_bytes, int row) {
+#pragma unroll
+  for (int block = 0; block < D / 64; ++block)
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+      uint4* ptr = reinterpret_cast<uint4*>(q_tile + block * block_bytes + row * 128 + (c << 4));
+      uint4 v = *ptr;
+      auto convert = [](uint32_t two_bf16) {
+        return pack_f16_sat(__uint_as_float(two_bf16 << 16), __uint_as_float(two_bf16 & 0xffff0000u));
+      };
+      v.x = convert(v.x);
+      v.y = convert(v.y);
+      v.z = convert(v.z);
+      v.w = convert(v.w);
+      *ptr = v;
+    }
 }
 
 // 2^y for two scores, on the special-function unit (two ex2.approx) or, with
