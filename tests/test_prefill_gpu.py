@@ -177,6 +177,33 @@ def test_varlen_func_fp8(dtype):
     check_rows(out.astype(np.float32).transpose(1, 0, 2), lse, want, want_lse, FP8_TOL)
 
 
+@pytest.mark.parametrize("q_scale,rotary", [(1e-3, False), (48.0, False), (1.0, True)])
+def test_varlen_func_fp8_query_ranges_and_rotary(q_scale, rotary):
+    """fp8 pools go to the tensor core with f16 operands: Q is converted from
+    bf16 to f16 in shared memory (after the fused rotation, when there is one).
+    Small queries (elements down to f16 subnormals), large ones (logits of tens of
+    nats) and rotated ones must all stay within the fp8 tolerance."""
+    import ml_dtypes
+    from flywheel_tpu import flash_attn_varlen_func
+    c = random_prefill_case(12, prefixes=(200, 0, 700), chunks=(90, 64, 150), hq=8, hk=2,
+                            page_size=64, dtype=ml_dtypes.float8_e4m3fn)
+    q = (c["q"].astype(np.float32) * np.float32(q_scale)).astype(oracle.BF16)
+    kwargs, q_ref = {}, q
+    if rotary:
+        angle = np.random.default_rng(29).random((900, 64)) * 2 * np.pi
+        cos, sin = np.cos(angle).astype(np.float32), np.sin(angle).astype(np.float32)
+        kwargs = dict(rotary_cos=cos, rotary_sin=sin, rotary_interleaved=False, rotary_k=False)
+        q_ref = oracle.rotate_packed_q(q, cos, sin, c["cu"], c["seqused"], False)
+    out, lse = flash_attn_varlen_func(
+        np.ascontiguousarray(q.transpose(1, 0, 2)), to_cuda(c["pool"]), None, c["cu"], None, 150, 900,
+        causal=True, return_softmax_lse=True, block_table=c["table"], seqused_k=c["seqused"],
+        k_descale=c["kd"], v_descale=c["vd"], nheads_k=2, **kwargs)
+    want, want_lse = oracle.ragged_paged_attention(
+        q_ref, c["pool"], c["cu"], c["seqused"], c["table"], nheads_k=2, causal=True,
+        k_descale=c["kd"], v_descale=c["vd"])
+    check_rows(out.astype(np.float32).transpose(1, 0, 2), lse, want, want_lse, FP8_TOL)
+
+
 @pytest.mark.parametrize("window_left", [None, 700])
 def test_needle_probes_at_tile_and_page_edges(window_left):
     """The needle-probe construction of the reference's paged tests
